@@ -1,0 +1,19 @@
+// Entry points each kernel translation unit gives the C-ABI launcher.
+#pragma once
+
+#include "fa_params.cuh"
+
+namespace atrex_sm100 {
+
+// ---- fa_mma.cu: split-KV mma.sync kernel ----
+int mma_rows_for(int packed_rows);            // 16, 32 or 64 rows per CTA
+cudaError_t mma_prepare();                    // per-device kernel attributes
+cudaError_t mma_launch(const FwdParams& p, int head_dim, int m_rows, cudaStream_t stream);
+
+// ---- fa_combine.cu: merge split partials; tile plan ----
+cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream);
+// order[batch], tile_prefix[batch + 1] for row tiles of m_rows packed rows
+cudaError_t plan_launch(const FwdParams& p, int m_rows, int32_t* order, int32_t* tile_prefix,
+                        cudaStream_t stream);
+
+}  // namespace atrex_sm100

@@ -1,0 +1,344 @@
+// C-ABI launcher of the sm_100a attention kernels (declared in include/atrex_fa_sm100.h).
+//
+// Host-only logic: argument checks, the route / split policy (from graph-static
+// sizes only, as the reference's decode policy insists,
+// src/nvidia/flash_attn/sm103/decode_runtime.py:443-470), TMA descriptor
+// encoding, workspace carving and the launches.  Nothing here allocates,
+// synchronises or reads device memory.
+#include <atomic>
+#include <cstring>
+
+#include "atrex_fa_sm100.h"
+#include "fa_kernels.cuh"
+
+namespace atrex_sm100 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int kMaxSplits = 256;
+constexpr int kTileN = 64;
+
+struct DeviceInfo {
+  std::atomic<int> state{0};  // 0 unknown, 1 usable, -1 wrong architecture
+  std::atomic<int> prepared{0};
+  int sm_count = 0;
+};
+DeviceInfo g_devices[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::atomic<EncodeTiledFn> g_encode{nullptr};
+
+EncodeTiledFn encode_fn() {
+  EncodeTiledFn fn = g_encode.load(std::memory_order_acquire);
+  if (fn != nullptr) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || sym == nullptr)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  g_encode.store(fn, std::memory_order_release);
+  return fn;
+}
+
+int current_device(DeviceInfo** info) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+  if (dev < 0 || dev >= kMaxDevices) return ATREX_FA_UNSUPPORTED;
+  DeviceInfo& d = g_devices[dev];
+  int st = d.state.load(std::memory_order_acquire);
+  if (st == 0) {
+    int major = 0, minor = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return ATREX_FA_CUDA_ERROR;
+    d.sm_count = sms;
+    st = (major == 10 && minor == 0) ? 1 : -1;
+    d.state.store(st, std::memory_order_release);
+  }
+  *info = &d;
+  return st == 1 ? ATREX_FA_OK : ATREX_FA_WRONG_DEVICE;
+}
+
+int prepare_device(DeviceInfo& d) {
+  if (d.prepared.load(std::memory_order_acquire)) return ATREX_FA_OK;
+  if (mma_prepare() != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+  d.prepared.store(1, std::memory_order_release);
+  return ATREX_FA_OK;
+}
+
+inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+struct Resolved {
+  int route, m_rows, splits, launches;
+  bool tiled;          // more than one row tile per request possible -> device plan
+  int num_row_tiles;   // grid upper bound
+  uint64_t off_order, off_prefix, off_lse, off_o, bytes;
+};
+
+int check_params(const atrex_fa_sm100_params* p) {
+  if (p == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (p->struct_bytes != sizeof(atrex_fa_sm100_params) || p->abi_version != ATREX_FA_SM100_ABI_VERSION)
+    return ATREX_FA_ABI_MISMATCH;
+  if (p->batch < 0 || p->total_q < 0 || p->total_k < 0 || p->num_pages < 0 || p->page_size < 0 ||
+      p->max_seqlen_q < 0 || p->max_seqlen_k < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 ||
+      p->num_q_heads % p->num_kv_heads != 0 || p->num_splits < 0)
+    return ATREX_FA_INVALID_VALUE;
+  if (p->cu_seqlens_q == nullptr || p->out == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (p->total_q > 0 && p->q == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (p->page_size > 0) {
+    if (p->block_table == nullptr || p->seqused_k == nullptr) return ATREX_FA_INVALID_VALUE;
+  } else if (p->cu_seqlens_k == nullptr) {
+    return ATREX_FA_INVALID_VALUE;
+  }
+  if (p->return_lse && p->lse == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (p->softcap < 0.f) return ATREX_FA_INVALID_VALUE;
+  if (p->head_dim != 128 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;
+  if (p->dtype != ATREX_FA_BF16) return ATREX_FA_UNSUPPORTED;  // E4M3 belongs to the tcgen05 route
+  if (p->num_splits > kMaxSplits) return ATREX_FA_UNSUPPORTED;
+  if (p->page_size > 0 && p->page_size % 64 != 0 && p->page_size != 16 && p->page_size != 32)
+    return ATREX_FA_UNSUPPORTED;
+  if (p->route != ATREX_FA_ROUTE_AUTO && p->route != ATREX_FA_ROUTE_MMA) return ATREX_FA_UNSUPPORTED;
+  // 16-byte alignment of everything the kernels touch with vectors or TMA
+  const uint64_t es = 2;
+  auto misaligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0; };
+  if (misaligned(p->q) || misaligned(p->k) || misaligned(p->v) || misaligned(p->out)) return ATREX_FA_UNSUPPORTED;
+  const int64_t strides[] = {p->q_row_stride, p->q_head_stride, p->k_row_stride, p->k_head_stride,
+                             p->v_row_stride, p->v_head_stride, p->out_row_stride, p->out_head_stride,
+                             p->page_size ? p->k_page_stride : 0, p->page_size ? p->v_page_stride : 0};
+  for (int64_t s : strides)
+    if (s < 0 || (static_cast<uint64_t>(s) * es) % 16 != 0) return ATREX_FA_UNSUPPORTED;
+  return ATREX_FA_OK;
+}
+
+int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
+  const int group = p->num_q_heads / p->num_kv_heads;
+  const int64_t packed_max = (int64_t)p->max_seqlen_q * group;
+  r->route = ATREX_FA_ROUTE_MMA;
+  r->m_rows = mma_rows_for((int)(packed_max > 64 ? 64 : packed_max));
+  r->tiled = packed_max > r->m_rows;
+  const int64_t tiles_bound =
+      r->tiled ? ((int64_t)p->total_q * group) / r->m_rows + p->batch : (int64_t)p->batch;
+  if (tiles_bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
+  r->num_row_tiles = (int)tiles_bound;
+
+  // keys one row tile can see, at the upper bound (a two-sided window limits it)
+  int64_t span = p->max_seqlen_k;
+  if (p->window_left >= 0 && (p->causal || p->window_right >= 0)) {
+    const int64_t rows_q = r->tiled ? (r->m_rows + group - 1) / group + 1 : p->max_seqlen_q;
+    const int64_t w = (int64_t)p->window_left + rows_q + (p->causal ? 0 : p->window_right) + 1 + kTileN;
+    if (w < span) span = w;  // + one tile above: the window need not start on a tile edge
+  }
+  const int kv_tiles = (int)((span + kTileN - 1) / kTileN);
+  int splits;
+  if (p->num_splits > 0) {
+    splits = p->num_splits;
+  } else {
+    const int64_t items = (int64_t)r->num_row_tiles * p->num_kv_heads;
+    const int64_t slots = (int64_t)sm_count * (p->head_dim == 128 ? 2 : 1);
+    const int64_t want = items > 0 ? (slots * 8 + items - 1) / items : 1;  // about eight waves of CTAs
+    const int64_t cap = kv_tiles / 8;                                      // >= 512 keys per split
+    splits = (int)(want < cap ? want : cap);
+  }
+  if (splits > kv_tiles) splits = kv_tiles;
+  if (splits > kMaxSplits) splits = kMaxSplits;
+  if (splits < 1) splits = 1;
+  r->splits = splits;
+  r->launches = 1 + (r->tiled ? 1 : 0) + (splits > 1 ? 1 : 0);
+
+  uint64_t off = 0;
+  r->off_order = off;
+  if (r->tiled) off = align_up(off + 4ull * p->batch, 256);
+  r->off_prefix = off;
+  if (r->tiled) off = align_up(off + 4ull * (p->batch + 1), 256);
+  r->off_lse = off;
+  if (splits > 1) off = align_up(off + 4ull * splits * p->total_q * p->num_q_heads, 256);
+  r->off_o = off;
+  if (splits > 1) off = align_up(off + 4ull * splits * p->total_q * p->num_q_heads * p->head_dim, 256);
+  r->bytes = off;
+  return ATREX_FA_OK;
+}
+
+// K or V as a 4-D tensor (D, heads, rows, pages).  The three outer dimensions
+// are handed to the encoder in ascending-stride order (HND cache views have the
+// head stride above the row stride); perm[] tells the kernel where each went.
+int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64_t row_stride,
+                  int64_t page_stride, int heads, int64_t rows, int64_t pages, int head_dim, int box_rows,
+                  int8_t perm[3]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return ATREX_FA_CUDA_ERROR;
+  struct Dim { uint64_t extent, stride; uint32_t box; int which; };
+  Dim dims[3] = {{(uint64_t)heads, (uint64_t)head_stride * 2, 1u, 0},
+                 {(uint64_t)rows, (uint64_t)row_stride * 2, (uint32_t)box_rows, 1},
+                 {(uint64_t)pages, (uint64_t)page_stride * 2, 1u, 2}};
+  for (int i = 0; i < 3; ++i)       // extent-1 dimensions never move: give them a harmless stride
+    if (dims[i].extent <= 1) { dims[i].extent = 1; }
+  for (int i = 0; i < 3; ++i)
+    for (int j = i + 1; j < 3; ++j)
+      if (dims[j].stride < dims[i].stride) { Dim t = dims[i]; dims[i] = dims[j]; dims[j] = t; }
+  cuuint64_t extent[4] = {(cuuint64_t)head_dim, dims[0].extent, dims[1].extent, dims[2].extent};
+  cuuint64_t stride[3] = {dims[0].stride, dims[1].stride, dims[2].stride};
+  cuuint32_t box[4] = {64u, dims[0].box, dims[1].box, dims[2].box};
+  cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
+  for (int i = 0; i < 3; ++i) {
+    if (stride[i] == 0) stride[i] = 16;  // extent-1 dimension with a zero stride
+    if (stride[i] % 16 != 0 || stride[i] >= (1ull << 40)) return ATREX_FA_UNSUPPORTED;
+    perm[dims[i].which] = (int8_t)i;
+  }
+  const CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), extent, stride, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return res == CUDA_SUCCESS ? ATREX_FA_OK : ATREX_FA_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace atrex_sm100
+
+using namespace atrex_sm100;
+
+extern "C" {
+
+int atrex_fa_sm100_abi_version(void) { return ATREX_FA_SM100_ABI_VERSION; }
+
+size_t atrex_fa_sm100_params_bytes(void) { return sizeof(atrex_fa_sm100_params); }
+
+const char* atrex_fa_sm100_status_string(int status) {
+  switch (status) {
+    case ATREX_FA_OK: return "ok";
+    case ATREX_FA_INVALID_VALUE: return "invalid value in attention parameters";
+    case ATREX_FA_UNSUPPORTED: return "well-formed call that the sm100 kernels do not serve (dtype, head_dim, page_size, alignment or route)";
+    case ATREX_FA_WORKSPACE_TOO_SMALL: return "workspace is missing, misaligned or smaller than the plan requires";
+    case ATREX_FA_CUDA_ERROR: return "a CUDA runtime or driver call failed";
+    case ATREX_FA_WRONG_DEVICE: return "current CUDA device is not compute capability 10.0 (sm_100a)";
+    case ATREX_FA_ABI_MISMATCH: return "parameter block does not match this library's ABI version or size";
+    default: return "unknown status";
+  }
+}
+
+int atrex_fa_sm100_plan(const atrex_fa_sm100_params* p, atrex_fa_sm100_plan_info* plan) {
+  if (plan == nullptr) return ATREX_FA_INVALID_VALUE;
+  int st = check_params(p);
+  if (st != ATREX_FA_OK) return st;
+  int sm_count = p->sm_count;
+  if (sm_count <= 0) {
+    DeviceInfo* info = nullptr;
+    st = current_device(&info);
+    if (st != ATREX_FA_OK) return st;
+    sm_count = info->sm_count;
+  }
+  Resolved r;
+  st = resolve(p, sm_count, &r);
+  if (st != ATREX_FA_OK) return st;
+  plan->route = r.route;
+  plan->num_splits = r.splits;
+  plan->kernel_launches = r.launches;
+  plan->m_rows = r.m_rows;
+  plan->workspace_bytes = r.bytes;
+  return ATREX_FA_OK;
+}
+
+int atrex_fa_sm100_prewarm(void) {
+  DeviceInfo* info = nullptr;
+  const int st = current_device(&info);
+  if (st != ATREX_FA_OK) return st;
+  return prepare_device(*info);
+}
+
+int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint64_t workspace_bytes,
+                           void* stream_ptr) {
+  int st = check_params(p);
+  if (st != ATREX_FA_OK) return st;
+  DeviceInfo* info = nullptr;
+  st = current_device(&info);
+  if (st != ATREX_FA_OK) return st;
+  Resolved r;
+  st = resolve(p, p->sm_count > 0 ? p->sm_count : info->sm_count, &r);
+  if (st != ATREX_FA_OK) return st;
+  if (r.bytes > 0 && (workspace == nullptr || workspace_bytes < r.bytes ||
+                      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0))
+    return ATREX_FA_WORKSPACE_TOO_SMALL;
+  if (p->batch == 0 || p->total_q == 0) return ATREX_FA_OK;
+  st = prepare_device(*info);
+  if (st != ATREX_FA_OK) return st;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  FwdParams f;
+  std::memset(&f, 0, sizeof(f));
+  const bool paged = p->page_size > 0;
+  const int64_t rows = paged ? p->page_size : p->total_k;
+  const int64_t pages = paged ? p->num_pages : 1;
+  const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
+  const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
+  int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
+  if (empty_kv) {
+    // No key exists: the kernels will not issue a copy, but the descriptors must still be valid.
+    st = encode_kv_map(&f.k_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, kperm);
+    if (st == ATREX_FA_OK)
+      st = encode_kv_map(&f.v_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, vperm);
+  } else {
+    st = encode_kv_map(&f.k_map, p->k, p->k_head_stride, p->k_row_stride,
+                       paged ? p->k_page_stride : p->k_row_stride * rows, p->num_kv_heads, rows, pages,
+                       p->head_dim, box_rows, kperm);
+    if (st == ATREX_FA_OK)
+      st = encode_kv_map(&f.v_map, p->v, p->v_head_stride, p->v_row_stride,
+                         paged ? p->v_page_stride : p->v_row_stride * rows, p->num_kv_heads, rows, pages,
+                         p->head_dim, box_rows, vperm);
+  }
+  if (st != ATREX_FA_OK) return st;
+  for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
+
+  f.q = p->q; f.out = p->out; f.lse = p->return_lse ? p->lse : nullptr;
+  f.cu_seqlens_q = p->cu_seqlens_q;
+  f.cu_seqlens_k = paged ? nullptr : p->cu_seqlens_k;
+  f.seqused_k = p->seqused_k;
+  f.block_table = p->block_table;
+  f.q_descale = p->q_descale; f.k_descale = p->k_descale; f.v_descale = p->v_descale;
+  f.sink = static_cast<const __nv_bfloat16*>(p->sink);
+  f.status = p->device_status;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (r.tiled) {
+    f.order = reinterpret_cast<int32_t*>(ws + r.off_order);
+    f.tile_prefix = reinterpret_cast<int32_t*>(ws + r.off_prefix);
+  }
+  if (r.splits > 1) {
+    f.part_lse = reinterpret_cast<float*>(ws + r.off_lse);
+    f.part_o = reinterpret_cast<float*>(ws + r.off_o);
+  }
+  f.q_row_stride = p->q_row_stride; f.q_head_stride = p->q_head_stride;
+  f.out_row_stride = p->out_row_stride; f.out_head_stride = p->out_head_stride;
+  f.block_table_row_stride = p->block_table_row_stride;
+  f.q_descale_bs = p->q_descale_batch_stride; f.q_descale_hs = p->q_descale_head_stride;
+  f.k_descale_bs = p->k_descale_batch_stride; f.k_descale_hs = p->k_descale_head_stride;
+  f.v_descale_bs = p->v_descale_batch_stride; f.v_descale_hs = p->v_descale_head_stride;
+  f.batch = p->batch; f.total_q = p->total_q; f.total_k = p->total_k;
+  f.num_pages = empty_kv ? 0 : (int)pages;
+  f.page_size = p->page_size; f.box_rows = box_rows;
+  f.num_q_heads = p->num_q_heads; f.num_kv_heads = p->num_kv_heads;
+  f.group = p->num_q_heads / p->num_kv_heads;
+  f.causal = p->causal ? 1 : 0;
+  f.window_left = p->window_left < 0 ? -1 : p->window_left;
+  f.window_right = p->causal ? 0 : (p->window_right < 0 ? -1 : p->window_right);
+  f.num_splits = r.splits;
+  f.num_row_tiles = r.num_row_tiles;
+  f.softmax_scale = p->softmax_scale;
+  f.softcap = p->softcap;
+
+  if (r.tiled &&
+      plan_launch(f, r.m_rows, const_cast<int32_t*>(f.order), const_cast<int32_t*>(f.tile_prefix), stream) !=
+          cudaSuccess)
+    return ATREX_FA_CUDA_ERROR;
+  if (p->profile_event_begin != nullptr &&
+      cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream) != cudaSuccess)
+    return ATREX_FA_CUDA_ERROR;
+  if (mma_launch(f, p->head_dim, r.m_rows, stream) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+  if (p->profile_event_end != nullptr &&
+      cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream) != cudaSuccess)
+    return ATREX_FA_CUDA_ERROR;
+  if (r.splits > 1 && combine_launch(f, p->head_dim, stream) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+  return ATREX_FA_OK;
+}
+
+}  // extern "C"

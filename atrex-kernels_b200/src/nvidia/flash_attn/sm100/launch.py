@@ -1,0 +1,39 @@
+"""Launch policy of the sm_100a attention path: ``forward(**kwargs) -> (out, lse)``.
+
+Same private ABI as the reference's per-arch launch modules
+(src/nvidia/flash_attn/sm103/launch.py:282-311; keywords listed at
+python/atrex/api/flash_attn.py:396-420).  The caller has already validated the
+call.  This module allocates what the caller did not pass (``out``, ``lse``), asks
+the native launcher how much call-local scratch the call needs, takes it from the
+torch allocator (so a CUDA-graph pool owns it during capture and nothing is
+retained between calls, as the reference requires:
+src/nvidia/flash_attn/sm103/decode_runtime.py:829-847) and issues the custom op.
+The route and the split count are resolved inside the native launcher from
+graph-static sizes only.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import runtime
+
+
+def forward(*, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, max_seqlen_q, max_seqlen_k, page_table,
+            softmax_scale, causal, softcap, window_size_left, window_size_right, learnable_sink, out,
+            return_lse, q_descale, k_descale, v_descale, num_splits, route=runtime.ROUTE_AUTO):
+    if out is None:
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if return_lse else None
+    window_left = -1 if window_size_left is None else int(window_size_left)
+    window_right = -1 if window_size_right is None else int(window_size_right)
+    status = runtime.device_status(q.device)
+    args = (q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, page_table, q_descale, k_descale,
+            v_descale, learnable_sink, status, int(max_seqlen_q), int(max_seqlen_k), float(softmax_scale),
+            float(softcap), bool(causal), window_left, window_right, int(num_splits), int(route))
+    info = runtime.plan(runtime.build_params(*args))
+    workspace = None
+    if info.workspace_bytes:
+        workspace = torch.empty(info.workspace_bytes, dtype=torch.uint8, device=q.device)
+    runtime.fa_fwd(q, k, v, out, lse, workspace, *args[5:])
+    return out, lse

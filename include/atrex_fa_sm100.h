@@ -1,0 +1,163 @@
+/*
+ * C ABI of the sm_100a (B200) FlashAttention launcher behind
+ * atrex.flash_attn_varlen_func.
+ *
+ * This is the boundary a host-side binding links against.  It replaces, for the
+ * ("nvidia", "sm100") target, what the reference reaches through its private
+ * Python ABI `forward(**kwargs) -> (out, lse)` (python/atrex/api/flash_attn.py:395-421)
+ * and follows the shape of the reference's only native launcher,
+ *   int atrex_ppu_decode(void** pointers, int64_t* metadata, float scale, int splits, void* stream)
+ *   int atrex_ppu_decode_resources(int* out)
+ * (src/ppu/flash_attn/zwm890p/native_decode.cu:1032-1104, 1106-1120):
+ * raw device pointers, a plain metadata block, a CUDA stream, an int status.
+ *
+ * Rules every entry point keeps:
+ *   - plain C types only; no exceptions cross the boundary; 0 means success;
+ *   - nothing is allocated or freed and the device is never synchronised;
+ *   - all device work is enqueued on the caller's stream, so the call can be
+ *     captured into a CUDA graph (lengths, page tables and descales are read on
+ *     the device at every launch);
+ *   - arguments are range-checked before anything is launched
+ *     (native_decode.cu:1035-1043 does the same and returns InvalidValue).
+ */
+#ifndef ATREX_FA_SM100_H_
+#define ATREX_FA_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATREX_FA_SM100_ABI_VERSION 4
+
+#if defined(__GNUC__)
+#define ATREX_FA_API __attribute__((visibility("default")))
+#else
+#define ATREX_FA_API
+#endif
+
+enum atrex_fa_status {
+  ATREX_FA_OK = 0,
+  ATREX_FA_INVALID_VALUE = 1,      /* malformed call            -> ValueError          */
+  ATREX_FA_UNSUPPORTED = 2,        /* well formed, not served   -> NotImplementedError */
+  ATREX_FA_WORKSPACE_TOO_SMALL = 3,
+  ATREX_FA_CUDA_ERROR = 4,         /* a CUDA runtime/driver call failed -> RuntimeError */
+  ATREX_FA_WRONG_DEVICE = 5,       /* current device is not compute capability 10.0     */
+  ATREX_FA_ABI_MISMATCH = 6
+};
+
+enum atrex_fa_dtype { ATREX_FA_BF16 = 0, ATREX_FA_E4M3 = 1 };
+
+/* Kernel family.  AUTO lets the launcher choose from graph-static sizes only. */
+enum atrex_fa_route {
+  ATREX_FA_ROUTE_AUTO = 0,
+  ATREX_FA_ROUTE_MMA = 1,     /* split-KV mma.sync kernel (+ combine): short-Q decode, compatibility prefill */
+  ATREX_FA_ROUTE_UMMA = 2     /* warp-specialised TMA + tcgen05 prefill                                       */
+};
+
+/*
+ * One attention call.  Field meaning follows the keyword arguments of the
+ * reference's private ABI (python/atrex/api/flash_attn.py:396-420) and the
+ * fields of its native DecodeParams (native_decode.cu:28-74), widened to the
+ * whole contract.  Strides are in ELEMENTS of the tensor they describe.
+ * Unused pointers are NULL.
+ */
+typedef struct atrex_fa_sm100_params {
+  uint32_t struct_bytes;   /* sizeof(atrex_fa_sm100_params) as the caller sees it */
+  uint32_t abi_version;    /* ATREX_FA_SM100_ABI_VERSION                          */
+
+  const void* q;           /* [total_q, Hq, D]                                              */
+  const void* k;           /* paged [num_pages, page_size, Hkv, D] or packed [total_k,Hkv,D] */
+  const void* v;
+  void* out;               /* [total_q, Hq, D] BF16                                          */
+  float* lse;              /* [Hq, total_q] natural log, or NULL                             */
+  const int32_t* cu_seqlens_q;  /* [batch+1]                                                 */
+  const int32_t* cu_seqlens_k;  /* [batch+1] packed K/V only, else NULL                      */
+  const int32_t* seqused_k;     /* [batch] or NULL (packed K/V may give either)              */
+  const int32_t* block_table;   /* [batch, max_pages_per_seq] or NULL for packed K/V         */
+  const float* q_descale;       /* [batch, Hkv] FP8 only, or NULL                            */
+  const float* k_descale;
+  const float* v_descale;
+  const void* sink;             /* BF16 [Hq] sink logits (s_aux) or NULL                     */
+  int32_t* device_status;       /* optional: kernels store a nonzero code here if a bounded wait expires */
+  void* profile_event_begin;    /* optional cudaEvent_t pair recorded on the stream right before and right   */
+  void* profile_event_end;      /* after the dominant kernel of the call (not the plan or combine kernels)   */
+
+  int64_t q_row_stride, q_head_stride;
+  int64_t k_page_stride, k_row_stride, k_head_stride;   /* page stride ignored for packed K/V */
+  int64_t v_page_stride, v_row_stride, v_head_stride;
+  int64_t out_row_stride, out_head_stride;
+  int64_t block_table_row_stride;
+  int64_t q_descale_batch_stride, q_descale_head_stride;  /* may be 0 (broadcast views) */
+  int64_t k_descale_batch_stride, k_descale_head_stride;
+  int64_t v_descale_batch_stride, v_descale_head_stride;
+
+  int32_t batch;
+  int32_t total_q;
+  int32_t total_k;             /* rows of packed K/V; 0 when paged */
+  int32_t num_pages;           /* pool size when paged             */
+  int32_t page_size;           /* 0 = packed K/V                   */
+  int32_t max_pages_per_seq;   /* block_table width                */
+  int32_t max_seqlen_q;        /* upper bounds only: real lengths are read on the device */
+  int32_t max_seqlen_k;
+  int32_t num_q_heads, num_kv_heads, head_dim;
+  int32_t dtype;               /* enum atrex_fa_dtype of q/k/v     */
+  int32_t causal;
+  int32_t window_left, window_right;   /* -1 = unbounded                  */
+  int32_t return_lse;
+  int32_t num_splits;          /* 0 = launcher chooses, else 1..256 */
+  int32_t route;               /* enum atrex_fa_route               */
+  int32_t sm_count;            /* 0 = query the current device      */
+  float softmax_scale;
+  float softcap;               /* 0 = off                           */
+} atrex_fa_sm100_params;
+
+/* What the launcher will do for a call: filled by atrex_fa_sm100_plan. */
+typedef struct atrex_fa_sm100_plan_info {
+  int32_t route;            /* resolved enum atrex_fa_route                     */
+  int32_t num_splits;       /* resolved split count (>= 1)                      */
+  int32_t kernel_launches;  /* kernels one forward call enqueues                */
+  int32_t m_rows;           /* packed (query x group) rows per CTA tile         */
+  uint64_t workspace_bytes; /* scratch the caller must pass to forward (may be 0) */
+} atrex_fa_sm100_plan_info;
+
+/* ABI handshake: callers compare these with their own header. */
+ATREX_FA_API int atrex_fa_sm100_abi_version(void);
+ATREX_FA_API size_t atrex_fa_sm100_params_bytes(void);
+
+/* English text for a status code; never NULL. */
+ATREX_FA_API const char* atrex_fa_sm100_status_string(int status);
+
+/*
+ * Pure host query (counterpart of atrex_ppu_decode_resources,
+ * native_decode.cu:1106-1120): validates `p`, resolves route and split count
+ * from graph-static sizes (batch, heads, max_seqlen_*, SM count) and reports the
+ * scratch size.  Launches nothing.
+ */
+ATREX_FA_API int atrex_fa_sm100_plan(const atrex_fa_sm100_params* p, atrex_fa_sm100_plan_info* plan);
+
+/*
+ * Enqueue one attention call on `stream` (a cudaStream_t).  `workspace` is
+ * caller-owned device scratch of at least plan.workspace_bytes, 256-byte
+ * aligned; its contents on entry are irrelevant and may be NaN.  Replaces
+ * `forward(**kwargs)` of the reference's per-arch launch modules
+ * (src/nvidia/flash_attn/sm103/launch.py:282-311) and, in shape,
+ * atrex_ppu_decode (native_decode.cu:1032-1104).
+ */
+ATREX_FA_API int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint64_t workspace_bytes,
+                           void* stream);
+
+/*
+ * One-time per-device set-up (kernel attributes such as the dynamic shared
+ * memory limit).  forward() does it on first use; calling it explicitly keeps
+ * that work out of a latency-sensitive first call.  Counterpart of the
+ * reference's compile-before-capture rule (src/nvidia/flash_attn/sm103/launch.py:155-241).
+ */
+ATREX_FA_API int atrex_fa_sm100_prewarm(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATREX_FA_SM100_H_ */
