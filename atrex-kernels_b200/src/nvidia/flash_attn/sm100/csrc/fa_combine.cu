@@ -149,15 +149,15 @@ cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream
   const int64_t rows = (int64_t)p.total_q * p.num_q_heads;
   if (rows == 0) return cudaSuccess;
   const unsigned grid = (unsigned)((rows + kCombineWarps - 1) / kCombineWarps);
-  if (head_dim == 128) atrex_sm100_combine_kernel<128><<<grid, kCombineWarps * 32, 0, stream>>>(p);
-  else atrex_sm100_combine_kernel<256><<<grid, kCombineWarps * 32, 0, stream>>>(p);
-  return cudaGetLastError();
+  if (head_dim == 128)
+    return launch_kernel(atrex_sm100_combine_kernel<128>, dim3(grid), dim3(kCombineWarps * 32), 0, stream, p);
+  return launch_kernel(atrex_sm100_combine_kernel<256>, dim3(grid), dim3(kCombineWarps * 32), 0, stream, p);
 }
 
 cudaError_t plan_launch(const FwdParams& p, int m_rows, int32_t* order, int32_t* tile_prefix,
                         cudaStream_t stream) {
-  atrex_sm100_plan_kernel<<<1, kPlanThreads, 0, stream>>>(p, m_rows, order, tile_prefix);
-  return cudaGetLastError();
+  return launch_kernel(atrex_sm100_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, p, m_rows, order,
+                       tile_prefix);
 }
 
 }  // namespace atrex_sm100

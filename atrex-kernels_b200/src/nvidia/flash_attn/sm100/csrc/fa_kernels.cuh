@@ -5,8 +5,23 @@
 
 namespace atrex_sm100 {
 
+// Launch through cudaLaunchKernelEx and report ITS status: the kernel<<<>>> +
+// cudaGetLastError idiom would also pick up an unrelated stale error left in the
+// calling thread by other code.
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
+
 // ---- fa_mma.cu: split-KV mma.sync kernel ----
 int mma_rows_for(int packed_rows);            // 16, 32 or 64 rows per CTA
+int mma_tile_n(int head_dim);                 // KV tokens per pipeline stage
 cudaError_t mma_prepare();                    // per-device kernel attributes
 cudaError_t mma_launch(const FwdParams& p, int head_dim, int m_rows, cudaStream_t stream);
 

@@ -25,10 +25,14 @@ namespace atrex_sm100 {
 
 namespace {
 
-constexpr int kTileN = 64;  // KV tokens per pipeline stage
-
-template <int D, int WM, int WT, int STAGES>
+// A consumer waits on a stage's "full" barrier by phase parity, which is only
+// sound while it is at most one phase behind that barrier.  Every warp group
+// therefore owns fixed stages (STAGES % WT == 0) and sees each of their phases
+// in order.
+template <int D, int WM, int WT, int STAGES, int TN>
 struct MmaCfg {
+  static_assert(STAGES % WT == 0, "each stage must have one fixed consumer group");
+  static constexpr int kTileN = TN;                  // KV tokens per pipeline stage
   static constexpr int kM = 16 * WM;                 // packed rows per CTA
   static constexpr int kComputeWarps = WM * WT;
   static constexpr int kThreads = (kComputeWarps + 1) * 32;
@@ -40,18 +44,23 @@ struct MmaCfg {
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static_assert(kRedBytes <= kRingBytes, "merge buffer aliases the ring");
   static constexpr int kSmemBytes = kRingBytes + kQBytes + 2 * STAGES * 8 + 16;
+  // CTAs per SM the shared memory allows (228 KB per SM, 1 KB reserved per CTA), at most 3
+  static constexpr int kBySmem = (228 * 1024) / (kSmemBytes + 1024);
+  static constexpr int kByRegs = D == 256 ? (kThreads <= 96 ? 2 : 1) : (kThreads <= 96 ? 3 : 2);
+  static constexpr int kMinBlocks = kBySmem < 1 ? 1 : (kBySmem < kByRegs ? kBySmem : kByRegs);
 };
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <int D, int WM, int WT, int STAGES>
-__global__ void __launch_bounds__((WM * WT + 1) * 32, (D == 128 && STAGES <= 3) ? 2 : 1)
+template <int D, int WM, int WT, int STAGES, int TN>
+__global__ void __launch_bounds__((WM * WT + 1) * 32, MmaCfg<D, WM, WT, STAGES, TN>::kMinBlocks)
 atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
-  using Cfg = MmaCfg<D, WM, WT, STAGES>;
+  using Cfg = MmaCfg<D, WM, WT, STAGES, TN>;
   constexpr int M = Cfg::kM;
   constexpr int KB = Cfg::kKBlocks;
+  constexpr int kTileN = TN;
 
   // No static shared memory is declared, so the dynamic window starts at the
   // CTA's shared base; the swizzled tiles need 1024-byte alignment (checked below).
@@ -185,6 +194,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
         }
       }
     }
+    __syncwarp();
   } else {
     // ===================== compute warps =====================
     // Q tile -> shared memory (swizzled like K so ldmatrix is conflict free).
@@ -266,9 +276,9 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
       }
 
       // ---- S = Q K^T ----
-      float s[8][4];
+      float s[TN / 8][4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int j = 0; j < TN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb) {
 #pragma unroll
@@ -277,7 +287,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
           ldmatrix_x4(a[0], a[1], a[2], a[3],
                       q_addr + kb * (M * 128) + swz128(q_lane_row, ks * 2 + q_lane_chunk));
 #pragma unroll
-          for (int jp = 0; jp < 4; ++jp) {
+          for (int jp = 0; jp < TN / 16; ++jp) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4(b0, b1, b2, b3,
                         k_addr + kb * (kTileN * 128) + swz128(jp * 16 + k_lane_row, ks * 2 + k_lane_chunk));
@@ -290,7 +300,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
       // ---- scale, softcap, mask ----
       const bool need_mask = tok0 < full_lo || tok0 + kTileN > full_hi;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < TN / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float x = s[j][e];
@@ -310,7 +320,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
       for (int h = 0; h < 2; ++h) {
         float mx = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * h], s[j][2 * h + 1]));
+        for (int j = 0; j < TN / 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * h], s[j][2 * h + 1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m_run[h], mx);
@@ -319,7 +329,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
         m_run[h] = m_new;
         float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < TN / 8; ++j) {
           s[j][2 * h] = fast_exp2(s[j][2 * h] - m_use);
           s[j][2 * h + 1] = fast_exp2(s[j][2 * h + 1] - m_use);
           sum += s[j][2 * h] + s[j][2 * h + 1];
@@ -336,7 +346,7 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
 
       // ---- O += P V ----
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
+      for (int kk = 0; kk < TN / 16; ++kk) {
         uint32_t a[4];
         a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
         a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -441,19 +451,18 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
   }
 }
 
-template <int D, int WM, int WT, int STAGES>
+template <int D, int WM, int WT, int STAGES, int TN>
 cudaError_t launch_one(const FwdParams& p, cudaStream_t stream) {
-  using Cfg = MmaCfg<D, WM, WT, STAGES>;
-  auto kernel = atrex_sm100_fwd_mma_kernel<D, WM, WT, STAGES>;
+  using Cfg = MmaCfg<D, WM, WT, STAGES, TN>;
+  auto kernel = atrex_sm100_fwd_mma_kernel<D, WM, WT, STAGES, TN>;
   dim3 grid((unsigned)p.num_row_tiles * p.num_kv_heads, (unsigned)p.num_splits, 1);
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  return launch_kernel(kernel, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p);
 }
 
-template <int D, int WM, int WT, int STAGES>
+template <int D, int WM, int WT, int STAGES, int TN>
 cudaError_t prepare_one() {
-  using Cfg = MmaCfg<D, WM, WT, STAGES>;
-  return cudaFuncSetAttribute(atrex_sm100_fwd_mma_kernel<D, WM, WT, STAGES>,
+  using Cfg = MmaCfg<D, WM, WT, STAGES, TN>;
+  return cudaFuncSetAttribute(atrex_sm100_fwd_mma_kernel<D, WM, WT, STAGES, TN>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
 }
 
@@ -461,26 +470,32 @@ cudaError_t prepare_one() {
 
 int mma_rows_for(int packed_rows) { return packed_rows <= 16 ? 16 : (packed_rows <= 32 ? 32 : 64); }
 
+// KV tokens per stage: a stage is 32 KB (K + V) for both head dimensions.
+int mma_tile_n(int head_dim) { return head_dim == 128 ? 64 : 32; }
+
+#define ATREX_MMA_VARIANTS(X)  \
+  X(128, 1, 2, 2, 64)          \
+  X(128, 2, 2, 2, 64)          \
+  X(128, 4, 1, 3, 64)          \
+  X(256, 1, 2, 2, 32)          \
+  X(256, 2, 2, 4, 32)          \
+  X(256, 4, 1, 3, 32)
+
 cudaError_t mma_prepare() {
   cudaError_t e;
-  if ((e = prepare_one<128, 1, 4, 3>()) != cudaSuccess) return e;
-  if ((e = prepare_one<128, 2, 2, 3>()) != cudaSuccess) return e;
-  if ((e = prepare_one<128, 4, 1, 3>()) != cudaSuccess) return e;
-  if ((e = prepare_one<256, 1, 4, 3>()) != cudaSuccess) return e;
-  if ((e = prepare_one<256, 2, 2, 3>()) != cudaSuccess) return e;
-  if ((e = prepare_one<256, 4, 1, 3>()) != cudaSuccess) return e;
+#define X(D, WM, WT, ST, TN) \
+  if ((e = prepare_one<D, WM, WT, ST, TN>()) != cudaSuccess) return e;
+  ATREX_MMA_VARIANTS(X)
+#undef X
   return cudaSuccess;
 }
 
 cudaError_t mma_launch(const FwdParams& p, int head_dim, int m_rows, cudaStream_t stream) {
-  if (head_dim == 128) {
-    if (m_rows == 16) return launch_one<128, 1, 4, 3>(p, stream);
-    if (m_rows == 32) return launch_one<128, 2, 2, 3>(p, stream);
-    return launch_one<128, 4, 1, 3>(p, stream);
-  }
-  if (m_rows == 16) return launch_one<256, 1, 4, 3>(p, stream);
-  if (m_rows == 32) return launch_one<256, 2, 2, 3>(p, stream);
-  return launch_one<256, 4, 1, 3>(p, stream);
+#define X(D, WM, WT, ST, TN) \
+  if (head_dim == D && m_rows == 16 * WM) return launch_one<D, WM, WT, ST, TN>(p, stream);
+  ATREX_MMA_VARIANTS(X)
+#undef X
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace atrex_sm100

@@ -6,6 +6,7 @@
 // encoding, workspace carving and the launches.  Nothing here allocates,
 // synchronises or reads device memory.
 #include <atomic>
+#include <cstdio>
 #include <cstring>
 
 #include "atrex_fa_sm100.h"
@@ -14,9 +15,18 @@
 namespace atrex_sm100 {
 namespace {
 
+thread_local char g_last_error[256] = "";
+
+int fail(int status, const char* what, cudaError_t cuda = cudaSuccess) {
+  if (cuda != cudaSuccess)
+    std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(cuda));
+  else
+    std::snprintf(g_last_error, sizeof(g_last_error), "%s", what);
+  return status;
+}
+
 constexpr int kMaxDevices = 64;
 constexpr int kMaxSplits = 256;
-constexpr int kTileN = 64;
 
 struct DeviceInfo {
   std::atomic<int> state{0};  // 0 unknown, 1 usable, -1 wrong architecture
@@ -45,8 +55,9 @@ EncodeTiledFn encode_fn() {
 
 int current_device(DeviceInfo** info) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
-  if (dev < 0 || dev >= kMaxDevices) return ATREX_FA_UNSUPPORTED;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail(ATREX_FA_UNSUPPORTED, "device ordinal out of range");
   DeviceInfo& d = g_devices[dev];
   int st = d.state.load(std::memory_order_acquire);
   if (st == 0) {
@@ -54,18 +65,19 @@ int current_device(DeviceInfo** info) {
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      return ATREX_FA_CUDA_ERROR;
+      return fail(ATREX_FA_CUDA_ERROR, "cudaDeviceGetAttribute failed");
     d.sm_count = sms;
     st = (major == 10 && minor == 0) ? 1 : -1;
     d.state.store(st, std::memory_order_release);
   }
   *info = &d;
-  return st == 1 ? ATREX_FA_OK : ATREX_FA_WRONG_DEVICE;
+  return st == 1 ? ATREX_FA_OK : fail(ATREX_FA_WRONG_DEVICE, "current device is not compute capability 10.0");
 }
 
 int prepare_device(DeviceInfo& d) {
   if (d.prepared.load(std::memory_order_acquire)) return ATREX_FA_OK;
-  if (mma_prepare() != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+  const cudaError_t e = mma_prepare();
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (mma kernels)", e);
   d.prepared.store(1, std::memory_order_release);
   return ATREX_FA_OK;
 }
@@ -125,6 +137,7 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   if (tiles_bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
   r->num_row_tiles = (int)tiles_bound;
 
+  const int kTileN = mma_tile_n(p->head_dim);
   // keys one row tile can see, at the upper bound (a two-sided window limits it)
   int64_t span = p->max_seqlen_k;
   if (p->window_left >= 0 && (p->causal || p->window_right >= 0)) {
@@ -138,9 +151,9 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
     splits = p->num_splits;
   } else {
     const int64_t items = (int64_t)r->num_row_tiles * p->num_kv_heads;
-    const int64_t slots = (int64_t)sm_count * (p->head_dim == 128 ? 2 : 1);
+    const int64_t slots = (int64_t)sm_count * (p->head_dim == 128 ? (r->m_rows == 16 ? 3 : 2) : 1);
     const int64_t want = items > 0 ? (slots * 8 + items - 1) / items : 1;  // about eight waves of CTAs
-    const int64_t cap = kv_tiles / 8;                                      // >= 512 keys per split
+    const int64_t cap = (int64_t)kv_tiles * kTileN / 512;                  // >= 512 keys per split
     splits = (int)(want < cap ? want : cap);
   }
   if (splits > kv_tiles) splits = kv_tiles;
@@ -169,7 +182,7 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
                   int64_t page_stride, int heads, int64_t rows, int64_t pages, int head_dim, int box_rows,
                   int8_t perm[3]) {
   EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return ATREX_FA_CUDA_ERROR;
+  if (fn == nullptr) return fail(ATREX_FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
   struct Dim { uint64_t extent, stride; uint32_t box; int which; };
   Dim dims[3] = {{(uint64_t)heads, (uint64_t)head_stride * 2, 1u, 0},
                  {(uint64_t)rows, (uint64_t)row_stride * 2, (uint32_t)box_rows, 1},
@@ -185,13 +198,14 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
   cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
   for (int i = 0; i < 3; ++i) {
     if (stride[i] == 0) stride[i] = 16;  // extent-1 dimension with a zero stride
-    if (stride[i] % 16 != 0 || stride[i] >= (1ull << 40)) return ATREX_FA_UNSUPPORTED;
+    if (stride[i] % 16 != 0 || stride[i] >= (1ull << 40))
+      return fail(ATREX_FA_UNSUPPORTED, "K/V stride is not a multiple of 16 bytes below 2^40");
     perm[dims[i].which] = (int8_t)i;
   }
   const CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), extent, stride, box,
                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return res == CUDA_SUCCESS ? ATREX_FA_OK : ATREX_FA_UNSUPPORTED;
+  return res == CUDA_SUCCESS ? ATREX_FA_OK : fail(ATREX_FA_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the K/V layout");
 }
 
 }  // namespace
@@ -200,6 +214,8 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
 using namespace atrex_sm100;
 
 extern "C" {
+
+const char* atrex_fa_sm100_last_error(void) { return g_last_error; }
 
 int atrex_fa_sm100_abi_version(void) { return ATREX_FA_SM100_ABI_VERSION; }
 
@@ -219,9 +235,9 @@ const char* atrex_fa_sm100_status_string(int status) {
 }
 
 int atrex_fa_sm100_plan(const atrex_fa_sm100_params* p, atrex_fa_sm100_plan_info* plan) {
-  if (plan == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (plan == nullptr) return fail(ATREX_FA_INVALID_VALUE, "plan is NULL");
   int st = check_params(p);
-  if (st != ATREX_FA_OK) return st;
+  if (st != ATREX_FA_OK) return fail(st, "parameter check failed");
   int sm_count = p->sm_count;
   if (sm_count <= 0) {
     DeviceInfo* info = nullptr;
@@ -250,7 +266,7 @@ int atrex_fa_sm100_prewarm(void) {
 int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint64_t workspace_bytes,
                            void* stream_ptr) {
   int st = check_params(p);
-  if (st != ATREX_FA_OK) return st;
+  if (st != ATREX_FA_OK) return fail(st, "parameter check failed");
   DeviceInfo* info = nullptr;
   st = current_device(&info);
   if (st != ATREX_FA_OK) return st;
@@ -259,7 +275,7 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   if (st != ATREX_FA_OK) return st;
   if (r.bytes > 0 && (workspace == nullptr || workspace_bytes < r.bytes ||
                       (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0))
-    return ATREX_FA_WORKSPACE_TOO_SMALL;
+    return fail(ATREX_FA_WORKSPACE_TOO_SMALL, "workspace missing, misaligned or too small");
   if (p->batch == 0 || p->total_q == 0) return ATREX_FA_OK;
   st = prepare_device(*info);
   if (st != ATREX_FA_OK) return st;
@@ -270,6 +286,7 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   const bool paged = p->page_size > 0;
   const int64_t rows = paged ? p->page_size : p->total_k;
   const int64_t pages = paged ? p->num_pages : 1;
+  const int kTileN = mma_tile_n(p->head_dim);
   const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
   const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
   int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
@@ -326,18 +343,20 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   f.softmax_scale = p->softmax_scale;
   f.softcap = p->softcap;
 
-  if (r.tiled &&
-      plan_launch(f, r.m_rows, const_cast<int32_t*>(f.order), const_cast<int32_t*>(f.tile_prefix), stream) !=
-          cudaSuccess)
-    return ATREX_FA_CUDA_ERROR;
+  cudaError_t e;
+  if (r.tiled && (e = plan_launch(f, r.m_rows, const_cast<int32_t*>(f.order), const_cast<int32_t*>(f.tile_prefix),
+                                  stream)) != cudaSuccess)
+    return fail(ATREX_FA_CUDA_ERROR, "launch of the plan kernel", e);
   if (p->profile_event_begin != nullptr &&
-      cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream) != cudaSuccess)
-    return ATREX_FA_CUDA_ERROR;
-  if (mma_launch(f, p->head_dim, r.m_rows, stream) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+      (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream)) != cudaSuccess)
+    return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_begin)", e);
+  if ((e = mma_launch(f, p->head_dim, r.m_rows, stream)) != cudaSuccess)
+    return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
   if (p->profile_event_end != nullptr &&
-      cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream) != cudaSuccess)
-    return ATREX_FA_CUDA_ERROR;
-  if (r.splits > 1 && combine_launch(f, p->head_dim, stream) != cudaSuccess) return ATREX_FA_CUDA_ERROR;
+      (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream)) != cudaSuccess)
+    return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_end)", e);
+  if (r.splits > 1 && (e = combine_launch(f, p->head_dim, stream)) != cudaSuccess)
+    return fail(ATREX_FA_CUDA_ERROR, "launch of the combine kernel", e);
   return ATREX_FA_OK;
 }
 

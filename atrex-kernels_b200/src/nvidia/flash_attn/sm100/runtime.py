@@ -81,6 +81,7 @@ def load_library():
         lib.atrex_fa_sm100_params_bytes.restype = ctypes.c_size_t
         lib.atrex_fa_sm100_status_string.restype = ctypes.c_char_p
         lib.atrex_fa_sm100_status_string.argtypes = [ctypes.c_int]
+        lib.atrex_fa_sm100_last_error.restype = ctypes.c_char_p
         lib.atrex_fa_sm100_plan.restype = ctypes.c_int
         lib.atrex_fa_sm100_plan.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(PlanInfo)]
         lib.atrex_fa_sm100_forward.restype = ctypes.c_int
@@ -95,8 +96,10 @@ def load_library():
 def raise_for_status(status: int) -> None:
     if status == 0:
         return
-    text = load_library().atrex_fa_sm100_status_string(status).decode()
-    raise _STATUS_EXCEPTIONS.get(status, RuntimeError)(f"atrex sm100 attention: {text} (status {status})")
+    lib = load_library()
+    text = lib.atrex_fa_sm100_status_string(status).decode()
+    detail = lib.atrex_fa_sm100_last_error().decode()
+    raise _STATUS_EXCEPTIONS.get(status, RuntimeError)(f"atrex sm100 attention: {text} (status {status}; {detail})")
 
 
 def _ptr_of(t):

@@ -131,6 +131,14 @@ ATREX_FA_API size_t atrex_fa_sm100_params_bytes(void);
 ATREX_FA_API const char* atrex_fa_sm100_status_string(int status);
 
 /*
+ * Detail of the last non-zero status returned on the calling thread (which check
+ * failed, or which CUDA call with its error string); empty if there was none.
+ * The reference reports launcher failures the same way, as text in the raised
+ * RuntimeError (src/ppu/flash_attn/zwm890p/decode_runtime.py:108-113).
+ */
+ATREX_FA_API const char* atrex_fa_sm100_last_error(void);
+
+/*
  * Pure host query (counterpart of atrex_ppu_decode_resources,
  * native_decode.cu:1106-1120): validates `p`, resolves route and split count
  * from graph-static sizes (batch, heads, max_seqlen_*, SM count) and reports the

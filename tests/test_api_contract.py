@@ -1,0 +1,347 @@
+"""CPU-only tests of the public boundary: lazy import, device classification, fail-fast validation,
+and the C-ABI library's exports and host-side planning.
+
+The validation is exercised on CPU tensors by making ``detect_device_target`` report a B200, the way the
+reference's own infrastructure tests swap in fakes (op_test/test_lazy_import.py, op_test/test_device_target.py).
+Cases follow the reference's eligibility tests (op_test/nvidia/flash_attn/test_flash_attn_sm103.py:837-880,
+op_test/nvidia/flash_attn/test_flash_attn_sm120.py:36-68).
+"""
+
+import ctypes
+import re
+import subprocess
+import sys
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import atrex
+from atrex.utils.device_target import DeviceTarget, detect_device_target
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ---------------------------------------------------------------- lazy public API
+def test_import_is_lazy():
+    code = ("import sys; sys.path.insert(0, %r); import atrex; "
+            "assert 'torch' not in sys.modules and 'atrex.api.flash_attn' not in sys.modules; "
+            "assert callable(atrex.flash_attn_varlen_func) and callable(atrex.can_use_flash_attn_varlen_func)"
+            % os.path.join(ROOT, "atrex-kernels_b200", "python"))
+    subprocess.check_call([sys.executable, "-c", code])
+
+
+def test_lazy_proxy_rebinds_after_first_call(monkeypatch):
+    imports = []
+
+    def implementation(value, *, increment=1):
+        return value + increment
+
+    def fake_import(name):
+        imports.append(name)
+        return SimpleNamespace(implementation=implementation)
+
+    monkeypatch.setattr(atrex, "_import_module", fake_import)
+    proxy = atrex._lazy_import_and_call("implementation", "atrex.api.example", public_name="example")
+    monkeypatch.setattr(atrex, "example", proxy, raising=False)
+    assert imports == [] and proxy.__name__ == "example"
+    assert atrex.example(3, increment=2) == 5
+    assert atrex.example is implementation
+    assert atrex.example(4) == 5 and imports == ["atrex.api.example"]
+
+
+def test_lazy_proxy_keeps_proxy_when_import_fails(monkeypatch):
+    proxy = atrex._lazy_import_and_call("missing", "atrex.api.missing")
+    monkeypatch.setattr(atrex, "missing", proxy, raising=False)
+
+    def fail_import(name):
+        raise ModuleNotFoundError(name)
+
+    monkeypatch.setattr(atrex, "_import_module", fail_import)
+    with pytest.raises(ModuleNotFoundError):
+        atrex.missing()
+    assert atrex.missing is proxy
+
+
+# ---------------------------------------------------------------- device classification
+class _FakeCuda:
+    def __init__(self, name, capability, gfx=""):
+        self._props = SimpleNamespace(name=name, gcnArchName=gfx)
+        self._cap = capability
+
+    def get_device_properties(self, index):
+        return self._props
+
+    def get_device_capability(self, index):
+        return self._cap
+
+    def is_available(self):
+        return True
+
+    def current_device(self):
+        return 0
+
+
+def _fake_torch(monkeypatch, name, capability=(10, 0), cuda="12.9", hip=None, gfx=""):
+    fake = SimpleNamespace(cuda=_FakeCuda(name, capability, gfx), version=SimpleNamespace(cuda=cuda, hip=hip))
+    monkeypatch.setitem(sys.modules, "torch", fake)
+
+
+@pytest.mark.parametrize("name,cap,kwargs,expect", [
+    ("NVIDIA B200", (10, 0), {}, ("nvidia", "sm100")),
+    ("NVIDIA B300 SXM6", (10, 3), {}, ("nvidia", "sm103")),
+    ("NVIDIA L40S", (8, 9), {}, ("nvidia", "sm89")),
+    ("ZW-M890P", (8, 9), {"cuda": "13.0"}, ("alibaba_ppu", "zwm890p")),
+    ("AMD Instinct MI308X", (9, 4), {"hip": "7.2", "gfx": "gfx942:sramecc+:xnack-"}, ("amd", "gfx942")),
+    ("Mystery Accelerator", (9, 0), {}, ("unknown", "unknown")),
+])
+def test_device_classification(monkeypatch, name, cap, kwargs, expect):
+    _fake_torch(monkeypatch, name, cap, **kwargs)
+    target = detect_device_target(0)
+    assert (target.family, target.arch) == expect
+
+
+def test_cpu_device_is_not_a_target():
+    target = detect_device_target(torch.device("cpu"))
+    assert (target.family, target.arch) == ("cpu", "cpu")
+
+
+# ---------------------------------------------------------------- validation on CPU tensors
+@pytest.fixture
+def as_b200(monkeypatch):
+    from atrex.api import flash_attn
+
+    monkeypatch.setattr(flash_attn, "detect_device_target",
+                        lambda device: DeviceTarget("nvidia", "sm100", "12.9", 0))
+    return flash_attn
+
+
+def _call(fp8=False, paged=True, hq=8, hkv=2, d=128, page=64):
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    q = torch.zeros(6, hq, d).to(dt)
+    if paged:
+        k = torch.zeros(10, page, hkv, d).to(dt)
+        v = torch.zeros(10, page, hkv, d).to(dt)
+        extra = dict(seqused_k=torch.tensor([100, 200], dtype=torch.int32),
+                     block_table=torch.zeros(2, 4, dtype=torch.int32))
+    else:
+        k = torch.zeros(300, hkv, d).to(dt)
+        v = torch.zeros(300, hkv, d).to(dt)
+        extra = dict(cu_seqlens_k=torch.tensor([0, 100, 300], dtype=torch.int32))
+    call = dict(q=q, k=k, v=v, max_seqlen_q=4, cu_seqlens_q=torch.tensor([0, 2, 6], dtype=torch.int32),
+                max_seqlen_k=256, causal=True, **extra)
+    if fp8:
+        for name in ("q_descale", "k_descale", "v_descale"):
+            call[name] = torch.ones(2, hkv)
+    return call
+
+
+def test_good_calls_are_eligible(as_b200):
+    for kwargs in (dict(), dict(fp8=True), dict(paged=False), dict(d=256), dict(page=16), dict(page=4224),
+                   dict(hq=64, hkv=4)):
+        assert atrex.can_use_flash_attn_varlen_func(**_call(**kwargs)), kwargs
+    good = _call()
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, fa_version=4))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, window_size=(4095, 0)))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, s_aux=torch.zeros(8, dtype=torch.bfloat16)))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, softcap=30.0, num_splits=256, causal=False))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, logits_soft_cap=30.0))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(_call(fp8=True), k_descale=torch.ones(1, 1).expand(2, 2)))
+
+
+BAD = [
+    (dict(fa_version=3), NotImplementedError, "fa_version"),
+    (dict(fa_version=2), NotImplementedError, "fa_version"),
+    (dict(deterministic=True), NotImplementedError, "deterministic"),
+    (dict(scheduler_metadata=torch.zeros(1)), NotImplementedError, "scheduler_metadata"),
+    (dict(num_prefill=3), NotImplementedError, "num_prefill"),
+    (dict(max_seqlen_k_decode=1), NotImplementedError, "max_seqlen_k_decode"),
+    (dict(dropout_p=0.1), NotImplementedError, "dropout"),
+    (dict(return_attn_probs=True), NotImplementedError, "return_attn_probs"),
+    (dict(cp_world_size=2), NotImplementedError, "context parallelism"),
+    (dict(cp_tot_seqused_k=torch.zeros(1)), NotImplementedError, "context parallelism"),
+    (dict(alibi_slopes=torch.zeros(8)), NotImplementedError, "ALiBi"),
+    (dict(q_v=torch.zeros(1)), NotImplementedError, "q_v"),
+    (dict(qv=torch.zeros(1)), NotImplementedError, "qv"),
+    (dict(output_scale=torch.zeros(1)), NotImplementedError, "output_scale"),
+    (dict(mask_mod=lambda *a: True), NotImplementedError, "mask_mod"),
+    (dict(dynamic_causal=torch.zeros(1)), NotImplementedError, "dynamic_causal"),
+    (dict(cu_seqlens_k=torch.tensor([0, 1, 2], dtype=torch.int32)), ValueError, "exactly one"),
+    (dict(seqused_k=None), ValueError, "exactly one"),
+    (dict(num_splits=-1), ValueError, "num_splits"),
+    (dict(num_splits=257), NotImplementedError, "num_splits"),
+    (dict(window_size=(1, 2, 3)), ValueError, "window_size"),
+    (dict(softcap=1.0, logits_soft_cap=2.0), ValueError, "softcap"),
+    (dict(cu_seqlens_q=None), ValueError, "cu_seqlens_q"),
+    (dict(cu_seqlens_q=torch.tensor([0, 2, 6], dtype=torch.int64)), ValueError, "cu_seqlens_q"),
+    (dict(block_table=torch.zeros(3, 4, dtype=torch.int32)), ValueError, "block_table"),
+    (dict(seqused_k=torch.zeros(3, dtype=torch.int32)), ValueError, "seqused_k"),
+    (dict(max_seqlen_k=-1), ValueError, "maximum sequence lengths"),
+    (dict(s_aux=torch.zeros(8)), ValueError, "s_aux"),
+    (dict(s_aux=torch.zeros(4, dtype=torch.bfloat16)), ValueError, "s_aux"),
+    (dict(q_descale=torch.ones(2, 2)), NotImplementedError, "descales"),
+    (dict(out=torch.zeros(6, 8, 128)), ValueError, "out"),
+    (dict(out=torch.zeros(7, 8, 128, dtype=torch.bfloat16)), ValueError, "out"),
+    (dict(out=torch.zeros(6, 8, 256, dtype=torch.bfloat16)[..., ::2]), ValueError, "out"),
+]
+
+
+@pytest.mark.parametrize("update,exc,match", BAD, ids=[f"{i}-{m}" for i, (_, _, m) in enumerate(BAD)])
+def test_ineligible_calls_fail_fast(as_b200, update, exc, match):
+    kwargs = dict(_call(), **update)
+    assert not atrex.can_use_flash_attn_varlen_func(**kwargs)
+    with pytest.raises(exc, match=re.escape(match)):
+        atrex.flash_attn_varlen_func(**kwargs)
+
+
+def test_shape_and_dtype_rejections(as_b200):
+    base = _call()
+    cases = [
+        (dict(q=base["q"].float(), k=base["k"].float(), v=base["v"].float()), NotImplementedError, "dtype"),
+        (dict(k=base["k"].to(torch.float8_e4m3fn)), NotImplementedError, "matching Q/K/V dtypes"),
+        (dict(q=torch.zeros(6, 8, 64, dtype=torch.bfloat16)), NotImplementedError, "head dimensions"),
+        (dict(q=torch.zeros(6, 7, 128, dtype=torch.bfloat16)), ValueError, "divisible"),
+        (dict(v=torch.zeros(10, 64, 1, 128, dtype=torch.bfloat16)), ValueError, "K/V"),
+        (dict(k=torch.zeros(10, 64, 2, 256, dtype=torch.bfloat16)[..., ::2]), ValueError, "contiguous"),
+        (dict(k=torch.zeros(10, 48, 2, 128, dtype=torch.bfloat16),
+              v=torch.zeros(10, 48, 2, 128, dtype=torch.bfloat16)), NotImplementedError, "page_size"),
+        (dict(q=torch.zeros(6, 8, 128, dtype=torch.float8_e5m2), k=base["k"].to(torch.float8_e5m2),
+              v=base["v"].to(torch.float8_e5m2)), NotImplementedError, "float8_e5m2"),
+    ]
+    for update, exc, match in cases:
+        kwargs = dict(base, **update)
+        assert not atrex.can_use_flash_attn_varlen_func(**kwargs), match
+        with pytest.raises(exc, match=re.escape(match)):
+            atrex.flash_attn_varlen_func(**kwargs)
+    fp8 = _call(fp8=True)
+    for bad in (torch.ones(2, 3), torch.ones(2, 2, dtype=torch.float64)):
+        with pytest.raises(ValueError, match="descales"):
+            atrex.flash_attn_varlen_func(**dict(fp8, v_descale=bad))
+
+
+def test_other_devices_are_rejected():
+    """Without the B200 stand-in a CPU call names the detected target, as the reference does for unknown targets
+    (python/atrex/api/flash_attn.py:239-244)."""
+    with pytest.raises(NotImplementedError, match="nvidia/sm100"):
+        atrex.flash_attn_varlen_func(**_call())
+    assert not atrex.can_use_flash_attn_varlen_func(**_call())
+
+
+def test_can_use_never_reaches_the_launcher(as_b200, monkeypatch):
+    """Eligibility must not load, build or launch anything (reference: op_test/ppu/flash_attn/test_flash_attn_zwm890p.py:686-708)."""
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime
+
+    def boom(*a, **k):
+        raise AssertionError("eligibility check reached the native path")
+
+    monkeypatch.setattr(runtime, "load_library", boom)
+    monkeypatch.setattr(launch, "forward", boom)
+    assert atrex.can_use_flash_attn_varlen_func(**_call())
+    assert not atrex.can_use_flash_attn_varlen_func(**dict(_call(), fa_version=3))
+
+
+def test_runtime_errors_propagate_without_fallback(as_b200, monkeypatch):
+    """An exception from the selected runtime is the caller's answer; nothing else is tried
+    (reference: op_test/ppu/flash_attn/test_flash_attn_zwm890p.py:375-395)."""
+    from atrex.src.nvidia.flash_attn.sm100 import launch
+
+    for exc in (ValueError, RuntimeError, NotImplementedError):
+        def raiser(**kwargs):
+            raise exc("from the runtime")
+
+        monkeypatch.setattr(launch, "forward", raiser)
+        monkeypatch.setattr(torch.cuda, "device", lambda d: __import__("contextlib").nullcontext())
+        with pytest.raises(exc, match="from the runtime"):
+            atrex.flash_attn_varlen_func(**_call())
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    monkeypatch.setattr(runtime, "_lib", None)
+    monkeypatch.setattr(runtime, "LIBRARY_PATH", tmp_path / "libatrex_fa_sm100.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        runtime.load_library()
+
+
+# ---------------------------------------------------------------- C ABI: exports and host-side planning
+HEADER = os.path.join(ROOT, "include", "atrex_fa_sm100.h")
+
+
+def test_library_exports_every_declared_symbol():
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    lib = runtime.load_library()
+    declared = re.findall(r"ATREX_FA_API\s+[\w\s\*]+?\b(atrex_fa_sm100_\w+)\s*\(", open(HEADER).read())
+    assert len(declared) >= 7
+    for name in declared:
+        assert hasattr(lib, name), name
+    version = int(re.search(r"#define ATREX_FA_SM100_ABI_VERSION (\d+)", open(HEADER).read()).group(1))
+    assert lib.atrex_fa_sm100_abi_version() == version == runtime.ABI_VERSION
+    assert lib.atrex_fa_sm100_params_bytes() == ctypes.sizeof(runtime.Params)
+    assert lib.atrex_fa_sm100_status_string(2).decode().startswith("well-formed")
+
+
+def _plan(call, **over):
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    out = torch.empty(call["q"].shape, dtype=torch.bfloat16)
+    p = runtime.build_params(call["q"], call["k"], call["v"], out, None, call["cu_seqlens_q"],
+                             call.get("cu_seqlens_k"), call.get("seqused_k"), call.get("block_table"),
+                             None, None, None, None, None, over.pop("max_seqlen_q", call["max_seqlen_q"]),
+                             over.pop("max_seqlen_k", call["max_seqlen_k"]), 0.1, 0.0, True,
+                             over.pop("window_left", -1), -1, over.pop("num_splits", 0), 0)
+    p.sm_count = 148
+    for key, val in over.items():
+        setattr(p, key, val)
+    return runtime, p
+
+
+def test_plan_is_a_pure_function_of_static_sizes():
+    """Split counts come from batch, heads, upper bounds and the SM count, never from device data
+    (reference policy tests: op_test/nvidia/flash_attn/test_flash_attn_sm120.py:116-163)."""
+    call = _call(hq=32, hkv=8)
+    runtime, p = _plan(call, max_seqlen_q=1, max_seqlen_k=16384)
+    info = runtime.plan(p)
+    assert info.route == runtime.ROUTE_MMA and info.m_rows == 16 and info.num_splits > 1
+    assert info.kernel_launches == 2
+    assert info.workspace_bytes >= info.num_splits * 6 * 32 * (128 + 1) * 4
+    again = runtime.plan(p)
+    assert (again.num_splits, again.workspace_bytes) == (info.num_splits, info.workspace_bytes)
+    # an explicit request is honoured, clamped to the number of KV tiles
+    assert runtime.plan(_plan(call, max_seqlen_q=1, max_seqlen_k=16384, num_splits=7)[1]).num_splits == 7
+    assert runtime.plan(_plan(call, max_seqlen_q=1, max_seqlen_k=64, num_splits=7)[1]).num_splits == 1
+    one = runtime.plan(_plan(call, max_seqlen_q=1, max_seqlen_k=16384, num_splits=1)[1])
+    assert one.kernel_launches == 1 and one.workspace_bytes == 0
+    # a window bounds the keys a row can see, hence the useful splits
+    wide = runtime.plan(_plan(call, max_seqlen_q=1, max_seqlen_k=1 << 20)[1]).num_splits
+    narrow = runtime.plan(_plan(call, max_seqlen_q=1, max_seqlen_k=1 << 20, window_left=1023)[1]).num_splits
+    assert narrow < wide
+    # long queries: several row tiles per request -> device-side tile plan kernel + scratch for it
+    tiled = runtime.plan(_plan(call, max_seqlen_q=4, max_seqlen_k=256, num_splits=1)[1])
+    assert tiled.m_rows == 16 and tiled.kernel_launches == 1
+    tiled = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=256, num_splits=1)[1])
+    assert tiled.m_rows == 64 and tiled.kernel_launches == 2 and tiled.workspace_bytes > 0
+
+
+def test_launcher_rejects_bad_blocks_before_any_launch():
+    call = _call()
+    runtime, p = _plan(call)
+    lib = runtime.load_library()
+    info = runtime.PlanInfo()
+    p.abi_version = 1
+    assert lib.atrex_fa_sm100_plan(ctypes.byref(p), ctypes.byref(info)) == 6
+    runtime, p = _plan(call, head_dim=96)
+    with pytest.raises(NotImplementedError):
+        runtime.plan(p)
+    runtime, p = _plan(call, num_kv_heads=3)
+    with pytest.raises(ValueError):
+        runtime.plan(p)
+    runtime, p = _plan(call, page_size=48)
+    with pytest.raises(NotImplementedError):
+        runtime.plan(p)
+    runtime, p = _plan(call, k_row_stride=3)
+    with pytest.raises(NotImplementedError, match="status 2"):
+        runtime.plan(p)
+    assert lib.atrex_fa_sm100_plan(None, ctypes.byref(info)) == 1
