@@ -22,6 +22,8 @@ from atrex.utils.device_target import detect_device_target
 _TARGET_FA_VERSIONS = {("nvidia", "sm100"): frozenset({4})}
 
 _HEAD_DIMS = (128, 256)
+# E4M3 needs the tcgen05 route (the mma.sync route is BF16 only); flipped when that route serves FP8.
+_FP8_ROUTE_BUILT = False
 _MAX_SPLITS = 256
 
 # (argument, value that means "not used", message) for vLLM arguments that no
@@ -124,6 +126,10 @@ def _validate_sm100_call(call, torch, batch, window, softcap):
             raise ValueError(f"{name} must be a Python int")
     if q.shape[0] >= 2**31 or k.shape[0] >= 2**31:
         raise NotImplementedError("Atrex sm100 attention indexes rows and pages with 32 bits")
+    if block_table is None and call["cu_seqlens_k"] is None:
+        raise NotImplementedError("Atrex sm100 packed K/V requires cu_seqlens_k")
+    if q.dtype == torch.float8_e4m3fn and not _FP8_ROUTE_BUILT:
+        raise NotImplementedError("Atrex sm100 attention does not serve float8_e4m3fn yet (BF16 only)")
 
 
 def _validate_flash_attn_call(call):

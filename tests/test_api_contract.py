@@ -138,7 +138,9 @@ def _call(fp8=False, paged=True, hq=8, hkv=2, d=128, page=64):
 
 
 def test_good_calls_are_eligible(as_b200):
-    for kwargs in (dict(), dict(fp8=True), dict(paged=False), dict(d=256), dict(page=16), dict(page=4224),
+    fp8_ok = as_b200._FP8_ROUTE_BUILT
+    assert atrex.can_use_flash_attn_varlen_func(**_call(fp8=True)) == fp8_ok
+    for kwargs in (dict(), dict(paged=False), dict(d=256), dict(page=16), dict(page=4224),
                    dict(hq=64, hkv=4)):
         assert atrex.can_use_flash_attn_varlen_func(**_call(**kwargs)), kwargs
     good = _call()
@@ -147,7 +149,8 @@ def test_good_calls_are_eligible(as_b200):
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, s_aux=torch.zeros(8, dtype=torch.bfloat16)))
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, softcap=30.0, num_splits=256, causal=False))
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, logits_soft_cap=30.0))
-    assert atrex.can_use_flash_attn_varlen_func(**dict(_call(fp8=True), k_descale=torch.ones(1, 1).expand(2, 2)))
+    assert atrex.can_use_flash_attn_varlen_func(
+        **dict(_call(fp8=True), k_descale=torch.ones(1, 1).expand(2, 2))) == fp8_ok
 
 
 BAD = [
@@ -218,6 +221,9 @@ def test_shape_and_dtype_rejections(as_b200):
     for bad in (torch.ones(2, 3), torch.ones(2, 2, dtype=torch.float64)):
         with pytest.raises(ValueError, match="descales"):
             atrex.flash_attn_varlen_func(**dict(fp8, v_descale=bad))
+    if not as_b200._FP8_ROUTE_BUILT:
+        with pytest.raises(NotImplementedError, match="float8_e4m3fn"):
+            atrex.flash_attn_varlen_func(**fp8)
 
 
 def test_other_devices_are_rejected():
