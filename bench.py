@@ -38,6 +38,9 @@ WORKLOADS = {
     # BF16 paged decode, query length 1
     "decode_q1": dict(batch=64, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024, kv_hi=16384, pool=20000,
                       window=None, sink=False, lse=False, metric="paged_decode_hbm_bandwidth", unit="GB/s"),
+    # same shape at a quarter of the batch and a small pool: the case profiler captures run on
+    "decode_q1_small": dict(batch=16, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024, kv_hi=16384, pool=2500,
+                            window=None, sink=False, lse=False, metric="paged_decode_hbm_bandwidth", unit="GB/s"),
     # BF16 speculative decode, query length 4, sliding window, sinks, LSE
     "decode_q4_window": dict(batch=128, q_len=4, hq=64, hkv=4, d=128, page=128, kv_lo=32768, kv_hi=32768,
                              pool=128 * 256 + 64, window=(4095, 0), sink=True, lse=True,
@@ -297,13 +300,22 @@ def main():
     workspace = torch.empty(max(1, info.workspace_bytes), dtype=torch.uint8, device=device)
     lib = runtime.load_library()
     stream = torch.cuda.current_stream().cuda_stream
-    kernel_ms = []
-    for i in range(warmup + min(args.steps, 50)):
+    # Calls are queued back to back, each with its own event pair, so that an event is recorded when the previous
+    # call's last kernel retires and the attention kernel starts right behind it (no idle-GPU launch latency inside
+    # the measured interval).
+    n_timed = min(args.steps, 50)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
+    for a, b in pairs:
+        a.record(); b.record()
+    torch.cuda.synchronize()
+    for i in range(warmup + n_timed):
+        if i >= warmup:
+            a, b = pairs[i - warmup]
+            params.profile_event_begin, params.profile_event_end = a.cuda_event, b.cuda_event
         runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(params), workspace.data_ptr(),
                                                              workspace.numel(), stream))
-        torch.cuda.synchronize()
-        if i >= warmup:
-            kernel_ms.append(ev0.elapsed_time(ev1))
+    torch.cuda.synchronize()
+    kernel_ms = [a.elapsed_time(b) for a, b in pairs]
     kernel_ms_avg = sum(kernel_ms) / len(kernel_ms)
 
     # ---------------- end to end: host inputs in, host result out ----------------
