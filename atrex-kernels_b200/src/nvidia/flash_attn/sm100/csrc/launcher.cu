@@ -361,3 +361,72 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing (no counterpart in the reference).
+//
+// Some hosts of this library have no way to hand it scratch memory: a serving
+// process that binds the C ABI over FFI and only ever receives device pointers
+// from another runtime owns no device allocator; an engine that reserved all of
+// HBM for its KV-cache pool at start-up makes any later cudaMalloc fail; and a
+// latency-critical loop cannot afford cudaMalloc / cudaFree, which synchronise
+// the whole device.  For them the split-KV scratch (partial O and partial LSE,
+// plus the row-tile plan) lives in the fixed array below, which every GPU that
+// loads this library holds until the process exits.
+// ---------------------------------------------------------------------------
+namespace atrex_sm100 {
+namespace {
+
+constexpr uint64_t kStaticScratchBytes = ATREX_FA_SM100_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device.  In host code the array's
+// name is only a stand-in for the symbol, never a device address, so it is
+// resolved with cudaGetSymbolAddress once per device, with that device current.
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
+
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail(ATREX_FA_UNSUPPORTED, "device ordinal out of range");
+  void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(ATREX_FA_CUDA_ERROR, "cudaGetSymbolAddress(static scratch)", e);
+    g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
+  }
+  *out = ptr;
+  return ATREX_FA_OK;
+}
+
+}  // namespace
+}  // namespace atrex_sm100
+
+extern "C" {
+
+uint64_t atrex_fa_sm100_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int atrex_fa_sm100_forward_static_scratch(const atrex_fa_sm100_params* p, void* stream) {
+  atrex_fa_sm100_plan_info info;
+  int st = atrex_fa_sm100_plan(p, &info);
+  if (st != ATREX_FA_OK) return st;
+  if (info.workspace_bytes > kStaticScratchBytes) {
+    char text[200];
+    std::snprintf(text, sizeof(text),
+                  "call needs %llu bytes of scratch but the built-in scratch holds %llu: lower num_splits or "
+                  "use atrex_fa_sm100_forward with caller scratch",
+                  (unsigned long long)info.workspace_bytes, (unsigned long long)kStaticScratchBytes);
+    return fail(ATREX_FA_WORKSPACE_TOO_SMALL, text);
+  }
+  void* scratch = nullptr;
+  st = static_scratch_for_current_device(&scratch);
+  if (st != ATREX_FA_OK) return st;
+  // Nothing in the scratch has to start at zero: every partial a combine reads
+  // was written by the attention kernel of the same call, and a split without
+  // keys publishes LSE = -inf so its (stale) partial O is never read.
+  return atrex_fa_sm100_forward(p, scratch, kStaticScratchBytes, stream);
+}
+
+}  // extern "C"

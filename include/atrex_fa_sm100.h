@@ -165,6 +165,32 @@ ATREX_FA_API int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* wo
  */
 ATREX_FA_API int atrex_fa_sm100_prewarm(void);
 
+/*
+ * Same as atrex_fa_sm100_forward, for callers that cannot provide scratch memory.
+ * This entry point has no counterpart in the reference.  It exists for hosts that
+ * cannot allocate on the device: an FFI binding that only receives device pointers
+ * from another runtime and owns no allocator, a server whose HBM was handed
+ * entirely to its KV-cache pool at start-up, or a latency-critical loop that must
+ * not call cudaMalloc / cudaFree because they synchronise the device.
+ *
+ * The split-KV scratch comes from a fixed array inside the library
+ * (ATREX_FA_SM100_STATIC_SCRATCH_BYTES per GPU, held by every GPU that loads the
+ * library until the process exits).  A call whose plan needs more returns
+ * ATREX_FA_WORKSPACE_TOO_SMALL and launches nothing; atrex_fa_sm100_last_error()
+ * then names both sizes.  The call allocates and frees nothing, in this library or
+ * through any other.
+ *
+ * The first call on a device looks up the array's device address; make that first
+ * call (or any call of this function on that device) before starting a stream
+ * capture.  All calls on one device share the one array and it keeps the previous
+ * call's contents: nothing in it needs clearing between calls, but two calls whose
+ * kernels can overlap on the GPU (different streams without an ordering between
+ * them) race on it and must be serialised by the caller.
+ */
+#define ATREX_FA_SM100_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+ATREX_FA_API uint64_t atrex_fa_sm100_static_scratch_bytes(void);
+ATREX_FA_API int atrex_fa_sm100_forward_static_scratch(const atrex_fa_sm100_params* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
