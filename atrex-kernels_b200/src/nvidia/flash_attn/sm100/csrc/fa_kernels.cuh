@@ -25,6 +25,12 @@ int mma_tile_n(int head_dim);                 // KV tokens per pipeline stage
 cudaError_t mma_prepare();                    // per-device kernel attributes
 cudaError_t mma_launch(const FwdParams& p, int head_dim, int m_rows, cudaStream_t stream);
 
+// ---- fa_umma.cu: tcgen05 prefill kernel (BF16, head_dim 128) ----
+bool umma_supports(int head_dim, int group, int dtype_is_bf16);
+int umma_rows_per_item();                     // packed rows one work item covers (256)
+cudaError_t umma_prepare();
+cudaError_t umma_launch(const FwdParams& p, int sm_count, cudaStream_t stream);
+
 // ---- fa_combine.cu: merge split partials; tile plan ----
 cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream);
 // order[batch], tile_prefix[batch + 1] for row tiles of m_rows packed rows

@@ -17,6 +17,9 @@ constexpr float kLn2 = 0.6931471805599453f;
 struct alignas(64) FwdParams {
   CUtensorMap k_map;
   CUtensorMap v_map;
+  // Q as (D, Hq, total_q) with a box of (64 elements x group heads x 128/group rows): one box is
+  // 128 packed GQA rows of one KV head.  Only encoded for the tcgen05 route.
+  CUtensorMap q_map;
 
   const void* q;
   void* out;

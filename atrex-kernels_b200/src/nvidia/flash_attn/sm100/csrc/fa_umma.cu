@@ -1,0 +1,497 @@
+// Warp-specialised prefill kernel on tcgen05 tensor cores (UMMA) with TMEM accumulators.
+//
+// Native counterpart of the reference's Blackwell prefill
+// (src/nvidia/flash_attn/sm103/prefill_cutedsl.py:146-4331), designed for B200 and
+// head_dim 128 (which the reference never runs on tcgen05):
+//
+//   * one CTA walks a static stripe of work items; an item is 256 packed GQA rows
+//     (two 128-row Q subtiles) of one (request, KV head), heaviest requests first;
+//   * warp 9 is the TMA producer: Q subtiles once per item, then K and V tiles of
+//     128 tokens gathered page by page through the block table into a 4-slot ring of
+//     128-byte-swizzled tiles (no multicast);
+//   * warp 8 issues tcgen05.mma: S = Q K^T (both operands K-major in shared memory)
+//     into TMEM, then O_tile = P V with P read straight from TMEM and V MN-major in
+//     shared memory, alternating between the two subtiles so that one subtile's
+//     softmax overlaps the other's matrix work;
+//   * warpgroups 0 and 1 (one thread per row) do the online softmax in the log2
+//     domain, write P as BF16 back into the S columns of TMEM, and accumulate the
+//     per-tile P V result from TMEM into FP32 registers with the running rescale, so
+//     no separate correction pass over a TMEM-resident O is needed;
+//   * TMEM: S0 | S1 | PV0 | PV1, 128 columns each (all 512).
+//
+// Every mbarrier wait is bounded; on expiry the CTA records a code, drains its
+// copies, frees TMEM and returns.
+#include "fa_kernels.cuh"
+#include "umma.cuh"
+
+namespace atrex_sm100 {
+
+namespace {
+
+constexpr int kBM = 128;                      // rows per Q subtile (UMMA M)
+constexpr int kBN = 128;                      // KV tokens per tile (UMMA N of QK^T, K of PV)
+constexpr int kHD = 128;                      // head dimension
+constexpr int kTileBytes = kBN * kHD * 2;     // one K, V or Q tile: 32 KB
+constexpr int kBlockBytes = kBN * 128;        // one 64-element column block of a tile: 16 KB
+constexpr int kSlots = 4;                     // K/V ring: K(j), V(j), K(j+1), V(j+1)
+constexpr int kUmmaThreads = 384;
+constexpr int kRowsPerItem = 2 * kBM;
+constexpr uint32_t kTmemCols = 512;
+
+constexpr int kOffQ = 0;
+constexpr int kOffKV = 2 * kTileBytes;
+constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
+// barriers (8 bytes each)
+enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kOEmpty = 16, kNumBars = 18 };
+constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (u32), abort flag (int)
+constexpr int kUmmaSmemBytes = kOffMisc + 16;
+
+struct Item {
+  int b, kvh, row0, q_start, q_len, rows_total, kv_len, k_start, off;
+  int tile_lo, n_tiles;
+};
+
+// Work item `item` (request-major in heaviest-first order, KV head fastest).  False when past the end.
+__device__ __forceinline__ bool decode_item(const FwdParams& p, int item, Item& it) {
+  const int total_tiles = p.tile_prefix[p.batch];
+  const int tile_rank = item / p.num_kv_heads;
+  if (tile_rank >= total_tiles) return false;
+  it.kvh = item % p.num_kv_heads;
+  int lo = 0, hi = p.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.tile_prefix[mid] <= tile_rank) lo = mid; else hi = mid;
+  }
+  it.b = p.order[lo];
+  const int tiles_b = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
+  const int mt = tiles_b - 1 - (tile_rank - p.tile_prefix[lo]);  // last (heaviest causal) row tile first
+  it.row0 = mt * kRowsPerItem;
+  it.q_start = p.cu_seqlens_q[it.b];
+  it.q_len = p.cu_seqlens_q[it.b + 1] - it.q_start;
+  it.rows_total = it.q_len * p.group;
+  request_kv(p, it.b, it.kv_len, it.k_start);
+  it.off = it.kv_len - it.q_len;
+  const int qi_lo = it.row0 / p.group;
+  const int qi_hi = min(it.q_len - 1, (it.row0 + kRowsPerItem - 1) / p.group);
+  int kv_end = it.kv_len, kv_begin = 0;
+  if (p.window_right >= 0) kv_end = min(it.kv_len, qi_hi + it.off + p.window_right + 1);
+  if (p.window_left >= 0) kv_begin = max(0, qi_lo + it.off - p.window_left);
+  it.tile_lo = 0;
+  it.n_tiles = 0;
+  if (kv_end > kv_begin) {
+    it.tile_lo = kv_begin / kBN;
+    it.n_tiles = (kv_end + kBN - 1) / kBN - it.tile_lo;
+  }
+  return true;
+}
+
+#define UMMA_WAIT(bar_ptr, parity, code)                          \
+  if (!mbar_wait((bar_ptr), (parity))) {                          \
+    if (p.status) atomicExch(p.status, (code));                   \
+    atomicExch(abort_flag, 1);                                    \
+    break;                                                        \
+  }
+
+}  // namespace
+
+namespace {
+
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_smem = smem + kOffQ;
+  uint8_t* kv_smem = smem + kOffKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc);
+  int* abort_flag = reinterpret_cast<int*>(smem + kOffMisc + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (tid == 0 && p.status) atomicExch(p.status, kBadSmemAlignment);
+    return;
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(&bars[kQFull], 1);
+    mbar_init(&bars[kQEmpty], 1);
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&bars[kKVFull + s], 1);
+      mbar_init(&bars[kKVEmpty + s], 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&bars[kSFull + w], 1);
+      mbar_init(&bars[kPFull + w], kBM);
+      mbar_init(&bars[kOFull + w], 1);
+      mbar_init(&bars[kOEmpty + w], kBM);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_items_step = gridDim.x;
+
+  if (warp >= 8) {
+    // ============================ warpgroup 2: MMA issuer, TMA producer ============================
+    setmaxnreg_dec<96>();
+    if (warp == 9) {
+      // ------------------------------- TMA producer -------------------------------
+      if (lane == 0) {
+        prefetch_tensormap(&p.q_map);
+        prefetch_tensormap(&p.k_map);
+        prefetch_tensormap(&p.v_map);
+        const int boxes = kBN / p.box_rows;
+        const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
+        uint32_t it_count = 0, seq = 0;
+        bool q_issued = false;
+        for (int item = blockIdx.x;; item += n_items_step) {
+          Item it;
+          if (!decode_item(p, item, it)) break;
+          if (*(volatile int*)abort_flag) break;
+          if (it_count > 0) UMMA_WAIT(&bars[kQEmpty], (it_count - 1) & 1u, kWaitEmptyTimeout)
+          mbar_arrive_expect_tx(&bars[kQFull], 2u * kTileBytes);
+          q_issued = true;
+#pragma unroll
+          for (int w = 0; w < 2; ++w)
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+              tma_load_3d(q_smem + w * kTileBytes + kb * kBlockBytes, &p.q_map, &bars[kQFull], kb * 64,
+                          it.kvh * p.group, it.q_start + (it.row0 + w * kBM) / p.group);
+          const int32_t* table = p.page_size ? p.block_table + (int64_t)it.b * p.block_table_row_stride : nullptr;
+          bool failed = false;
+          for (int j = 0; j < it.n_tiles && !failed; ++j) {
+            const int tok0 = (it.tile_lo + j) * kBN;
+            for (int is_v = 0; is_v < 2; ++is_v) {
+              const uint32_t slot = seq % kSlots;
+              if (seq >= (uint32_t)kSlots && !mbar_wait(&bars[kKVEmpty + slot], ((seq / kSlots) - 1) & 1u)) {
+                if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
+                atomicExch(abort_flag, 1);
+                failed = true;
+                break;
+              }
+              uint8_t* dst = kv_smem + slot * kTileBytes;
+              const CUtensorMap* map = is_v ? &p.v_map : &p.k_map;
+              const int8_t(&perm)[3] = is_v ? p.v_perm : p.k_perm;
+              // which boxes exist, so the byte count is posted before any copy can complete
+              uint32_t live_mask = 0;
+              int live = 0;
+              for (int x = 0; x < boxes; ++x) {
+                const int tok = tok0 + x * p.box_rows;
+                if (tok >= it.kv_len) break;
+                if (p.page_size) {
+                  const int pg = table[tok / p.page_size];
+                  if (pg < 0 || pg >= p.num_pages) continue;
+                }
+                live_mask |= 1u << x;
+                ++live;
+              }
+              mbar_arrive_expect_tx(&bars[kKVFull + slot], (uint32_t)live * box_bytes * 2u);
+              for (int x = 0; x < boxes; ++x) {
+                if (!(live_mask >> x & 1u)) continue;
+                const int tok = tok0 + x * p.box_rows;
+                int pg = 0, row = it.k_start + tok;
+                if (p.page_size) {
+                  pg = table[tok / p.page_size];
+                  row = tok % p.page_size;
+                }
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb)
+                  tma_load_kv(dst + kb * kBlockBytes + x * box_bytes, map, &bars[kKVFull + slot], kb * 64, it.kvh, row,
+                              pg, perm);
+              }
+              ++seq;
+            }
+          }
+          if (failed) break;
+          ++it_count;
+        }
+        // Drain: every copy this thread issued must have landed before the CTA may exit.
+        if (q_issued) mbar_wait(&bars[kQFull], (it_count > 0 ? it_count - 1 : 0) & 1u);
+        for (uint32_t back = 1; back <= (uint32_t)kSlots && back <= seq; ++back) {
+          const uint32_t n = seq - back;
+          mbar_wait(&bars[kKVFull + n % kSlots], (n / kSlots) & 1u);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 8) {
+      // ------------------------------- MMA issuer -------------------------------
+      constexpr uint32_t kIdescQK = umma_idesc(kBM, kBN, 1, 1, 0, 0);
+      constexpr uint32_t kIdescPV = umma_idesc(kBM, kHD, 1, 1, 0, 1);
+      const uint32_t q_addr = smem_u32(q_smem);
+      const uint32_t kv_addr = smem_u32(kv_smem);
+      uint32_t it_count = 0, seq = 0, cp[2] = {0, 0}, co[2] = {0, 0};
+      bool dead = false;
+      auto issue_qk = [&](int w, uint32_t slot) {
+        if (lane == 0) {
+#pragma unroll
+          for (int ks = 0; ks < kHD / 16; ++ks) {
+            const uint32_t koff = (ks >> 2) * kBlockBytes + (ks & 3) * 32;
+            umma_ss_f16(tmem_base + w * kBN, umma_desc_sw128(q_addr + w * kTileBytes + koff, 16, 1024),
+                        umma_desc_sw128(kv_addr + slot * kTileBytes + koff, 16, 1024), kIdescQK, ks > 0);
+          }
+          umma_commit(&bars[kSFull + w]);
+        }
+      };
+      for (int item = blockIdx.x; !dead; item += n_items_step) {
+        Item it;
+        if (!decode_item(p, item, it)) break;
+        if (*(volatile int*)abort_flag) break;
+        if (it.n_tiles > 0) {
+          do {  // single pass; UMMA_WAIT leaves it on a timeout
+            UMMA_WAIT(&bars[kQFull], it_count & 1u, kWaitFullTimeout)
+            uint32_t slot_k = seq % kSlots;
+            UMMA_WAIT(&bars[kKVFull + slot_k], (seq / kSlots) & 1u, kWaitFullTimeout)
+            ++seq;
+            tcgen05_fence_after();
+            issue_qk(0, slot_k);
+            issue_qk(1, slot_k);
+            if (lane == 0) umma_commit(&bars[kKVEmpty + slot_k]);
+            for (int j = 0; j < it.n_tiles && !dead; ++j) {
+              const bool more = j + 1 < it.n_tiles;
+              const uint32_t slot_v = seq % kSlots;
+              if (!mbar_wait(&bars[kKVFull + slot_v], (seq / kSlots) & 1u)) { dead = true; break; }
+              ++seq;
+              // V rows past the end of the request may hold NaN: P is 0 there but 0 * NaN is NaN.
+              const int tok0 = (it.tile_lo + j) * kBN;
+              if (tok0 + kBN > it.kv_len) {
+                const int first = max(0, it.kv_len - tok0);
+                uint8_t* v_ptr = kv_smem + slot_v * kTileBytes;
+                for (int idx = lane; idx < (kBN - first) * 16; idx += 32) {
+                  const int r = first + idx / 16, c = idx % 16;
+                  *reinterpret_cast<uint4*>(v_ptr + (c / 8) * kBlockBytes + swz128(r, c % 8)) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();
+                __syncwarp();
+              }
+              uint32_t slot_k2 = 0;
+              if (more) {
+                slot_k2 = seq % kSlots;
+                if (!mbar_wait(&bars[kKVFull + slot_k2], (seq / kSlots) & 1u)) { dead = true; break; }
+                ++seq;
+              }
+              for (int w = 0; w < 2; ++w) {
+                if (!mbar_wait(&bars[kPFull + w], cp[w] & 1u)) { dead = true; break; }
+                ++cp[w];
+                if (!mbar_wait(&bars[kOEmpty + w], (co[w] + 1) & 1u)) { dead = true; break; }
+                ++co[w];
+                tcgen05_fence_after();
+                if (lane == 0) {
+#pragma unroll
+                  for (int ks = 0; ks < kBN / 16; ++ks)
+                    umma_ts_f16(tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
+                                umma_desc_sw128(kv_addr + slot_v * kTileBytes + ks * 2048, kBlockBytes, 1024),
+                                kIdescPV, ks > 0);
+                  umma_commit(&bars[kOFull + w]);
+                }
+                if (more) issue_qk(w, slot_k2);
+              }
+              if (dead) break;
+              if (lane == 0) {
+                umma_commit(&bars[kKVEmpty + slot_v]);
+                if (more) umma_commit(&bars[kKVEmpty + slot_k2]);
+              }
+            }
+            if (!dead && lane == 0) umma_commit(&bars[kQEmpty]);
+          } while (false);
+          if (dead || *(volatile int*)abort_flag) {
+            if (dead && lane == 0) {
+              if (p.status) atomicExch(p.status, kWaitMmaTimeout);
+              atomicExch(abort_flag, 1);
+            }
+            break;
+          }
+        } else {
+          // No key is visible: nothing to multiply, but the Q tiles were loaded and must be released.
+          bool ok = mbar_wait(&bars[kQFull], it_count & 1u);
+          if (!ok) { if (lane == 0) { if (p.status) atomicExch(p.status, kWaitFullTimeout); atomicExch(abort_flag, 1); } break; }
+          if (lane == 0) mbar_arrive(&bars[kQEmpty]);
+        }
+        ++it_count;
+      }
+      __syncwarp();
+    }
+  } else {
+    // ============================ warpgroups 0 and 1: softmax + accumulate ============================
+    setmaxnreg_inc<200>();
+    const int w = warp >> 2;                                   // subtile
+    const int r = (warp & 3) * 32 + lane;                      // row inside the subtile = TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_off + w * kBN;
+    const uint32_t o_tmem = tmem_base + lane_off + 2 * kBN + w * kHD;
+    uint32_t cs = 0, co = 0;
+    bool dead = false;
+    for (int item = blockIdx.x; !dead; item += n_items_step) {
+      Item it;
+      if (!decode_item(p, item, it)) break;
+      if (*(volatile int*)abort_flag) break;
+      const int sub_row0 = it.row0 + w * kBM;
+      const int row = sub_row0 + r;
+      const int qi = min(row / p.group, max(it.q_len - 1, 0));
+      const int hd = it.kvh * p.group + row % p.group;
+      const int vis_hi = p.window_right >= 0 ? min(it.kv_len, qi + it.off + p.window_right + 1) : it.kv_len;
+      const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
+      const int sqi_lo = sub_row0 / p.group;
+      const int sqi_hi = min(it.q_len - 1, (sub_row0 + kBM - 1) / p.group);
+      const int full_lo = p.window_left >= 0 ? max(0, sqi_hi + it.off - p.window_left) : 0;
+      const int full_hi = p.window_right >= 0 ? min(it.kv_len, sqi_lo + it.off + p.window_right + 1) : it.kv_len;
+      float dq = 1.f, dk = 1.f, dv = 1.f;
+      if (p.q_descale) dq = p.q_descale[it.b * p.q_descale_bs + it.kvh * p.q_descale_hs];
+      if (p.k_descale) dk = p.k_descale[it.b * p.k_descale_bs + it.kvh * p.k_descale_hs];
+      if (p.v_descale) dv = p.v_descale[it.b * p.v_descale_bs + it.kvh * p.v_descale_hs];
+      const float scale = p.softmax_scale * dq * dk;
+      const float scale_log2 = scale * kLog2e;
+      const float cap_in = p.softcap > 0.f ? scale / p.softcap : 0.f;
+      const float cap_out = p.softcap * kLog2e;
+
+      float m_run = -INFINITY, l_run = 0.f;
+      float o_acc[kHD];
+#pragma unroll
+      for (int i = 0; i < kHD; ++i) o_acc[i] = 0.f;
+
+      for (int j = 0; j < it.n_tiles; ++j) {
+        const int tok0 = (it.tile_lo + j) * kBN;
+        const bool need_mask = tok0 < full_lo || tok0 + kBN > full_hi;
+        if (!mbar_wait(&bars[kSFull + w], cs & 1u)) { dead = true; break; }
+        ++cs;
+        tcgen05_fence_after();
+        // ---- pass 1: row maximum of the scaled, masked scores ----
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(s_tmem + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[i]);
+            x = p.softcap > 0.f ? cap_out * fast_tanh(x * cap_in) : x * scale_log2;
+            if (need_mask) {
+              const int col = tok0 + c * 32 + i;
+              if (col < vis_lo || col >= vis_hi) x = -INFINITY;
+            }
+            mx = fmaxf(mx, x);
+          }
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = fast_exp2(m_run - m_use);
+        m_run = m_new;
+        // ---- pass 2: P = 2^(s - m) as BF16 into the S columns, row sum ----
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(s_tmem + c * 32, v);
+          tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+            if (p.softcap > 0.f) {
+              x0 = cap_out * fast_tanh(x0 * cap_in) - m_use;
+              x1 = cap_out * fast_tanh(x1 * cap_in) - m_use;
+            } else {
+              x0 = fmaf(x0, scale_log2, -m_use);
+              x1 = fmaf(x1, scale_log2, -m_use);
+            }
+            if (need_mask) {
+              const int col = tok0 + c * 32 + i;
+              if (col < vis_lo || col >= vis_hi) x0 = -INFINITY;
+              if (col + 1 < vis_lo || col + 1 >= vis_hi) x1 = -INFINITY;
+            }
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            sum += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
+          tmem_st16(s_tmem + c * 16, packed);
+        }
+        l_run = l_run * alpha + sum;
+        tmem_st_wait();
+        tcgen05_fence_before();
+        mbar_arrive(&bars[kPFull + w]);
+        // ---- accumulate this tile's P V (rescaling what came before) ----
+        if (!mbar_wait(&bars[kOFull + w], co & 1u)) { dead = true; break; }
+        ++co;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int c = 0; c < kHD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+        }
+        tcgen05_fence_before();
+        mbar_arrive(&bars[kOEmpty + w]);
+      }
+      if (dead) {
+        if (p.status) atomicExch(p.status, kWaitMmaTimeout);
+        atomicExch(abort_flag, 1);
+        break;
+      }
+      // ---- epilogue: normalise, store BF16 row and natural-log LSE ----
+      if (row < it.rows_total) {
+        float sink_l2 = -INFINITY;
+        if (p.sink != nullptr) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
+        const float m_f = fmaxf(m_run, sink_l2);
+        const float m_use = m_f == -INFINITY ? 0.f : m_f;
+        const float resc = fast_exp2(m_run - m_use);
+        float l = l_run * resc;
+        if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use);
+        const float inv = l > 0.f ? dv * resc / l : 0.f;
+        const int64_t q_row = it.q_start + row / p.group;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
+                             (int64_t)hd * p.out_head_stride;
+#pragma unroll
+        for (int i = 0; i < kHD; i += 8) {
+          uint4 pk;
+          pk.x = pack_bf16(o_acc[i] * inv, o_acc[i + 1] * inv);
+          pk.y = pack_bf16(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
+          pk.z = pack_bf16(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
+          pk.w = pack_bf16(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + i) = pk;
+        }
+        if (p.lse != nullptr)
+          p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l)) * kLn2 : -INFINITY;
+      }
+    }
+  }
+
+  // All roles meet here (every wait above is bounded), then the allocating warp frees TMEM.
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+bool umma_supports(int head_dim, int group, int dtype_is_bf16) {
+  return head_dim == kHD && dtype_is_bf16 && group >= 1 && group <= kBM && (kBM % group) == 0;
+}
+
+int umma_rows_per_item() { return kRowsPerItem; }
+
+cudaError_t umma_prepare() {
+  return cudaFuncSetAttribute(atrex_sm100_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kUmmaSmemBytes);
+}
+
+cudaError_t umma_launch(const FwdParams& p, int sm_count, cudaStream_t stream) {
+  const long long items = (long long)p.num_row_tiles * p.num_kv_heads;
+  const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
+  return launch_kernel(atrex_sm100_fwd_umma_kernel, dim3(grid), dim3(kUmmaThreads), kUmmaSmemBytes, stream, p);
+}
+
+}  // namespace atrex_sm100

@@ -76,8 +76,10 @@ int current_device(DeviceInfo** info) {
 
 int prepare_device(DeviceInfo& d) {
   if (d.prepared.load(std::memory_order_acquire)) return ATREX_FA_OK;
-  const cudaError_t e = mma_prepare();
+  cudaError_t e = mma_prepare();
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (mma kernels)", e);
+  e = umma_prepare();
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 kernel)", e);
   d.prepared.store(1, std::memory_order_release);
   return ATREX_FA_OK;
 }
@@ -113,7 +115,8 @@ int check_params(const atrex_fa_sm100_params* p) {
   if (p->num_splits > kMaxSplits) return ATREX_FA_UNSUPPORTED;
   if (p->page_size > 0 && p->page_size % 64 != 0 && p->page_size != 16 && p->page_size != 32)
     return ATREX_FA_UNSUPPORTED;
-  if (p->route != ATREX_FA_ROUTE_AUTO && p->route != ATREX_FA_ROUTE_MMA) return ATREX_FA_UNSUPPORTED;
+  if (p->route != ATREX_FA_ROUTE_AUTO && p->route != ATREX_FA_ROUTE_MMA && p->route != ATREX_FA_ROUTE_UMMA)
+    return ATREX_FA_INVALID_VALUE;
   // 16-byte alignment of everything the kernels touch with vectors or TMA
   const uint64_t es = 2;
   auto misaligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0; };
@@ -129,6 +132,28 @@ int check_params(const atrex_fa_sm100_params* p) {
 int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   const int group = p->num_q_heads / p->num_kv_heads;
   const int64_t packed_max = (int64_t)p->max_seqlen_q * group;
+  // The tcgen05 kernel takes prefill-shaped BF16 head_dim-128 calls (more packed rows than one
+  // mma.sync row tile) whose GQA group divides its 128-row subtile; everything else, and every call
+  // that asks for KV splits, runs on the mma.sync kernel.
+  const bool umma_ok = umma_supports(p->head_dim, group, p->dtype == ATREX_FA_BF16) && p->softcap == 0.f &&
+                       p->q_head_stride <= p->q_row_stride;
+  if (p->route == ATREX_FA_ROUTE_UMMA && !umma_ok) return ATREX_FA_UNSUPPORTED;
+  const bool use_umma = p->route == ATREX_FA_ROUTE_UMMA ||
+                        (p->route == ATREX_FA_ROUTE_AUTO && umma_ok && packed_max > 64 && p->num_splits <= 1);
+  if (use_umma) {
+    r->route = ATREX_FA_ROUTE_UMMA;
+    r->m_rows = umma_rows_per_item();
+    r->tiled = true;
+    const int64_t bound = ((int64_t)p->total_q * group) / r->m_rows + p->batch;
+    if (bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
+    r->num_row_tiles = (int)bound;
+    r->splits = 1;
+    r->launches = 2;
+    r->off_order = 0;
+    r->off_prefix = align_up(4ull * p->batch, 256);
+    r->off_lse = r->off_o = r->bytes = align_up(r->off_prefix + 4ull * (p->batch + 1), 256);
+    return ATREX_FA_OK;
+  }
   r->route = ATREX_FA_ROUTE_MMA;
   r->m_rows = mma_rows_for((int)(packed_max > 64 ? 64 : packed_max));
   r->tiled = packed_max > r->m_rows;
@@ -206,6 +231,21 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return res == CUDA_SUCCESS ? ATREX_FA_OK : fail(ATREX_FA_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the K/V layout");
+}
+
+// Q as (D, Hq, total_q); one box = 64 elements x `group` heads x 128/group rows = 128 packed GQA rows.
+int encode_q_map(CUtensorMap* map, const void* base, int64_t head_stride, int64_t row_stride, int heads,
+                 int64_t rows, int head_dim, int group) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(ATREX_FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t extent[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+  cuuint64_t stride[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)group, (cuuint32_t)(128 / group)};
+  cuuint32_t elem[3] = {1u, 1u, 1u};
+  const CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), extent, stride, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return res == CUDA_SUCCESS ? ATREX_FA_OK : fail(ATREX_FA_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the Q layout");
 }
 
 }  // namespace
@@ -306,6 +346,11 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   }
   if (st != ATREX_FA_OK) return st;
   for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
+  if (r.route == ATREX_FA_ROUTE_UMMA) {
+    st = encode_q_map(&f.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
+                      p->num_q_heads / p->num_kv_heads);
+    if (st != ATREX_FA_OK) return st;
+  }
 
   f.q = p->q; f.out = p->out; f.lse = p->return_lse ? p->lse : nullptr;
   f.cu_seqlens_q = p->cu_seqlens_q;
@@ -350,8 +395,9 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   if (p->profile_event_begin != nullptr &&
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream)) != cudaSuccess)
     return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_begin)", e);
-  if ((e = mma_launch(f, p->head_dim, r.m_rows, stream)) != cudaSuccess)
-    return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
+  e = r.route == ATREX_FA_ROUTE_UMMA ? umma_launch(f, p->sm_count > 0 ? p->sm_count : info->sm_count, stream)
+                                     : mma_launch(f, p->head_dim, r.m_rows, stream);
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
   if (p->profile_event_end != nullptr &&
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream)) != cudaSuccess)
     return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_end)", e);

@@ -18,10 +18,17 @@ import torch
 
 from . import runtime
 
+# Route used when the caller does not pass one: AUTO lets the native launcher choose.  Tests set this to
+# pin a kernel family, the way the reference's tests observe or force a route
+# (op_test/nvidia/flash_attn/test_flash_attn_sm103.py:415-427,894-930).
+DEFAULT_ROUTE = runtime.ROUTE_AUTO
+
 
 def forward(*, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, max_seqlen_q, max_seqlen_k, page_table,
             softmax_scale, causal, softcap, window_size_left, window_size_right, learnable_sink, out,
-            return_lse, q_descale, k_descale, v_descale, num_splits, route=runtime.ROUTE_AUTO):
+            return_lse, q_descale, k_descale, v_descale, num_splits, route=None):
+    if route is None:
+        route = DEFAULT_ROUTE
     if out is None:
         out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if return_lse else None

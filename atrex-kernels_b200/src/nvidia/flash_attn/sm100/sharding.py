@@ -1,0 +1,77 @@
+"""Sharding one attention batch over the GPUs of a box.
+
+Attention for one request (and one KV head) never reads another request's data, so the natural unit is the
+request: every rank owns whole requests (their Q rows, their pages, their O rows) and the data path needs no
+collective.  ``partition_requests`` balances the ranks by cost (visible (query, key) pairs for prefill, keys read
+for decode) with the longest-processing-time-first rule.  ``split_heads`` / ``gather_heads`` are the optional
+KV-head split: rank r computes KV heads [r*Hkv/G, (r+1)*Hkv/G) and their query heads for ALL requests, then one
+all-gather assembles O.  The reference has no multi-GPU code at all (its API rejects context-parallel arguments,
+python/atrex/api/flash_attn.py:128-135); this module is new surface that sits above the unchanged operator.
+"""
+
+from __future__ import annotations
+
+import heapq
+from typing import Sequence
+
+
+def request_cost(q_len: int, kv_len: int, causal: bool = True, window_left: int = -1) -> int:
+    """Visible (query, key) pairs of one request: proportional to its FLOPs (prefill) or its keys read (q_len 1)."""
+    if q_len <= 0 or kv_len <= 0:
+        return 0
+    off = kv_len - q_len
+    total = 0
+    if not causal and window_left < 0:
+        return q_len * kv_len
+    if window_left < 0 and off >= 0:
+        return q_len * off + q_len * (q_len + 1) // 2
+    for i in range(q_len):
+        hi = min(kv_len - 1, i + off) if causal else kv_len - 1
+        lo = max(0, i + off - window_left) if window_left >= 0 else 0
+        total += max(0, hi - lo + 1)
+    return total
+
+
+def partition_requests(costs: Sequence[int], world_size: int) -> list[list[int]]:
+    """Greedy LPT: requests in descending cost, each to the currently lightest rank.  Returns request ids per rank
+    (each list ascending).  Deterministic, so every rank can compute the same partition without communicating."""
+    if world_size <= 0:
+        raise ValueError("world_size must be positive")
+    shards: list[list[int]] = [[] for _ in range(world_size)]
+    heap = [(0, r) for r in range(world_size)]
+    heapq.heapify(heap)
+    for idx in sorted(range(len(costs)), key=lambda i: (-costs[i], i)):
+        load, rank = heapq.heappop(heap)
+        shards[rank].append(idx)
+        heapq.heappush(heap, (load + costs[idx], rank))
+    return [sorted(s) for s in shards]
+
+
+def shard_loads(costs: Sequence[int], shards: Sequence[Sequence[int]]) -> list[int]:
+    return [sum(costs[i] for i in shard) for shard in shards]
+
+
+def split_heads(num_q_heads: int, num_kv_heads: int, world_size: int, rank: int) -> tuple[slice, slice]:
+    """Query-head and KV-head slices rank ``rank`` computes in the KV-head-split variant."""
+    if num_kv_heads % world_size:
+        raise ValueError("num_kv_heads must be divisible by the number of ranks for a KV-head split")
+    kv_per = num_kv_heads // world_size
+    group = num_q_heads // num_kv_heads
+    return (slice(rank * kv_per * group, (rank + 1) * kv_per * group), slice(rank * kv_per, (rank + 1) * kv_per))
+
+
+def gather_heads(local_out, world_size: int, group=None):
+    """All-gather ``local_out [total_q, Hq/G, D]`` from every rank into ``[total_q, Hq, D]`` (rank-major heads).
+
+    One ``all_gather_into_tensor`` over NCCL / NVLink followed by a local transpose; with ``world_size == 1`` it is
+    the identity.  The tensors are this GPU's own memory on both sides of the collective.
+    """
+    import torch
+    import torch.distributed as dist
+
+    if world_size == 1:
+        return local_out
+    total_q, heads, dim = local_out.shape
+    staged = torch.empty((world_size * total_q, heads, dim), dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(staged, local_out.contiguous(), group=group)
+    return staged.view(world_size, total_q, heads, dim).permute(1, 0, 2, 3).reshape(total_q, world_size * heads, dim)

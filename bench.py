@@ -5,11 +5,13 @@
 One "step" is one call of ``atrex.flash_attn_varlen_func`` over one synthetic batch.
 The default workload is the BF16 Q1 paged decode configuration (batch 64, 32 query /
 8 KV heads, head_dim 128, page 64, KV lengths uniform in [1024, 16384], block table =
-seeded permutation of a 20000-page pool, N(0,1) inputs, num_splits = 0).  The metric
+seeded permutation of a 20000-page pool, N(0,1) inputs, num_splits = 0).  Its metric
 is achieved HBM GB/s on ALGORITHMIC bytes: the K and V rows every query can see, plus
-Q, O and the page-table entries read.  With N > 1 every rank runs its own batch of
-the same shape (weak scaling, no collective on the data path); time is the maximum
-over ranks, value the sum of bytes over ranks divided by it.
+Q, O and the page-table entries read.  Prefill workloads report TFLOP/s on algorithmic
+FLOPs (4 * D * Hq * visible pairs).  With N > 1 a "weak" workload gives every rank its
+own batch of the same shape; the "strong" prefill workload shards one fixed request
+set over the ranks, FLOP-balanced, request by request.  No collective is on the data
+path; time is the maximum over ranks, value the work of all ranks divided by it.
 
 ``--impl reference`` times the CPU FP32 attention (the oracle port of the reference's
 ``reference()`` in op_test/utils/flash_attn_contract.py:81-111) on the host cores on a
@@ -34,17 +36,31 @@ for _p in (os.path.join(ROOT, "atrex-kernels_b200", "python"), ROOT, os.path.joi
 
 import numpy as np  # noqa: E402
 
+
 WORKLOADS = {
     # BF16 paged decode, query length 1
-    "decode_q1": dict(batch=64, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024, kv_hi=16384, pool=20000,
-                      window=None, sink=False, lse=False, metric="paged_decode_hbm_bandwidth", unit="GB/s"),
+    "decode_q1": dict(kind="decode", batch=64, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024, kv_hi=16384,
+                      pool=20000, window=None, sink=False, lse=False, scaling="weak"),
     # same shape at a quarter of the batch and a small pool: the case profiler captures run on
-    "decode_q1_small": dict(batch=16, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024, kv_hi=16384, pool=2500,
-                            window=None, sink=False, lse=False, metric="paged_decode_hbm_bandwidth", unit="GB/s"),
+    "decode_q1_small": dict(kind="decode", batch=16, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024,
+                            kv_hi=16384, pool=2500, window=None, sink=False, lse=False, scaling="weak"),
     # BF16 speculative decode, query length 4, sliding window, sinks, LSE
-    "decode_q4_window": dict(batch=128, q_len=4, hq=64, hkv=4, d=128, page=128, kv_lo=32768, kv_hi=32768,
-                             pool=128 * 256 + 64, window=(4095, 0), sink=True, lse=True,
-                             metric="paged_decode_hbm_bandwidth", unit="GB/s"),
+    "decode_q4_window": dict(kind="decode", batch=128, q_len=4, hq=64, hkv=4, d=128, page=128, kv_lo=32768,
+                             kv_hi=32768, pool=128 * 256 + 64, window=(4095, 0), sink=True, lse=True,
+                             scaling="weak"),
+    # BF16 causal paged prefill, head_dim 128, query = full KV; lengths log-normal (median 8192, sigma 0.75,
+    # clipped to [1024, 131072]).  "prefill_hd128" is a 16-request batch per GPU; "prefill_sharded" is one fixed
+    # 256-request set sharded over the ranks by request, FLOP-balanced.
+    "prefill_hd128": dict(kind="prefill", batch=16, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
+                          clip=(1024, 131072), window=None, sink=False, lse=False, scaling="weak"),
+    "prefill_small": dict(kind="prefill", batch=4, hq=64, hkv=8, d=128, page=64, median=4096, sigma=0.5,
+                          clip=(1024, 16384), window=None, sink=False, lse=False, scaling="weak"),
+    "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
+                            clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
+}
+KIND = {
+    "decode": dict(metric="paged_decode_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
+    "prefill": dict(metric="paged_prefill_tensor_throughput", unit="TFLOP/s", scale=1e12, bound="tensor"),
 }
 
 
@@ -53,25 +69,34 @@ def measured_peaks():
     if os.path.isfile(path):
         with open(path) as f:
             data = json.load(f)
-        return dict(hbm_gbs=float(data["hbm_gbs"]), source="measured")
-    return dict(hbm_gbs=6650.0, source="fallback")
+        return dict(hbm=float(data["hbm_gbs"]), tensor=float(data["bf16_tflops_sustained"]),
+                    tensor_burst=float(data["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
 
 
 def draw_lengths(spec, seed):
+    """(q_lens, kv_lens) of one batch."""
     rng = np.random.default_rng(seed)
-    return rng.integers(spec["kv_lo"], spec["kv_hi"] + 1, size=spec["batch"]).tolist()
+    if spec["kind"] == "decode":
+        kv = rng.integers(spec["kv_lo"], spec["kv_hi"] + 1, size=spec["batch"]).tolist()
+        return [spec["q_len"]] * spec["batch"], kv
+    raw = np.exp(rng.normal(np.log(spec["median"]), spec["sigma"], spec["batch"]))
+    kv = np.clip(np.round(raw), *spec["clip"]).astype(int).tolist()
+    return list(kv), list(kv)
 
 
-def algorithmic_bytes(spec, kv_lens):
-    from oracle.fa_oracle import algorithmic_decode_bytes
+def work_units(spec, q_lens, kv_lens):
+    """Algorithmic bytes (decode) or FLOPs (prefill) of one pass over the batch."""
+    from oracle import fa_oracle
 
     window = spec["window"] or (-1, -1)
-    total = algorithmic_decode_bytes([spec["q_len"]] * spec["batch"], kv_lens, spec["hq"], spec["hkv"], spec["d"], 2,
-                                     spec["page"], window=window)
-    if spec["lse"]:
-        total += 4 * spec["batch"] * spec["q_len"] * spec["hq"]
-    return total
-
+    if spec["kind"] == "decode":
+        total = fa_oracle.algorithmic_decode_bytes(q_lens, kv_lens, spec["hq"], spec["hkv"], spec["d"], 2,
+                                                   spec["page"], window=window)
+        if spec["lse"]:
+            total += 4 * sum(q_lens) * spec["hq"]
+        return total
+    return fa_oracle.algorithmic_flops(q_lens, kv_lens, spec["hq"], spec["d"], True, window)
 
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read only)."""
@@ -131,33 +156,47 @@ def physical_gpu_index(local_index):
     return local_index
 
 
-def build_device_case(spec, kv_lens, seed, device):
+
+def physical_gpu_index(local_index):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        try:
+            return int(visible.split(",")[local_index])
+        except (ValueError, IndexError):
+            return local_index
+    return local_index
+
+
+def build_device_case(spec, q_lens, kv_lens, seed, device):
     """Synthetic batch resident on ``device`` plus pinned host copies of the per-step inputs."""
     import torch
 
     g = torch.Generator(device=device).manual_seed(seed)
-    pool, page, hkv, d = spec["pool"], spec["page"], spec["hkv"], spec["d"]
+    page, hkv, d = spec["page"], spec["hkv"], spec["d"]
+    counts = [-(-n // page) for n in kv_lens]
+    pool = spec.get("pool") or sum(counts) + 8
     k = torch.randn((pool, page, hkv, d), generator=g, device=device, dtype=torch.bfloat16)
     v = torch.randn((pool, page, hkv, d), generator=g, device=device, dtype=torch.bfloat16)
-    batch, q_len = spec["batch"], spec["q_len"]
-    q = torch.randn((batch * q_len, spec["hq"], d), generator=g, device=device, dtype=torch.bfloat16)
-    counts = [-(-n // page) for n in kv_lens]
-    width = max(counts)
+    total_q = sum(q_lens)
+    q = torch.randn((total_q, spec["hq"], d), generator=g, device=device, dtype=torch.bfloat16)
+    width = max(counts + [1])
     rng = np.random.default_rng(seed + 1)
     perm = rng.permutation(pool).astype(np.int32)
-    table = np.full((batch, width), -1, dtype=np.int32)
+    table = np.full((len(counts), width), -1, dtype=np.int32)
     o = 0
     for r, n in enumerate(counts):
         table[r, :n] = perm[o:o + n]
         o += n
     assert o <= pool
+    cu = np.zeros(len(q_lens) + 1, dtype=np.int32)
+    cu[1:] = np.cumsum(q_lens)
     host = dict(
         q=q.cpu().pin_memory(),
-        cu_seqlens_q=(torch.arange(batch + 1, dtype=torch.int32) * q_len).pin_memory(),
+        cu_seqlens_q=torch.from_numpy(cu).pin_memory(),
         seqused_k=torch.tensor(kv_lens, dtype=torch.int32).pin_memory(),
         block_table=torch.from_numpy(table).pin_memory(),
     )
-    case = dict(q=q, k=k, v=v, max_seqlen_q=q_len, cu_seqlens_q=host["cu_seqlens_q"].to(device),
+    case = dict(q=q, k=k, v=v, max_seqlen_q=max(q_lens + [0]), cu_seqlens_q=host["cu_seqlens_q"].to(device),
                 max_seqlen_k=width * page, seqused_k=host["seqused_k"].to(device),
                 block_table=host["block_table"].to(device), softmax_scale=d ** -0.5, causal=True,
                 window_size=spec["window"], num_splits=0, return_softmax_lse=spec["lse"],
@@ -167,60 +206,71 @@ def build_device_case(spec, kv_lens, seed, device):
     return case, host
 
 
-def cpu_baseline(spec, kv_lens, seed, budget_s=12.0):
-    """The CPU FP32 oracle on the first requests of the workload until about ``budget_s`` seconds are used."""
-    from oracle import fa_oracle
-
-    rng = np.random.default_rng(seed)
-    hq, hkv, d, page = spec["hq"], spec["hkv"], spec["d"], spec["page"]
-    done_bytes, used, n_req, t_total = 0, 0.0, 0, 0.0
-    window = spec["window"] or (-1, -1)
-    for b, n in enumerate(kv_lens):
-        pages = -(-n // page)
-        k = fa_oracle.bf16_round(rng.standard_normal((pages, page, hkv, d), dtype=np.float32))
-        v = fa_oracle.bf16_round(rng.standard_normal((pages, page, hkv, d), dtype=np.float32))
-        q = fa_oracle.bf16_round(rng.standard_normal((spec["q_len"], hq, d), dtype=np.float32))
-        table = np.arange(pages, dtype=np.int32)[None, :]
-        sink = rng.standard_normal(hq).astype(np.float32) if spec["sink"] else None
-        t0 = time.perf_counter()
-        fa_oracle.attention(q, k, v, np.array([0, spec["q_len"]], np.int32), seqused_k=np.array([n], np.int32),
-                            block_table=table, softmax_scale=d ** -0.5, causal=True, window=window, sink=sink)
-        t_total += time.perf_counter() - t0
-        done_bytes += algorithmic_bytes(dict(spec, batch=1), [n])
-        n_req += 1
-        if t_total >= budget_s or n_req >= 16:
-            break
+def cpu_threads():
     try:
         from threadpoolctl import threadpool_info
 
-        cores = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+        return max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
     except Exception:
-        cores = os.cpu_count() or 1
-    return dict(value=done_bytes / t_total / 1e9, unit=spec["unit"], cores=cores, kind="port",
-                sample=f"first {n_req} of {spec['batch']} requests of the workload, one pass, {t_total:.1f} s"), t_total
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(spec, q_lens, kv_lens, seed, budget_s=12.0):
+    """The CPU FP32 oracle over requests of the workload (shortest first for prefill) until about ``budget_s``
+    seconds are used.  Returns (cpu_baseline dict, seconds)."""
+    from oracle import fa_oracle
+
+    kind = KIND[spec["kind"]]
+    rng = np.random.default_rng(seed)
+    hq, hkv, d, page = spec["hq"], spec["hkv"], spec["d"], spec["page"]
+    window = spec["window"] or (-1, -1)
+    order = range(len(kv_lens)) if spec["kind"] == "decode" else np.argsort(kv_lens).tolist()
+    done, n_req, t_total = 0, 0, 0.0
+    for b in order:
+        nq, n = q_lens[b], kv_lens[b]
+        if spec["kind"] == "prefill" and n_req >= 1 and t_total > 0 and t_total * (1 + (n / kv_lens[order[0]]) ** 2) > 2.5 * budget_s:
+            break
+        pages = -(-n // page)
+        k = fa_oracle.bf16_round(rng.standard_normal((pages, page, hkv, d), dtype=np.float32))
+        v = fa_oracle.bf16_round(rng.standard_normal((pages, page, hkv, d), dtype=np.float32))
+        q = fa_oracle.bf16_round(rng.standard_normal((nq, hq, d), dtype=np.float32))
+        table = np.arange(pages, dtype=np.int32)[None, :]
+        sink = rng.standard_normal(hq).astype(np.float32) if spec["sink"] else None
+        t0 = time.perf_counter()
+        fa_oracle.attention(q, k, v, np.array([0, nq], np.int32), seqused_k=np.array([n], np.int32),
+                            block_table=table, softmax_scale=d ** -0.5, causal=True, window=window, sink=sink)
+        t_total += time.perf_counter() - t0
+        done += work_units(spec, [nq], [n])
+        n_req += 1
+        if t_total >= budget_s or n_req >= 16:
+            break
+    which = "first" if spec["kind"] == "decode" else "shortest"
+    return dict(value=done / t_total / kind["scale"], unit=kind["unit"], cores=cpu_threads(), kind="port",
+                sample=f"{which} {n_req} of {len(kv_lens)} requests of the workload, one pass, {t_total:.1f} s"), t_total
 
 
 def run_reference(args, spec, rank, world):
     """CPU arm: each step is the oracle over a bounded sample of the batch."""
     if rank != 0:
         return
-    kv_lens = draw_lengths(spec, 1729)
+    kind = KIND[spec["kind"]]
+    q_lens, kv_lens = draw_lengths(spec, 1729)
     steps, warm = max(1, args.steps), max(0, args.warmup)
     per_step = max(2.0, min(20.0, 120.0 / (steps + warm)))
     for _ in range(min(warm, 1)):
-        cpu_baseline(spec, kv_lens, 1729, budget_s=1.0)
-    values, samples, total_t = [], None, 0.0
+        cpu_baseline(spec, q_lens, kv_lens, 1729, budget_s=1.0)
+    values, sample, total_t = [], None, 0.0
     for _ in range(min(steps, 8)):
-        base, t = cpu_baseline(spec, kv_lens, 1729, budget_s=per_step)
-        values.append(base["value"])
-        samples, total_t = base, total_t + t
+        sample, t = cpu_baseline(spec, q_lens, kv_lens, 1729, budget_s=per_step)
+        values.append(sample["value"])
+        total_t += t
     value = statistics.median(values)
-    line = dict(impl="reference", metric=spec["metric"], value=value, unit=spec["unit"], n_gpus=args.gpus,
+    line = dict(impl="reference", metric=kind["metric"], value=value, unit=kind["unit"], n_gpus=args.gpus,
                 steps=len(values), warmup=min(warm, 1), ms_per_step=total_t / len(values) * 1e3,
-                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=args.workload, **{k: spec[k] for k in ("batch", "q_len", "hq", "hkv", "d", "page")}),
-                cpu_baseline=dict(samples, value=value),
-                e2e=dict(value=value, unit=spec["unit"], h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+                higher_is_better=True, scaling=spec["scaling"], vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, **{k: spec[k] for k in ("batch", "hq", "hkv", "d", "page")}),
+                cpu_baseline=dict(sample, value=value),
+                e2e=dict(value=value, unit=kind["unit"], h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
@@ -232,9 +282,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_q1", choices=sorted(WORKLOADS))
     ap.add_argument("--num-splits", type=int, default=0)
+    ap.add_argument("--route", default="auto", choices=["auto", "mma", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     spec = WORKLOADS[args.workload]
+    kind = KIND[spec["kind"]]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -250,15 +302,26 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     import atrex
-    from atrex.src.nvidia.flash_attn.sm100 import runtime
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime, sharding
 
     runtime.prewarm(device)
+    route = dict(auto=runtime.ROUTE_AUTO, mma=runtime.ROUTE_MMA, umma=runtime.ROUTE_UMMA)[args.route]
+    launch.DEFAULT_ROUTE = route
     warmup = max(3, args.warmup)
-    seed = 1729 + 1000 * rank
-    kv_lens = draw_lengths(spec, seed)
-    case, host = build_device_case(spec, kv_lens, seed, device)
+    if spec["scaling"] == "strong":
+        # one fixed request set for the whole job; every rank derives the same FLOP-balanced partition
+        seed = 1729
+        all_q, all_kv = draw_lengths(spec, seed)
+        costs = [sharding.request_cost(a, b) for a, b in zip(all_q, all_kv)]
+        mine = sharding.partition_requests(costs, world)[rank]
+        q_lens, kv_lens = [all_q[i] for i in mine], [all_kv[i] for i in mine]
+        seed += 1000 * rank
+    else:
+        seed = 1729 + 1000 * rank
+        q_lens, kv_lens = draw_lengths(spec, seed)
+    case, host = build_device_case(spec, q_lens, kv_lens, seed, device)
     case["num_splits"] = args.num_splits
-    my_bytes = algorithmic_bytes(spec, kv_lens)
+    my_work = work_units(spec, q_lens, kv_lens)
 
     def barrier():
         if world > 1:
@@ -284,19 +347,14 @@ def main():
     elapsed_ms = start.elapsed_time(stop)
 
     # ---------------- dominant kernel alone (events recorded by the launcher around it) ----------------
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(); ev1.record()
-    torch.cuda.synchronize()
-    plan_args = (case["q"], case["k"], case["v"], case["out"], None, case["cu_seqlens_q"], None, case["seqused_k"],
+    window = spec["window"] or (-1, -1)
+    plan_args = [case["q"], case["k"], case["v"], case["out"], None, case["cu_seqlens_q"], None, case["seqused_k"],
                  case["block_table"], None, None, None, case.get("s_aux"), None, case["max_seqlen_q"],
-                 case["max_seqlen_k"], case["softmax_scale"], 0.0, True,
-                 spec["window"][0] if spec["window"] else -1, spec["window"][1] if spec["window"] else -1,
-                 args.num_splits, 0)
+                 case["max_seqlen_k"], case["softmax_scale"], 0.0, True, window[0], window[1], args.num_splits, route]
+    if spec["lse"]:
+        plan_args[4] = torch.empty((spec["hq"], case["q"].shape[0]), dtype=torch.float32, device=device)
     params = runtime.build_params(*plan_args)
     info = runtime.plan(params)
-    lse_buf = torch.empty((spec["hq"], case["q"].shape[0]), dtype=torch.float32, device=device) if spec["lse"] else None
-    params = runtime.build_params(*plan_args[:4], lse_buf, *plan_args[5:])
-    params.profile_event_begin, params.profile_event_end = ev0.cuda_event, ev1.cuda_event
     workspace = torch.empty(max(1, info.workspace_bytes), dtype=torch.uint8, device=device)
     lib = runtime.load_library()
     stream = torch.cuda.current_stream().cuda_stream
@@ -308,10 +366,9 @@ def main():
     for a, b in pairs:
         a.record(); b.record()
     torch.cuda.synchronize()
-    for i in range(warmup + n_timed):
-        if i >= warmup:
-            a, b = pairs[i - warmup]
-            params.profile_event_begin, params.profile_event_end = a.cuda_event, b.cuda_event
+    for i in range(3 + n_timed):
+        a, b = pairs[max(i - 3, 0)]
+        params.profile_event_begin, params.profile_event_end = a.cuda_event, b.cuda_event
         runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(params), workspace.data_ptr(),
                                                              workspace.numel(), stream))
     torch.cuda.synchronize()
@@ -332,50 +389,60 @@ def main():
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for _ in range(warmup):
+    e2e_steps = args.steps if spec["kind"] == "decode" else max(1, min(args.steps, 5))
+    for _ in range(min(warmup, 3)):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         e2e_step()
     e2.record()
     barrier()
     # every step ends with a host-side stream synchronise, so wall clock and device events bracket the same work
-    e2e_ms = max(s2.elapsed_time(e2), (time.perf_counter() - t0) * 1e3)
+    e2e_ms = max(s2.elapsed_time(e2), (time.perf_counter() - t0) * 1e3) / e2e_steps
 
     status = runtime.check_device_status(device)
 
     # ---------------- reduce over ranks ----------------
     stats = torch.tensor([elapsed_ms, e2e_ms, kernel_ms_avg], dtype=torch.float64, device=device)
-    total_bytes = torch.tensor([float(my_bytes)], dtype=torch.float64, device=device)
+    total_work = torch.tensor([float(my_work)], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
+        dist.all_reduce(total_work, op=dist.ReduceOp.SUM)
     elapsed_ms, e2e_ms, kernel_ms_avg = stats.tolist()
-    total = total_bytes.item()
+    total = total_work.item()
 
     if rank == 0:
         peaks = measured_peaks()
-        value = total * args.steps / (elapsed_ms * 1e-3) / 1e9
-        achieved = my_bytes / (kernel_ms_avg * 1e-3) / 1e9
+        peak = peaks[kind["bound"]]
+        value = total * args.steps / (elapsed_ms * 1e-3) / kind["scale"]
+        achieved = my_work / (kernel_ms_avg * 1e-3) / kind["scale"]
+        kernel_name = "atrex_sm100_fwd_umma_kernel" if info.route == runtime.ROUTE_UMMA else "atrex_sm100_fwd_mma_kernel"
+        roofline = dict(bound=kind["bound"], achieved=achieved, peak=peak, unit=kind["unit"], frac=achieved / peak,
+                        traffic=None, peak_source=peaks["source"], kernel=kernel_name, kernel_ms=kernel_ms_avg)
+        if kind["bound"] == "hbm":
+            roofline["frac_of_nominal_8tbs"] = achieved / 8000.0
+        else:
+            roofline["peak_kind"] = "sustained cuBLAS bf16 (kernel timed inside a long step)"
+            roofline["frac_of_burst_peak"] = achieved / peaks["tensor_burst"]
+            roofline["frac_of_nominal_2250"] = achieved / 2250.0
         line = dict(
-            metric=spec["metric"], value=value, unit=spec["unit"], n_gpus=world, steps=args.steps, warmup=warmup,
-            ms_per_step=elapsed_ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+            metric=kind["metric"], value=value, unit=kind["unit"], n_gpus=world, steps=args.steps, warmup=warmup,
+            ms_per_step=elapsed_ms / args.steps, higher_is_better=True, scaling=spec["scaling"], vs_baseline=None,
             dtype="bf16", data="synthetic",
-            config=dict(workload=args.workload, batch_per_gpu=spec["batch"], q_len=spec["q_len"],
-                        num_q_heads=spec["hq"], num_kv_heads=spec["hkv"], head_dim=spec["d"],
-                        page_size=spec["page"], kv_len_range=[spec["kv_lo"], spec["kv_hi"]], pool_pages=spec["pool"],
-                        num_splits=info.num_splits, sharding="one batch per rank, no collective",
-                        l2="inputs larger than L2 (K/V touched per step >> 126 MB)",
-                        algorithmic_bytes_per_step_per_gpu=my_bytes),
-            roofline=dict(bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
-                          frac=achieved / peaks["hbm_gbs"], traffic=None, peak_source=peaks["source"],
-                          frac_of_nominal_8tbs=achieved / 8000.0, kernel="atrex_sm100_fwd_mma_kernel",
-                          kernel_ms=kernel_ms_avg),
-            e2e=dict(value=total * args.steps / (e2e_ms * 1e-3) / 1e9, unit=spec["unit"], h2d_bytes_per_step=h2d,
-                     d2h_bytes_per_step=d2h,
+            config=dict(workload=args.workload, requests_on_rank0=len(q_lens), batch=spec["batch"],
+                        num_q_heads=spec["hq"], num_kv_heads=spec["hkv"], head_dim=spec["d"], page_size=spec["page"],
+                        q_tokens_rank0=sum(q_lens), kv_tokens_rank0=sum(kv_lens), max_kv_len=max(kv_lens),
+                        num_splits=info.num_splits, route=args.route,
+                        sharding=("one batch per rank, no collective" if spec["scaling"] == "weak" else
+                                  "one request set, FLOP-balanced LPT by request, no collective"),
+                        l2="inputs larger than L2 (K/V + Q touched per step >> 126 MB)",
+                        algorithmic_work_per_step_rank0=my_work),
+            roofline=roofline,
+            e2e=dict(value=total / (e2e_ms * 1e-3) / kind["scale"], unit=kind["unit"], h2d_bytes_per_step=h2d,
+                     d2h_bytes_per_step=d2h, steps=e2e_steps,
                      note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory, "
                           "O copied back; the paged KV cache is resident device state"),
             gpu_launches=info.kernel_launches * args.steps,
@@ -383,7 +450,7 @@ def main():
             device_status=status,
         )
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"], _ = cpu_baseline(spec, kv_lens, seed)
+            line["cpu_baseline"], _ = cpu_baseline(spec, q_lens, kv_lens, seed)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

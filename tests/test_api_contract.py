@@ -327,8 +327,18 @@ def test_plan_is_a_pure_function_of_static_sizes():
     # long queries: several row tiles per request -> device-side tile plan kernel + scratch for it
     tiled = runtime.plan(_plan(call, max_seqlen_q=4, max_seqlen_k=256, num_splits=1)[1])
     assert tiled.m_rows == 16 and tiled.kernel_launches == 1
-    tiled = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=256, num_splits=1)[1])
+    tiled = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=256, num_splits=1, route=runtime.ROUTE_MMA)[1])
     assert tiled.m_rows == 64 and tiled.kernel_launches == 2 and tiled.workspace_bytes > 0
+    # prefill-shaped BF16 head_dim-128 calls go to the tcgen05 kernel: 256 packed rows per item, no KV split
+    umma = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=256)[1])
+    assert umma.route == runtime.ROUTE_UMMA and umma.m_rows == 256 and umma.num_splits == 1
+    assert umma.kernel_launches == 2 and umma.workspace_bytes > 0
+    # ... unless the caller asks for splits, the head dimension is 256, or the group does not divide 128
+    assert runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=4096, num_splits=4)[1]).route == runtime.ROUTE_MMA
+    assert runtime.plan(_plan(_call(hq=12, hkv=4), max_seqlen_q=64, max_seqlen_k=256)[1]).route == runtime.ROUTE_MMA
+    assert runtime.plan(_plan(_call(d=256), max_seqlen_q=64, max_seqlen_k=256)[1]).route == runtime.ROUTE_MMA
+    with pytest.raises(NotImplementedError):
+        runtime.plan(_plan(_call(d=256), max_seqlen_q=64, max_seqlen_k=256, route=runtime.ROUTE_UMMA)[1])
 
 
 def test_launcher_rejects_bad_blocks_before_any_launch():

@@ -29,6 +29,28 @@ def _no_device_timeouts():
     assert runtime.check_device_status("cuda") == 0, "a kernel's bounded wait expired"
 
 
+@pytest.fixture(params=["auto", "mma"])
+def route(request, monkeypatch):
+    """Run a test once with the launcher's own routing (tcgen05 kernel where eligible) and once pinned to the
+    mma.sync kernel."""
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime
+
+    if request.param == "mma":
+        monkeypatch.setattr(launch, "DEFAULT_ROUTE", runtime.ROUTE_MMA)
+    return request.param
+
+
+def _planned_route(case, **knobs):
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    out = torch.empty_like(case["q"])
+    params = runtime.build_params(case["q"], case["k"], case["v"], out, None, case["cu_seqlens_q"],
+                                  case.get("cu_seqlens_k"), case.get("seqused_k"), case.get("block_table"), None,
+                                  None, None, None, None, case["max_seqlen_q"], case["max_seqlen_k"],
+                                  case["softmax_scale"], 0.0, knobs.get("causal", True), -1, -1, 0, 0)
+    return runtime.plan(params).route
+
+
 def _golden_to_device(case):
     dev = {}
     for key, val in case.items():
@@ -92,7 +114,7 @@ def test_ragged_q_with_empty_requests():
     assert torch.all(out[-2:] == 0) and torch.all(torch.isneginf(lse[:, -2:]))
 
 
-def test_q_longer_than_kv():
+def test_q_longer_than_kv(route):
     """Bottom-right alignment when q_len > kv_len: leading rows see nothing."""
     case = T.make_case(64, [5, 70], [3, 20], hq=4, hkv=2)
     T.check(case)
@@ -100,19 +122,19 @@ def test_q_longer_than_kv():
 
 @pytest.mark.parametrize("d", [128, 256])
 @pytest.mark.parametrize("causal", [True, False])
-def test_prefill_paged(d, causal):
+def test_prefill_paged(d, causal, route):
     case = T.make_case(64, [200, 1, 333, 64], [200, 900, 500, 64], hq=8, hkv=2, d=d, std=0.6)
     T.check(case, causal=causal)
 
 
 @pytest.mark.parametrize("group", [1, 3, 8])
-def test_prefill_group_sizes(group):
+def test_prefill_group_sizes(group, route):
     """Row tiles that straddle query rows when the group does not divide the tile."""
     case = T.make_case(128, [130, 77], [130, 400], hq=2 * group, hkv=2, std=0.6)
     T.check(case)
 
 
-def test_prefill_packed_kv():
+def test_prefill_packed_kv(route):
     """Contiguous K/V packed by cu_seqlens_k (BASELINE config 1 shape: [128,256,384,512], 16/2 heads)."""
     from atrex import flash_attn_varlen_func
 
@@ -132,7 +154,7 @@ def test_prefill_packed_kv():
 
 
 @pytest.mark.parametrize("window", [(0, 0), (5, 0), (63, 0), (64, 0), (200, 0), (4095, 0), (10, 10), (-1, 7), (30, -1)])
-def test_sliding_window(window):
+def test_sliding_window(window, route):
     """Parity unpinned by the reference (it rejects windows on NVIDIA): the oracle defines the expected result."""
     case = T.make_case(64, [4, 1, 130, 2], [700, 300, 260, 5000], hq=8, hkv=2, std=0.6)
     causal = window[1] == 0
@@ -141,7 +163,7 @@ def test_sliding_window(window):
         T.check(case, causal=True, window_size=window, num_splits=4)
 
 
-def test_sinks_and_lse():
+def test_sinks_and_lse(route):
     """Per-head sink logits join the denominator un-scaled; split and unsplit paths agree with the oracle."""
     case = T.make_case(128, [4, 4, 1, 100], [3000, 129, 50, 228], hq=16, hkv=1)
     sink = (torch.randn(16, generator=torch.Generator().manual_seed(3))).bfloat16().cuda()
@@ -238,6 +260,38 @@ def test_poisoned_scratch_is_never_read():
     poison = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")
     del poison
     T.check(args, num_splits=16)
+
+
+def test_umma_route_is_taken_and_matches_mma_route():
+    """The launcher sends BF16 head_dim-128 prefill to the tcgen05 kernel; its result agrees with the mma.sync
+    kernel's on the same inputs (both are checked against the oracle elsewhere)."""
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime
+
+    case = T.make_case(64, [700, 33, 256, 1], [900, 33, 1000, 77], hq=16, hkv=2, std=0.6, poison_tail=True)
+    assert _planned_route(case) == runtime.ROUTE_UMMA
+    a, la = T.run(case)
+    launch.DEFAULT_ROUTE = runtime.ROUTE_MMA
+    try:
+        b, lb = T.run(case)
+    finally:
+        launch.DEFAULT_ROUTE = runtime.ROUTE_AUTO
+    torch.cuda.synchronize()
+    assert (a.float() - b.float()).abs().max().item() <= T.BF16_O_ATOL
+    assert torch.allclose(la, lb, rtol=1e-3, atol=1e-3)
+    eo, el = T.oracle_for(case)
+    T.compare(a, la, eo, el, T.to_numpy(case["cu_seqlens_q"]))
+
+
+@pytest.mark.parametrize("page,layout", [(16, "plain"), (32, "interleaved"), (64, "hnd"), (128, "strided"), (256, "plain")])
+def test_umma_prefill_page_sizes_and_layouts(page, layout):
+    case = T.make_case(page, [300, 129], [300, 1500], hq=8, hkv=1, layout=layout, std=0.6, poison_tail=True)
+    T.check(case)
+
+
+def test_umma_prefill_long_causal():
+    """Several row tiles per request and many KV tiles; oracle on the whole (small-head) case."""
+    case = T.make_case(64, [2048, 513], [2048, 3000], hq=4, hkv=1, std=0.5)
+    T.check(case)
 
 
 def test_baseline_decode_config_subsample():
