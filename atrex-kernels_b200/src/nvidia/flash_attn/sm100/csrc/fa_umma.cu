@@ -14,10 +14,11 @@
 //     shared memory, alternating between the two subtiles so that one subtile's
 //     softmax overlaps the other's matrix work;
 //   * warpgroups 0 and 1 (one thread per row) do the online softmax in the log2
-//     domain, write P as BF16 back into the S columns of TMEM, and accumulate the
-//     per-tile P V result from TMEM into FP32 registers with the running rescale, so
-//     no separate correction pass over a TMEM-resident O is needed;
-//   * TMEM: S0 | S1 | PV0 | PV1, 128 columns each (all 512).
+//     domain and write P as BF16 back into the S columns of TMEM; O accumulates in
+//     TMEM across KV tiles and is rescaled in place only when a row maximum grows by
+//     more than 2^8 (the lazy rescale of prefill_cutedsl.py:2589-2593), which after
+//     the first tiles is rare;
+//   * TMEM: S0 | S1 | O0 | O1, 128 columns each (all 512).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a code, drains its
 // copies, frees TMEM and returns.
@@ -42,7 +43,7 @@ constexpr int kOffQ = 0;
 constexpr int kOffKV = 2 * kTileBytes;
 constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
 // barriers (8 bytes each)
-enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kOEmpty = 16, kNumBars = 18 };
+enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kNumBars = 16 };
 constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (u32), abort flag (int)
 constexpr int kUmmaSmemBytes = kOffMisc + 16;
 
@@ -92,6 +93,53 @@ __device__ __forceinline__ bool decode_item(const FwdParams& p, int item, Item& 
     break;                                                        \
   }
 
+// Growth of the running row maximum (log2 units) below which the old maximum is kept: P then
+// reaches at most 2^8, harmless in BF16 / FP32, and the TMEM-resident O needs no rescale.
+constexpr float kRescaleThreshold = 8.f;
+
+// One 128-key tile for one row (= one thread): scores from TMEM, running max with the lazy-rescale
+// rule, P = 2^(s*scale - m) written back over the S columns as BF16 pairs, row sum folded into l.
+// Returns the factor the caller must apply to the O accumulated so far (1 when the max was kept).
+template <bool kMask>
+__device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
+                                              float& m_run, float& l_run) {
+  uint32_t s[kBN];
+#pragma unroll
+  for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+  tmem_ld_wait();
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kBN; ++i) {
+    if (kMask) {
+      const int col = tok0 + i;
+      if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
+    }
+    mx = fmaxf(mx, __uint_as_float(s[i]));
+  }
+  mx *= scale_log2;
+  float alpha = 1.f;
+  if (mx > m_run + kRescaleThreshold) {  // also the first finite maximum of the row
+    alpha = fast_exp2(m_run - mx);
+    m_run = mx;
+  }
+  const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < kBN / 32; ++c) {
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
+      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
+      sum += p0 + p1;
+      packed[i >> 1] = pack_bf16(p0, p1);
+    }
+    tmem_st16(s_tmem + c * 16, packed);
+  }
+  l_run = l_run * alpha + sum;
+  return alpha;
+}
+
 }  // namespace
 
 namespace {
@@ -125,7 +173,6 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       mbar_init(&bars[kSFull + w], 1);
       mbar_init(&bars[kPFull + w], kBM);
       mbar_init(&bars[kOFull + w], 1);
-      mbar_init(&bars[kOEmpty + w], kBM);
     }
     fence_barrier_init();
   }
@@ -228,7 +275,7 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       constexpr uint32_t kIdescPV = umma_idesc(kBM, kHD, 1, 1, 0, 1);
       const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
-      uint32_t it_count = 0, seq = 0, cp[2] = {0, 0}, co[2] = {0, 0};
+      uint32_t it_count = 0, seq = 0, cp[2] = {0, 0};
       bool dead = false;
       auto issue_qk = [&](int w, uint32_t slot) {
         if (lane == 0) {
@@ -281,15 +328,13 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
               for (int w = 0; w < 2; ++w) {
                 if (!mbar_wait(&bars[kPFull + w], cp[w] & 1u)) { dead = true; break; }
                 ++cp[w];
-                if (!mbar_wait(&bars[kOEmpty + w], (co[w] + 1) & 1u)) { dead = true; break; }
-                ++co[w];
                 tcgen05_fence_after();
                 if (lane == 0) {
 #pragma unroll
                   for (int ks = 0; ks < kBN / 16; ++ks)
                     umma_ts_f16(tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
                                 umma_desc_sw128(kv_addr + slot_v * kTileBytes + ks * 2048, kBlockBytes, 1024),
-                                kIdescPV, ks > 0);
+                                kIdescPV, (j > 0) | (ks > 0));
                   umma_commit(&bars[kOFull + w]);
                 }
                 if (more) issue_qk(w, slot_k2);
@@ -320,7 +365,7 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       __syncwarp();
     }
   } else {
-    // ============================ warpgroups 0 and 1: softmax + accumulate ============================
+    // ============================ warpgroups 0 and 1: softmax, O kept in TMEM ============================
     setmaxnreg_inc<200>();
     const int w = warp >> 2;                                   // subtile
     const int r = (warp & 3) * 32 + lane;                      // row inside the subtile = TMEM lane
@@ -347,122 +392,86 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       if (p.q_descale) dq = p.q_descale[it.b * p.q_descale_bs + it.kvh * p.q_descale_hs];
       if (p.k_descale) dk = p.k_descale[it.b * p.k_descale_bs + it.kvh * p.k_descale_hs];
       if (p.v_descale) dv = p.v_descale[it.b * p.v_descale_bs + it.kvh * p.v_descale_hs];
-      const float scale = p.softmax_scale * dq * dk;
-      const float scale_log2 = scale * kLog2e;
-      const float cap_in = p.softcap > 0.f ? scale / p.softcap : 0.f;
-      const float cap_out = p.softcap * kLog2e;
+      const float scale_log2 = p.softmax_scale * dq * dk * kLog2e;   // > 0 on this route
 
       float m_run = -INFINITY, l_run = 0.f;
-      float o_acc[kHD];
-#pragma unroll
-      for (int i = 0; i < kHD; ++i) o_acc[i] = 0.f;
-
       for (int j = 0; j < it.n_tiles; ++j) {
         const int tok0 = (it.tile_lo + j) * kBN;
         const bool need_mask = tok0 < full_lo || tok0 + kBN > full_hi;
         if (!mbar_wait(&bars[kSFull + w], cs & 1u)) { dead = true; break; }
         ++cs;
         tcgen05_fence_after();
-        // ---- pass 1: row maximum of the scaled, masked scores ----
-        float mx = -INFINITY;
+        const float alpha = need_mask ? softmax_tile<true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
+                                      : softmax_tile<false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+        if (j > 0) {
+          // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.
+          if (!mbar_wait(&bars[kOFull + w], co & 1u)) { dead = true; break; }
+          ++co;
+          tcgen05_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(s_tmem + c * 32, v);
-          tmem_ld_wait();
+            for (int c = 0; c < kHD / 32; ++c) {
+              uint32_t v[32];
+              tmem_ld32(o_tmem + c * 32, v);
+              tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(v[i]);
-            x = p.softcap > 0.f ? cap_out * fast_tanh(x * cap_in) : x * scale_log2;
-            if (need_mask) {
-              const int col = tok0 + c * 32 + i;
-              if (col < vis_lo || col >= vis_hi) x = -INFINITY;
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tmem_st32(o_tmem + c * 32, v);
             }
-            mx = fmaxf(mx, x);
           }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = fast_exp2(m_run - m_use);
-        m_run = m_new;
-        // ---- pass 2: P = 2^(s - m) as BF16 into the S columns, row sum ----
-        float sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(s_tmem + c * 32, v);
-          tmem_ld_wait();
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-            if (p.softcap > 0.f) {
-              x0 = cap_out * fast_tanh(x0 * cap_in) - m_use;
-              x1 = cap_out * fast_tanh(x1 * cap_in) - m_use;
-            } else {
-              x0 = fmaf(x0, scale_log2, -m_use);
-              x1 = fmaf(x1, scale_log2, -m_use);
-            }
-            if (need_mask) {
-              const int col = tok0 + c * 32 + i;
-              if (col < vis_lo || col >= vis_hi) x0 = -INFINITY;
-              if (col + 1 < vis_lo || col + 1 >= vis_hi) x1 = -INFINITY;
-            }
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            sum += p0 + p1;
-            packed[i >> 1] = pack_bf16(p0, p1);
-          }
-          tmem_st16(s_tmem + c * 16, packed);
-        }
-        l_run = l_run * alpha + sum;
         tmem_st_wait();
         tcgen05_fence_before();
         mbar_arrive(&bars[kPFull + w]);
-        // ---- accumulate this tile's P V (rescaling what came before) ----
-        if (!mbar_wait(&bars[kOFull + w], co & 1u)) { dead = true; break; }
+      }
+      if (!dead && it.n_tiles > 0) {
+        if (!mbar_wait(&bars[kOFull + w], co & 1u)) dead = true;
         ++co;
         tcgen05_fence_after();
-#pragma unroll
-        for (int c = 0; c < kHD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(o_tmem + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(v[i]));
-        }
-        tcgen05_fence_before();
-        mbar_arrive(&bars[kOEmpty + w]);
       }
       if (dead) {
         if (p.status) atomicExch(p.status, kWaitMmaTimeout);
         atomicExch(abort_flag, 1);
         break;
       }
-      // ---- epilogue: normalise, store BF16 row and natural-log LSE ----
-      if (row < it.rows_total) {
-        float sink_l2 = -INFINITY;
-        if (p.sink != nullptr) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
-        const float m_f = fmaxf(m_run, sink_l2);
-        const float m_use = m_f == -INFINITY ? 0.f : m_f;
-        const float resc = fast_exp2(m_run - m_use);
-        float l = l_run * resc;
-        if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use);
-        const float inv = l > 0.f ? dv * resc / l : 0.f;
-        const int64_t q_row = it.q_start + row / p.group;
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
-                             (int64_t)hd * p.out_head_stride;
+      // ---- epilogue: O from TMEM, normalise, store BF16 row and natural-log LSE ----
+      float sink_l2 = -INFINITY;
+      if (p.sink != nullptr && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
+      const float m_f = fmaxf(m_run, sink_l2);
+      const float m_use = m_f == -INFINITY ? 0.f : m_f;
+      const float resc = fast_exp2(m_run - m_use);
+      float l = l_run * resc;
+      if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use);
+      const float inv = (l > 0.f && it.n_tiles > 0) ? dv * resc / l : 0.f;
+      const int64_t q_row = it.q_start + row / p.group;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
+                           (int64_t)hd * p.out_head_stride;
 #pragma unroll
-        for (int i = 0; i < kHD; i += 8) {
-          uint4 pk;
-          pk.x = pack_bf16(o_acc[i] * inv, o_acc[i + 1] * inv);
-          pk.y = pack_bf16(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-          pk.z = pack_bf16(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-          pk.w = pack_bf16(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + i) = pk;
+      for (int c = 0; c < kHD / 32; ++c) {
+        uint32_t v[32];
+        if (it.n_tiles > 0) {           // warp-uniform
+          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
-        if (p.lse != nullptr)
-          p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l)) * kLn2 : -INFINITY;
+        if (row < it.rows_total) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+          }
+        }
       }
+      if (row < it.rows_total && p.lse != nullptr)
+        p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l)) * kLn2 : -INFINITY;
+      // the next item's first P V overwrites O only after this warp's next P arrival, i.e. after these loads
+      tcgen05_fence_before();
     }
   }
 

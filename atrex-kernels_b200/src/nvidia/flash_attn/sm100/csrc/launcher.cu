@@ -136,7 +136,7 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   // mma.sync row tile) whose GQA group divides its 128-row subtile; everything else, and every call
   // that asks for KV splits, runs on the mma.sync kernel.
   const bool umma_ok = umma_supports(p->head_dim, group, p->dtype == ATREX_FA_BF16) && p->softcap == 0.f &&
-                       p->q_head_stride <= p->q_row_stride;
+                       p->softmax_scale > 0.f && p->q_head_stride <= p->q_row_stride;
   if (p->route == ATREX_FA_ROUTE_UMMA && !umma_ok) return ATREX_FA_UNSUPPORTED;
   const bool use_umma = p->route == ATREX_FA_ROUTE_UMMA ||
                         (p->route == ATREX_FA_ROUTE_AUTO && umma_ok && packed_max > 64 && p->num_splits <= 1);
