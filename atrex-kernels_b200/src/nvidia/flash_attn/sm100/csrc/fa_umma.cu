@@ -86,12 +86,69 @@ __device__ __forceinline__ bool decode_item(const FwdParams& p, int item, Item& 
   return true;
 }
 
+#ifdef ATREX_UMMA_TRACE
+__device__ long long g_umma_trace[8192];
+#define TRACE(slot, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_umma_trace[(slot) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(slot, idx) do { } while (0)
+#endif
+
 #define UMMA_WAIT(bar_ptr, parity, code)                          \
   if (!mbar_wait((bar_ptr), (parity))) {                          \
     if (p.status) atomicExch(p.status, (code));                   \
     atomicExch(abort_flag, 1);                                    \
     break;                                                        \
   }
+
+// K or V tiles of one work item, issued by one thread.  NB = TMA boxes per 128-token tile.  The page
+// ids of tile j+1 are loaded before the wait for tile j's slot, so the table lookup is off the issue path.
+// Copy issue is the serial part of the pipeline and this thread competes for issue slots with two
+// softmax warps, so the loop is kept as short as it can be.  Returns false on a bounded-wait expiry.
+template <int NB>
+__device__ __forceinline__ bool produce_tiles(const FwdParams& p, const Item& it, int is_v, uint8_t* kv_smem,
+                                              uint64_t* bars, uint32_t& seq, int pshift) {
+  constexpr int kBoxRows = kBN / NB;
+  constexpr uint32_t kBoxBytes = kBoxRows * 128u;
+  const CUtensorMap* map = is_v ? &p.v_map : &p.k_map;
+  const int8_t(&perm)[3] = is_v ? p.v_perm : p.k_perm;
+  const int32_t* table = p.page_size ? p.block_table + (int64_t)it.b * p.block_table_row_stride : nullptr;
+  const int row_mask = p.page_size - 1;
+  auto page_id = [&](int tok) -> int {
+    if (table == nullptr) return 0;
+    if (tok >= it.kv_len) return -1;
+    const int pg = table[pshift >= 0 ? tok >> pshift : tok / p.page_size];
+    return (pg >= 0 && pg < p.num_pages) ? pg : -1;
+  };
+  int cur[NB], nxt[NB];
+  int tok0 = it.tile_lo * kBN;
+#pragma unroll
+  for (int x = 0; x < NB; ++x) cur[x] = page_id(tok0 + x * kBoxRows);
+  for (int j = 0; j < it.n_tiles; ++j, tok0 += kBN) {
+    if (j + 1 < it.n_tiles) {
+#pragma unroll
+      for (int x = 0; x < NB; ++x) nxt[x] = page_id(tok0 + kBN + x * kBoxRows);
+    }
+    const uint32_t slot = seq % kSlots;
+    if (seq >= (uint32_t)kSlots && !mbar_wait(&bars[kKVEmpty + slot], ((seq / kSlots) - 1) & 1u)) return false;
+    uint8_t* dst = kv_smem + slot * kTileBytes;
+    int live = 0;
+#pragma unroll
+    for (int x = 0; x < NB; ++x) live += (cur[x] >= 0 && tok0 + x * kBoxRows < it.kv_len) ? 1 : 0;
+    mbar_arrive_expect_tx(&bars[kKVFull + slot], (uint32_t)live * kBoxBytes * 2u);
+#pragma unroll
+    for (int x = 0; x < NB; ++x) {
+      const int tok = tok0 + x * kBoxRows;
+      if (cur[x] < 0 || tok >= it.kv_len) continue;
+      const int row = p.page_size ? (pshift >= 0 ? tok & row_mask : tok % p.page_size) : it.k_start + tok;
+      tma_load_kv(dst + x * kBoxBytes, map, &bars[kKVFull + slot], 0, it.kvh, row, cur[x], perm);
+      tma_load_kv(dst + kBlockBytes + x * kBoxBytes, map, &bars[kKVFull + slot], 64, it.kvh, row, cur[x], perm);
+    }
+#pragma unroll
+    for (int x = 0; x < NB; ++x) cur[x] = nxt[x];
+    seq += 2;
+  }
+  return true;
+}
 
 // Growth of the running row maximum (log2 units) below which the old maximum is kept: P then
 // reaches at most 2^8, harmless in BF16 / FP32, and the TMEM-resident O needs no rescale.
@@ -107,15 +164,21 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
 #pragma unroll
   for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
   tmem_ld_wait();
-  float mx = -INFINITY;
+  // Several independent chains: with two softmax warps per scheduler there is little thread-level
+  // parallelism to hide the latency of one long max / add dependency chain.
+  float mxv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) mxv[k] = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kBN; ++i) {
     if (kMask) {
       const int col = tok0 + i;
       if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
     }
-    mx = fmaxf(mx, __uint_as_float(s[i]));
+    mxv[i & 7] = fmaxf(mxv[i & 7], __uint_as_float(s[i]));
   }
+  float mx = fmaxf(fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3])),
+                   fmaxf(fmaxf(mxv[4], mxv[5]), fmaxf(mxv[6], mxv[7])));
   mx *= scale_log2;
   float alpha = 1.f;
   if (mx > m_run + kRescaleThreshold) {  // also the first finite maximum of the row
@@ -123,7 +186,7 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
     m_run = mx;
   }
   const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-  float sum = 0.f;
+  float sumv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int c = 0; c < kBN / 32; ++c) {
     uint32_t packed[16];
@@ -131,11 +194,12 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
     for (int i = 0; i < 32; i += 2) {
       const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
       const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
-      sum += p0 + p1;
+      sumv[(i >> 1) & 3] += p0 + p1;
       packed[i >> 1] = pack_bf16(p0, p1);
     }
     tmem_st16(s_tmem + c * 16, packed);
   }
+  const float sum = (sumv[0] + sumv[1]) + (sumv[2] + sumv[3]);
   l_run = l_run * alpha + sum;
   return alpha;
 }
@@ -190,81 +254,51 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
   if (warp >= 8) {
     // ============================ warpgroup 2: MMA issuer, TMA producer ============================
     setmaxnreg_dec<96>();
-    if (warp == 9) {
-      // ------------------------------- TMA producer -------------------------------
+    if (warp == 9 || warp == 10) {
+      // ------------------------------- TMA producers -------------------------------
+      // Warp 9 loads Q and the K tiles (ring slots 0 and 2), warp 10 the V tiles (slots 1 and 3); one
+      // thread of each issues everything.
       if (lane == 0) {
-        prefetch_tensormap(&p.q_map);
-        prefetch_tensormap(&p.k_map);
-        prefetch_tensormap(&p.v_map);
+        const int is_v = warp == 10;
+        if (!is_v) prefetch_tensormap(&p.q_map);
+        prefetch_tensormap(is_v ? &p.v_map : &p.k_map);
         const int boxes = kBN / p.box_rows;
-        const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
-        uint32_t it_count = 0, seq = 0;
+        const int pshift = (p.page_size > 0 && (p.page_size & (p.page_size - 1)) == 0) ? __ffs(p.page_size) - 1 : -1;
+        uint32_t it_count = 0, seq = (uint32_t)is_v;
         bool q_issued = false;
         for (int item = blockIdx.x;; item += n_items_step) {
           Item it;
           if (!decode_item(p, item, it)) break;
           if (*(volatile int*)abort_flag) break;
-          if (it_count > 0) UMMA_WAIT(&bars[kQEmpty], (it_count - 1) & 1u, kWaitEmptyTimeout)
-          mbar_arrive_expect_tx(&bars[kQFull], 2u * kTileBytes);
-          q_issued = true;
+          if (!is_v) {
+            if (it_count > 0) UMMA_WAIT(&bars[kQEmpty], (it_count - 1) & 1u, kWaitEmptyTimeout)
+            mbar_arrive_expect_tx(&bars[kQFull], 2u * kTileBytes);
+            q_issued = true;
 #pragma unroll
-          for (int w = 0; w < 2; ++w)
+            for (int w = 0; w < 2; ++w)
 #pragma unroll
-            for (int kb = 0; kb < 2; ++kb)
-              tma_load_3d(q_smem + w * kTileBytes + kb * kBlockBytes, &p.q_map, &bars[kQFull], kb * 64,
-                          it.kvh * p.group, it.q_start + (it.row0 + w * kBM) / p.group);
-          const int32_t* table = p.page_size ? p.block_table + (int64_t)it.b * p.block_table_row_stride : nullptr;
-          bool failed = false;
-          for (int j = 0; j < it.n_tiles && !failed; ++j) {
-            const int tok0 = (it.tile_lo + j) * kBN;
-            for (int is_v = 0; is_v < 2; ++is_v) {
-              const uint32_t slot = seq % kSlots;
-              if (seq >= (uint32_t)kSlots && !mbar_wait(&bars[kKVEmpty + slot], ((seq / kSlots) - 1) & 1u)) {
-                if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
-                atomicExch(abort_flag, 1);
-                failed = true;
-                break;
-              }
-              uint8_t* dst = kv_smem + slot * kTileBytes;
-              const CUtensorMap* map = is_v ? &p.v_map : &p.k_map;
-              const int8_t(&perm)[3] = is_v ? p.v_perm : p.k_perm;
-              // which boxes exist, so the byte count is posted before any copy can complete
-              uint32_t live_mask = 0;
-              int live = 0;
-              for (int x = 0; x < boxes; ++x) {
-                const int tok = tok0 + x * p.box_rows;
-                if (tok >= it.kv_len) break;
-                if (p.page_size) {
-                  const int pg = table[tok / p.page_size];
-                  if (pg < 0 || pg >= p.num_pages) continue;
-                }
-                live_mask |= 1u << x;
-                ++live;
-              }
-              mbar_arrive_expect_tx(&bars[kKVFull + slot], (uint32_t)live * box_bytes * 2u);
-              for (int x = 0; x < boxes; ++x) {
-                if (!(live_mask >> x & 1u)) continue;
-                const int tok = tok0 + x * p.box_rows;
-                int pg = 0, row = it.k_start + tok;
-                if (p.page_size) {
-                  pg = table[tok / p.page_size];
-                  row = tok % p.page_size;
-                }
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb)
-                  tma_load_kv(dst + kb * kBlockBytes + x * box_bytes, map, &bars[kKVFull + slot], kb * 64, it.kvh, row,
-                              pg, perm);
-              }
-              ++seq;
-            }
+              for (int kb = 0; kb < 2; ++kb)
+                tma_load_3d(q_smem + w * kTileBytes + kb * kBlockBytes, &p.q_map, &bars[kQFull], kb * 64,
+                            it.kvh * p.group, it.q_start + (it.row0 + w * kBM) / p.group);
           }
-          if (failed) break;
+          bool ok;
+          switch (boxes) {
+            case 1: ok = produce_tiles<1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+            case 2: ok = produce_tiles<2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+            case 4: ok = produce_tiles<4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+            default: ok = produce_tiles<8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          }
+          if (!ok) {
+            if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
+            atomicExch(abort_flag, 1);
+            break;
+          }
           ++it_count;
         }
         // Drain: every copy this thread issued must have landed before the CTA may exit.
         if (q_issued) mbar_wait(&bars[kQFull], (it_count > 0 ? it_count - 1 : 0) & 1u);
-        for (uint32_t back = 1; back <= (uint32_t)kSlots && back <= seq; ++back) {
-          const uint32_t n = seq - back;
+        for (uint32_t back = 2; back <= (uint32_t)kSlots && back <= seq; back += 2) {
+          const uint32_t n = seq - back;   // this thread's last two tiles
           mbar_wait(&bars[kKVFull + n % kSlots], (n / kSlots) & 1u);
         }
       }
@@ -277,13 +311,18 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       const uint32_t kv_addr = smem_u32(kv_smem);
       uint32_t it_count = 0, seq = 0, cp[2] = {0, 0};
       bool dead = false;
+      // Descriptors are built once; per instruction only the start-address field (bytes >> 4) moves.
+      const uint64_t q_desc0 = umma_desc_sw128(q_addr, 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(kv_addr, 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(kv_addr, kBlockBytes, 1024);
       auto issue_qk = [&](int w, uint32_t slot) {
         if (lane == 0) {
+          const uint64_t qd = q_desc0 + (uint64_t)((w * kTileBytes) >> 4);
+          const uint64_t kd = k_desc0 + (uint64_t)((slot * kTileBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < kHD / 16; ++ks) {
-            const uint32_t koff = (ks >> 2) * kBlockBytes + (ks & 3) * 32;
-            umma_ss_f16(tmem_base + w * kBN, umma_desc_sw128(q_addr + w * kTileBytes + koff, 16, 1024),
-                        umma_desc_sw128(kv_addr + slot * kTileBytes + koff, 16, 1024), kIdescQK, ks > 0);
+            const uint32_t koff = ((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4;
+            umma_ss_f16(tmem_base + w * kBN, qd + koff, kd + koff, kIdescQK, ks > 0);
           }
           umma_commit(&bars[kSFull + w]);
         }
@@ -305,8 +344,10 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
             for (int j = 0; j < it.n_tiles && !dead; ++j) {
               const bool more = j + 1 < it.n_tiles;
               const uint32_t slot_v = seq % kSlots;
+              if (lane == 0) TRACE(12, cp[0]);
               if (!mbar_wait(&bars[kKVFull + slot_v], (seq / kSlots) & 1u)) { dead = true; break; }
               ++seq;
+              if (lane == 0) TRACE(13, cp[0]);
               // V rows past the end of the request may hold NaN: P is 0 there but 0 * NaN is NaN.
               const int tok0 = (it.tile_lo + j) * kBN;
               if (tok0 + kBN > it.kv_len) {
@@ -324,25 +365,29 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
                 slot_k2 = seq % kSlots;
                 if (!mbar_wait(&bars[kKVFull + slot_k2], (seq / kSlots) & 1u)) { dead = true; break; }
                 ++seq;
+                if (lane == 0) TRACE(14, cp[0]);
               }
               for (int w = 0; w < 2; ++w) {
                 if (!mbar_wait(&bars[kPFull + w], cp[w] & 1u)) { dead = true; break; }
+                if (lane == 0) TRACE(8 + 2 * w, cp[w]);
                 ++cp[w];
                 tcgen05_fence_after();
                 if (lane == 0) {
 #pragma unroll
                   for (int ks = 0; ks < kBN / 16; ++ks)
                     umma_ts_f16(tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
-                                umma_desc_sw128(kv_addr + slot_v * kTileBytes + ks * 2048, kBlockBytes, 1024),
-                                kIdescPV, (j > 0) | (ks > 0));
+                                v_desc0 + (uint64_t)((slot_v * kTileBytes + ks * 2048) >> 4), kIdescPV,
+                                (j > 0) | (ks > 0));
                   umma_commit(&bars[kOFull + w]);
                 }
                 if (more) issue_qk(w, slot_k2);
+                if (lane == 0) TRACE(9 + 2 * w, cp[w] - 1);
               }
               if (dead) break;
               if (lane == 0) {
                 umma_commit(&bars[kKVEmpty + slot_v]);
                 if (more) umma_commit(&bars[kKVEmpty + slot_k2]);
+                TRACE(18, cp[0] - 1);
               }
             }
             if (!dead && lane == 0) umma_commit(&bars[kQEmpty]);
@@ -401,6 +446,8 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
         if (!mbar_wait(&bars[kSFull + w], cs & 1u)) { dead = true; break; }
         ++cs;
         tcgen05_fence_after();
+        if (tid == 0) TRACE(0, cs - 1);
+        if (tid == 128) TRACE(4, cs - 1);
         const float alpha = need_mask ? softmax_tile<true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
                                       : softmax_tile<false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
         if (j > 0) {
@@ -420,9 +467,13 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
             }
           }
         }
+        if (tid == 0) TRACE(1, cs - 1);
         tmem_st_wait();
+        if (tid == 0) TRACE(2, cs - 1);
         tcgen05_fence_before();
         mbar_arrive(&bars[kPFull + w]);
+        if (tid == 0) TRACE(3, cs - 1);
+        if (tid == 128) TRACE(7, cs - 1);
       }
       if (!dead && it.n_tiles > 0) {
         if (!mbar_wait(&bars[kOFull + w], co & 1u)) dead = true;
@@ -491,6 +542,12 @@ bool umma_supports(int head_dim, int group, int dtype_is_bf16) {
 }
 
 int umma_rows_per_item() { return kRowsPerItem; }
+
+#ifdef ATREX_UMMA_TRACE
+extern "C" __attribute__((visibility("default"))) int atrex_fa_sm100_debug_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_umma_trace, sizeof(long long) * n);
+}
+#endif
 
 cudaError_t umma_prepare() {
   return cudaFuncSetAttribute(atrex_sm100_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -326,7 +326,8 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   const bool paged = p->page_size > 0;
   const int64_t rows = paged ? p->page_size : p->total_k;
   const int64_t pages = paged ? p->num_pages : 1;
-  const int kTileN = mma_tile_n(p->head_dim);
+  // rows one TMA box covers: a whole KV tile of the chosen kernel, or a page if pages are smaller
+  const int kTileN = r.route == ATREX_FA_ROUTE_UMMA ? 128 : mma_tile_n(p->head_dim);
   const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
   const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
   int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};

@@ -60,7 +60,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+    if (i > 4096) __nanosleep(64);
   }
   return false;
 }
@@ -78,11 +78,11 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tensor_m
 // ascending-stride ordering of the tensor map put them.
 __device__ __forceinline__ void tma_load_kv(void* smem_dst, const void* tensor_map, uint64_t* bar, int d0,
                                             int head, int row, int page, const int8_t (&perm)[3]) {
-  int c[3];
-  c[perm[0]] = head;
-  c[perm[1]] = row;
-  c[perm[2]] = page;
-  tma_load_4d(smem_dst, tensor_map, bar, d0, c[0], c[1], c[2]);
+  // selects instead of an indexed array: keeps the coordinates in registers
+  const int c0 = perm[0] == 0 ? head : (perm[1] == 0 ? row : page);
+  const int c1 = perm[0] == 1 ? head : (perm[1] == 1 ? row : page);
+  const int c2 = perm[0] == 2 ? head : (perm[1] == 2 ? row : page);
+  tma_load_4d(smem_dst, tensor_map, bar, d0, c0, c1, c2);
 }
 __device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
