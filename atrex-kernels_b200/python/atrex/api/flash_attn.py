@@ -22,8 +22,8 @@ from atrex.utils.device_target import detect_device_target
 _TARGET_FA_VERSIONS = {("nvidia", "sm100"): frozenset({4})}
 
 _HEAD_DIMS = (128, 256)
-# E4M3 needs the tcgen05 route (the mma.sync route is BF16 only); flipped when that route serves FP8.
-_FP8_ROUTE_BUILT = False
+# E4M3 runs on the head_dim-256 tcgen05 kernel only (the mma.sync kernels are BF16).
+_FP8_ROUTE_BUILT = True
 _MAX_SPLITS = 256
 
 # (argument, value that means "not used", message) for vLLM arguments that no
@@ -128,8 +128,21 @@ def _validate_sm100_call(call, torch, batch, window, softcap):
         raise NotImplementedError("Atrex sm100 attention indexes rows and pages with 32 bits")
     if block_table is None and call["cu_seqlens_k"] is None:
         raise NotImplementedError("Atrex sm100 packed K/V requires cu_seqlens_k")
-    if q.dtype == torch.float8_e4m3fn and not _FP8_ROUTE_BUILT:
-        raise NotImplementedError("Atrex sm100 attention does not serve float8_e4m3fn yet (BF16 only)")
+    if q.dtype == torch.float8_e4m3fn:
+        if not _FP8_ROUTE_BUILT:
+            raise NotImplementedError("Atrex sm100 attention does not serve float8_e4m3fn yet (BF16 only)")
+        group = q.shape[-2] // k.shape[-2]
+        if q.shape[-1] != 256:
+            raise NotImplementedError("Atrex sm100 float8_e4m3fn attention requires head_dim 256")
+        if 128 % group:
+            raise NotImplementedError(
+                "Atrex sm100 float8_e4m3fn attention requires a GQA group (num_q_heads / num_kv_heads) dividing 128"
+            )
+        if softcap:
+            raise NotImplementedError("Atrex sm100 float8_e4m3fn attention does not support softcap")
+        scale = call["softmax_scale"]
+        if scale is not None and scale <= 0:
+            raise NotImplementedError("Atrex sm100 float8_e4m3fn attention requires a positive softmax_scale")
 
 
 def _validate_flash_attn_call(call):

@@ -1,0 +1,540 @@
+// Head-dimension-256 prefill on tcgen05 tensor cores: BF16 and FP8 E4M3 inputs, BF16 output.
+//
+// This is the shape the reference's Blackwell prefill serves
+// (src/nvidia/flash_attn/sm103/prefill_cutedsl.py:146-4331: HD256, BF16 tile_n 64 / FP8 tile_n 128,
+// S ping-pong + O = all 512 TMEM columns, prefill_cutedsl.py:395-405), built single-CTA for B200:
+//
+//   * one work item = 128 packed GQA rows of one (request, KV head); the accumulator O takes 256
+//     TMEM columns, so there is one row tile per CTA and S is double-buffered instead:
+//     TMEM = S0 | S1 | O (tile_n + tile_n + 256 columns);
+//   * warp 4 issues QK^T for tile j+1 into the other S buffer while the softmax warpgroup works
+//     on tile j, then P V for tile j as soon as its P is in TMEM, so the matrix work of one tile
+//     hides behind the softmax of the next;
+//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles
+//     (128 keys x 256 B for FP8, 64 keys x 512 B for BF16), no multicast;
+//   * FP8: scores carry q_descale * k_descale inside the softmax scale, P is written as E4M3
+//     shifted up by 2^4 with a lazy-rescale threshold of 2^4 (P <= 256 < 448, the scheme of
+//     prefill_cutedsl.py:2577-2593), V stays MN-major E4M3 in shared memory, O is multiplied by
+//     v_descale in the epilogue.
+#include <cuda_fp8.h>
+
+#include "fa_kernels.cuh"
+#include "umma.cuh"
+
+namespace atrex_sm100 {
+
+namespace {
+
+constexpr int kRows = 128;          // packed rows per work item (UMMA M)
+constexpr int kD = 256;             // head dimension
+constexpr int kRing = 4;            // K/V ring slots of 32 KB
+constexpr int kSlotBytes = 32768;
+constexpr int kThreads256 = 256;
+constexpr uint32_t kTmemCols256 = 512;
+
+template <bool kFp8>
+struct Cfg256 {
+  static constexpr int kEsz = kFp8 ? 1 : 2;
+  static constexpr int kBN = kFp8 ? 128 : 64;                 // keys per tile
+  static constexpr int kNKB = kD * kEsz / 128;                // 128-byte column blocks per row
+  static constexpr int kQBytes = kRows * kD * kEsz;           // 32 KB / 64 KB
+  static constexpr int kQBlock = kRows * 128;                 // bytes of one Q column block
+  static constexpr int kKVBlock = kBN * 128;                  // bytes of one K/V column block
+  static constexpr int kKStepsQK = kNKB * 4;                  // 32 bytes of the head dimension per UMMA
+  static constexpr int kKStepsPV = 4;                         // 32 bytes of P per row per UMMA
+  static constexpr int kPVStepBytes = (32 / kEsz) * 128;      // V rows consumed per UMMA x 128 B
+  static constexpr float kThreshold = kFp8 ? 4.f : 8.f;       // lazy-rescale threshold (log2 units)
+  static constexpr float kShift = kFp8 ? 4.f : 0.f;           // P is stored as 2^shift * p
+  static constexpr int kOffKV = kQBytes;
+  static constexpr int kOffBar = kOffKV + kRing * kSlotBytes;
+  static constexpr int kSmemBytes = kOffBar + 24 * 8 + 16;
+  static constexpr uint32_t kFmt = kFp8 ? 0u : 1u;            // E4M3 (f8f6f4) / BF16 (f16)
+};
+
+enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
+
+struct Item256 {
+  int b, kvh, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
+};
+
+template <int BN>
+__device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Item256& it) {
+  const int total_tiles = p.tile_prefix[p.batch];
+  const int tile_rank = item / p.num_kv_heads;
+  if (tile_rank >= total_tiles) return false;
+  it.kvh = item % p.num_kv_heads;
+  int lo = 0, hi = p.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.tile_prefix[mid] <= tile_rank) lo = mid; else hi = mid;
+  }
+  it.b = p.order[lo];
+  const int tiles_b = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
+  it.row0 = (tiles_b - 1 - (tile_rank - p.tile_prefix[lo])) * kRows;   // heaviest causal row tile first
+  it.q_start = p.cu_seqlens_q[it.b];
+  it.q_len = p.cu_seqlens_q[it.b + 1] - it.q_start;
+  it.rows_total = it.q_len * p.group;
+  request_kv(p, it.b, it.kv_len, it.k_start);
+  it.off = it.kv_len - it.q_len;
+  const int qi_lo = it.row0 / p.group;
+  const int qi_hi = min(it.q_len - 1, (it.row0 + kRows - 1) / p.group);
+  int kv_end = it.kv_len, kv_begin = 0;
+  if (p.window_right >= 0) kv_end = min(it.kv_len, qi_hi + it.off + p.window_right + 1);
+  if (p.window_left >= 0) kv_begin = max(0, qi_lo + it.off - p.window_left);
+  it.tile_lo = 0;
+  it.n_tiles = 0;
+  if (kv_end > kv_begin) {
+    it.tile_lo = kv_begin / BN;
+    it.n_tiles = (kv_end + BN - 1) / BN - it.tile_lo;
+  }
+  return true;
+}
+
+// K or V tiles of one item, issued by one thread; NB boxes of (BN / NB) rows per tile, each box one
+// copy per 128-byte column block.  Page ids of tile j+1 are fetched before the wait for tile j's slot.
+template <bool kFp8, int NB>
+__device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item256& it, int is_v, uint8_t* kv_smem,
+                                                 uint64_t* bars, uint32_t& seq, int pshift) {
+  using C = Cfg256<kFp8>;
+  constexpr int kBoxRows = C::kBN / NB;
+  constexpr uint32_t kBoxBytes = kBoxRows * 128u;
+  constexpr int kInner = 128 / C::kEsz;   // elements per 128-byte block
+  const CUtensorMap* map = is_v ? &p.v_map : &p.k_map;
+  const int8_t(&perm)[3] = is_v ? p.v_perm : p.k_perm;
+  const int32_t* table = p.page_size ? p.block_table + (int64_t)it.b * p.block_table_row_stride : nullptr;
+  const int row_mask = p.page_size - 1;
+  auto page_id = [&](int tok) -> int {
+    if (table == nullptr) return 0;
+    if (tok >= it.kv_len) return -1;
+    const int pg = table[pshift >= 0 ? tok >> pshift : tok / p.page_size];
+    return (pg >= 0 && pg < p.num_pages) ? pg : -1;
+  };
+  int cur[NB], nxt[NB];
+  int tok0 = it.tile_lo * C::kBN;
+#pragma unroll
+  for (int x = 0; x < NB; ++x) cur[x] = page_id(tok0 + x * kBoxRows);
+  for (int j = 0; j < it.n_tiles; ++j, tok0 += C::kBN) {
+    if (j + 1 < it.n_tiles) {
+#pragma unroll
+      for (int x = 0; x < NB; ++x) nxt[x] = page_id(tok0 + C::kBN + x * kBoxRows);
+    }
+    const uint32_t slot = seq % kRing;
+    if (seq >= (uint32_t)kRing && !mbar_wait(&bars[bKVEmpty + slot], ((seq / kRing) - 1) & 1u)) return false;
+    uint8_t* dst = kv_smem + slot * kSlotBytes;
+    int live = 0;
+#pragma unroll
+    for (int x = 0; x < NB; ++x) live += (cur[x] >= 0 && tok0 + x * kBoxRows < it.kv_len) ? 1 : 0;
+    mbar_arrive_expect_tx(&bars[bKVFull + slot], (uint32_t)live * kBoxBytes * C::kNKB);
+#pragma unroll
+    for (int x = 0; x < NB; ++x) {
+      const int tok = tok0 + x * kBoxRows;
+      if (cur[x] < 0 || tok >= it.kv_len) continue;
+      const int row = p.page_size ? (pshift >= 0 ? tok & row_mask : tok % p.page_size) : it.k_start + tok;
+#pragma unroll
+      for (int kb = 0; kb < C::kNKB; ++kb)
+        tma_load_kv(dst + kb * C::kKVBlock + x * kBoxBytes, map, &bars[bKVFull + slot], kb * kInner, it.kvh, row,
+                    cur[x], perm);
+    }
+#pragma unroll
+    for (int x = 0; x < NB; ++x) cur[x] = nxt[x];
+    seq += 2;
+  }
+  return true;
+}
+
+// One tile of keys for one row (= one thread).  Same lazy-rescale rule as the head_dim-128 kernel; P is
+// written over the first columns of the S buffer it came from (BF16 pairs, or four E4M3 per column).
+// l_run and P are in units of 2^kShift.
+template <bool kFp8, bool kMask>
+__device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
+                                                 float& m_run, float& l_run) {
+  using C = Cfg256<kFp8>;
+  uint32_t s[C::kBN];
+#pragma unroll
+  for (int c = 0; c < C::kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+  tmem_ld_wait();
+  float mxv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) mxv[k] = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < C::kBN; ++i) {
+    if (kMask) {
+      const int col = tok0 + i;
+      if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
+    }
+    mxv[i & 7] = fmaxf(mxv[i & 7], __uint_as_float(s[i]));
+  }
+  float mx = fmaxf(fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3])),
+                   fmaxf(fmaxf(mxv[4], mxv[5]), fmaxf(mxv[6], mxv[7])));
+  mx *= scale_log2;
+  float alpha = 1.f;
+  if (mx > m_run + C::kThreshold) {  // also the first finite maximum of the row
+    alpha = fast_exp2(m_run - mx);
+    m_run = mx;
+  }
+  const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + C::kShift;
+  float sumv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < C::kBN / 32; ++c) {
+    if constexpr (kFp8) {
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 2]), scale_log2, neg_m));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 3]), scale_log2, neg_m));
+        sumv[(i >> 2) & 3] += (p0 + p1) + (p2 + p3);
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(p2, p3), __NV_SATFINITE, __NV_E4M3);
+        packed[i >> 2] = lo | (hi << 16);
+      }
+      tmem_st8(s_tmem + c * 8, packed);
+    } else {
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
+        sumv[(i >> 1) & 3] += p0 + p1;
+        packed[i >> 1] = pack_bf16(p0, p1);
+      }
+      tmem_st16(s_tmem + c * 16, packed);
+    }
+  }
+  l_run = l_run * alpha + ((sumv[0] + sumv[1]) + (sumv[2] + sumv[3]));
+  return alpha;
+}
+
+#define WAIT256(bar_ptr, parity, code)                            \
+  if (!mbar_wait((bar_ptr), (parity))) {                          \
+    if (p.status) atomicExch(p.status, (code));                   \
+    atomicExch(abort_flag, 1);                                    \
+    break;                                                        \
+  }
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreads256, 1)
+atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
+  using C = Cfg256<kFp8>;
+  constexpr int BN = C::kBN;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = smem + C::kOffKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  int* abort_flag = reinterpret_cast<int*>(bars + 21);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (tid == 0 && p.status) atomicExch(p.status, kBadSmemAlignment);
+    return;
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(&bars[bQFull], 1);
+    mbar_init(&bars[bQEmpty], 1);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(&bars[bKVFull + s], 1);
+      mbar_init(&bars[bKVEmpty + s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars[bSFull + b], 1);
+      mbar_init(&bars[bPFull + b], kRows);
+    }
+    mbar_init(&bars[bOFull], 1);
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, kTmemCols256);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t o_col = 2 * BN;
+  const int step = gridDim.x;
+
+  if (warp == 5 || warp == 6) {
+    // ------------------------------- TMA producers: K (+Q) and V -------------------------------
+    if (lane == 0) {
+      const int is_v = warp == 6;
+      if (!is_v) prefetch_tensormap(&p.q_map);
+      prefetch_tensormap(is_v ? &p.v_map : &p.k_map);
+      const int boxes = BN / p.box_rows;
+      const int pshift = (p.page_size > 0 && (p.page_size & (p.page_size - 1)) == 0) ? __ffs(p.page_size) - 1 : -1;
+      constexpr int kInner = 128 / C::kEsz;
+      uint32_t it_count = 0, seq = (uint32_t)is_v;
+      bool q_issued = false;
+      for (int item = blockIdx.x;; item += step) {
+        Item256 it;
+        if (!decode_item256<BN>(p, item, it)) break;
+        if (*(volatile int*)abort_flag) break;
+        if (!is_v) {
+          if (it_count > 0) WAIT256(&bars[bQEmpty], (it_count - 1) & 1u, kWaitEmptyTimeout)
+          mbar_arrive_expect_tx(&bars[bQFull], (uint32_t)C::kQBytes);
+          q_issued = true;
+#pragma unroll
+          for (int kb = 0; kb < C::kNKB; ++kb)
+            tma_load_3d(q_smem + kb * C::kQBlock, &p.q_map, &bars[bQFull], kb * kInner, it.kvh * p.group,
+                        it.q_start + it.row0 / p.group);
+        }
+        bool ok;
+        switch (boxes) {
+          case 1: ok = produce_tiles256<kFp8, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 2: ok = produce_tiles256<kFp8, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 4: ok = produce_tiles256<kFp8, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          default: ok = produce_tiles256<kFp8, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+        }
+        if (!ok) {
+          if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
+          atomicExch(abort_flag, 1);
+          break;
+        }
+        ++it_count;
+      }
+      if (q_issued) mbar_wait(&bars[bQFull], (it_count > 0 ? it_count - 1 : 0) & 1u);
+      for (uint32_t back = 2; back <= (uint32_t)kRing && back <= seq; back += 2) {
+        const uint32_t n = seq - back;
+        mbar_wait(&bars[bKVFull + n % kRing], (n / kRing) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // ------------------------------- MMA issuer -------------------------------
+    constexpr uint32_t kIdescQK = umma_idesc(kRows, BN, C::kFmt, C::kFmt, 0, 0);
+    constexpr uint32_t kIdescPV = umma_idesc(kRows, kD, C::kFmt, C::kFmt, 0, 1);
+    const uint64_t q_desc0 = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
+    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_smem), 16, 1024);
+    const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_smem), C::kKVBlock, 1024);
+    // ring numbering: tile t of the CTA's whole run has K number 2t and V number 2t + 1
+    uint32_t it_count = 0, base = 0, cp[2] = {0, 0};
+    bool dead = false;
+    auto issue_qk = [&](int buf, uint32_t slot) {
+      if (lane == 0) {
+        const uint64_t kd = k_desc0 + (uint64_t)((slot * kSlotBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < C::kKStepsQK; ++ks) {
+          const uint32_t qoff = ((ks >> 2) * C::kQBlock + (ks & 3) * 32) >> 4;
+          const uint32_t koff = ((ks >> 2) * C::kKVBlock + (ks & 3) * 32) >> 4;
+          if constexpr (kFp8) umma_ss_f8(tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
+          else umma_ss_f16(tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
+        }
+        umma_commit(&bars[bSFull + buf]);
+        umma_commit(&bars[bKVEmpty + slot]);
+      }
+    };
+    for (int item = blockIdx.x; !dead; item += step) {
+      Item256 it;
+      if (!decode_item256<BN>(p, item, it)) break;
+      if (*(volatile int*)abort_flag) break;
+      if (!mbar_wait(&bars[bQFull], it_count & 1u)) { dead = true; break; }
+      if (it.n_tiles == 0) {
+        if (lane == 0) mbar_arrive(&bars[bQEmpty]);
+        ++it_count;
+        continue;
+      }
+      {
+        const uint32_t slot_k = base % kRing;   // K(0)
+        if (!mbar_wait(&bars[bKVFull + slot_k], (base / kRing) & 1u)) { dead = true; break; }
+        tcgen05_fence_after();
+        issue_qk(0, slot_k);
+      }
+      for (int j = 0; j < it.n_tiles && !dead; ++j) {
+        const uint32_t n_v = base + 2 * j + 1;   // V(j)
+        if (j + 1 < it.n_tiles) {
+          const uint32_t n_k = base + 2 * j + 2; // K(j+1)
+          const uint32_t slot_k = n_k % kRing;
+          if (!mbar_wait(&bars[bKVFull + slot_k], (n_k / kRing) & 1u)) { dead = true; break; }
+          tcgen05_fence_after();
+          issue_qk((j + 1) & 1, slot_k);         // its S buffer held P(j-1), consumed by the earlier P V
+        }
+        const uint32_t slot_v = n_v % kRing;
+        if (!mbar_wait(&bars[bKVFull + slot_v], (n_v / kRing) & 1u)) { dead = true; break; }
+        const int tok0 = (it.tile_lo + j) * BN;
+        if (tok0 + BN > it.kv_len) {
+          // V rows past the end of the request may hold NaN: P is 0 there but 0 * NaN is NaN.
+          const int first = max(0, it.kv_len - tok0);
+          uint8_t* v_ptr = kv_smem + slot_v * kSlotBytes;
+          constexpr int kChunks = C::kNKB * 8;   // 16-byte chunks per row
+          for (int idx = lane; idx < (BN - first) * kChunks; idx += 32) {
+            const int r = first + idx / kChunks, c = idx % kChunks;
+            *reinterpret_cast<uint4*>(v_ptr + (c / 8) * C::kKVBlock + swz128(r, c % 8)) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async();
+          __syncwarp();
+        }
+        const int buf = j & 1;
+        if (!mbar_wait(&bars[bPFull + buf], cp[buf] & 1u)) { dead = true; break; }
+        ++cp[buf];
+        tcgen05_fence_after();
+        if (lane == 0) {
+          const uint64_t vd = v_desc0 + (uint64_t)((slot_v * kSlotBytes) >> 4);
+#pragma unroll
+          for (int ks = 0; ks < C::kKStepsPV; ++ks) {
+            const uint32_t voff = (ks * C::kPVStepBytes) >> 4;
+            if constexpr (kFp8)
+              umma_ts_f8(tmem_base + o_col, tmem_base + buf * BN + ks * 8, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+            else
+              umma_ts_f16(tmem_base + o_col, tmem_base + buf * BN + ks * 8, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+          }
+          umma_commit(&bars[bOFull]);
+          umma_commit(&bars[bKVEmpty + slot_v]);
+        }
+      }
+      if (dead) break;
+      if (lane == 0) umma_commit(&bars[bQEmpty]);
+      base += 2u * (uint32_t)it.n_tiles;
+      ++it_count;
+    }
+    if (dead && lane == 0) {
+      if (p.status) atomicExch(p.status, kWaitMmaTimeout);
+      atomicExch(abort_flag, 1);
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ------------------------------- softmax warpgroup -------------------------------
+    const int r = warp * 32 + lane;                       // row = TMEM lane
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_off + o_col;
+    uint32_t cs[2] = {0, 0}, co = 0;
+    bool dead = false;
+    for (int item = blockIdx.x; !dead; item += step) {
+      Item256 it;
+      if (!decode_item256<BN>(p, item, it)) break;
+      if (*(volatile int*)abort_flag) break;
+      const int row = it.row0 + r;
+      const int qi = min(row / p.group, max(it.q_len - 1, 0));
+      const int hd = it.kvh * p.group + row % p.group;
+      const int vis_hi = p.window_right >= 0 ? min(it.kv_len, qi + it.off + p.window_right + 1) : it.kv_len;
+      const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
+      const int sqi_lo = it.row0 / p.group;
+      const int sqi_hi = min(it.q_len - 1, (it.row0 + kRows - 1) / p.group);
+      const int full_lo = p.window_left >= 0 ? max(0, sqi_hi + it.off - p.window_left) : 0;
+      const int full_hi = p.window_right >= 0 ? min(it.kv_len, sqi_lo + it.off + p.window_right + 1) : it.kv_len;
+      float dq = 1.f, dk = 1.f, dv = 1.f;
+      if (p.q_descale) dq = p.q_descale[it.b * p.q_descale_bs + it.kvh * p.q_descale_hs];
+      if (p.k_descale) dk = p.k_descale[it.b * p.k_descale_bs + it.kvh * p.k_descale_hs];
+      if (p.v_descale) dv = p.v_descale[it.b * p.v_descale_bs + it.kvh * p.v_descale_hs];
+      const float scale_log2 = p.softmax_scale * dq * dk * kLog2e;   // > 0 on this route
+
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < it.n_tiles; ++j) {
+        const int buf = j & 1;
+        const uint32_t s_tmem = tmem_base + lane_off + buf * BN;
+        const int tok0 = (it.tile_lo + j) * BN;
+        const bool need_mask = tok0 < full_lo || tok0 + BN > full_hi;
+        if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) { dead = true; break; }
+        ++cs[buf];
+        tcgen05_fence_after();
+        const float alpha =
+            need_mask ? softmax_tile256<kFp8, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
+                      : softmax_tile256<kFp8, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+        if (j > 0) {
+          if (!mbar_wait(&bars[bOFull], co & 1u)) { dead = true; break; }
+          ++co;
+          tcgen05_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < kD / 32; ++c) {
+              uint32_t v[32];
+              tmem_ld32(o_tmem + c * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tmem_st32(o_tmem + c * 32, v);
+            }
+          }
+        }
+        tmem_st_wait();
+        tcgen05_fence_before();
+        mbar_arrive(&bars[bPFull + buf]);
+      }
+      if (!dead && it.n_tiles > 0) {
+        if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;
+        ++co;
+        tcgen05_fence_after();
+      }
+      if (dead) {
+        if (p.status) atomicExch(p.status, kWaitMmaTimeout);
+        atomicExch(abort_flag, 1);
+        break;
+      }
+      // ---- epilogue ----
+      float sink_l2 = -INFINITY;
+      if (p.sink != nullptr && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
+      const float m_f = fmaxf(m_run, sink_l2);
+      const float m_use = m_f == -INFINITY ? 0.f : m_f;
+      const float resc = fast_exp2(m_run - m_use);
+      float l = l_run * resc;                                        // in units of 2^kShift
+      if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use + C::kShift);
+      const float inv = (l > 0.f && it.n_tiles > 0) ? dv * resc / l : 0.f;
+      const int64_t q_row = it.q_start + row / p.group;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
+                           (int64_t)hd * p.out_head_stride;
+#pragma unroll
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t v[32];
+        if (it.n_tiles > 0) {
+          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row < it.rows_total) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+          }
+        }
+      }
+      if (row < it.rows_total && p.lse != nullptr)
+        p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l) - C::kShift) * kLn2 : -INFINITY;
+      tcgen05_fence_before();
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols256);
+  }
+}
+
+}  // namespace
+
+bool umma256_supports(int head_dim, int group) {
+  return head_dim == kD && group >= 1 && group <= kRows && (kRows % group) == 0;
+}
+int umma256_rows_per_item() { return kRows; }
+int umma256_tile_n(bool fp8) { return fp8 ? Cfg256<true>::kBN : Cfg256<false>::kBN; }
+
+cudaError_t umma256_prepare() {
+  cudaError_t e = cudaFuncSetAttribute(atrex_sm100_fwd_umma256_kernel<true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg256<true>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(atrex_sm100_fwd_umma256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg256<false>::kSmemBytes);
+}
+
+cudaError_t umma256_launch(const FwdParams& p, bool fp8, int sm_count, cudaStream_t stream) {
+  const long long items = (long long)p.num_row_tiles * p.num_kv_heads;
+  const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
+  if (fp8)
+    return launch_kernel(atrex_sm100_fwd_umma256_kernel<true>, dim3(grid), dim3(kThreads256),
+                         Cfg256<true>::kSmemBytes, stream, p);
+  return launch_kernel(atrex_sm100_fwd_umma256_kernel<false>, dim3(grid), dim3(kThreads256),
+                       Cfg256<false>::kSmemBytes, stream, p);
+}
+
+}  // namespace atrex_sm100

@@ -80,6 +80,8 @@ int prepare_device(DeviceInfo& d) {
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (mma kernels)", e);
   e = umma_prepare();
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 kernel)", e);
+  e = umma256_prepare();
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 head_dim-256 kernels)", e);
   d.prepared.store(1, std::memory_order_release);
   return ATREX_FA_OK;
 }
@@ -111,14 +113,15 @@ int check_params(const atrex_fa_sm100_params* p) {
   if (p->return_lse && p->lse == nullptr) return ATREX_FA_INVALID_VALUE;
   if (p->softcap < 0.f) return ATREX_FA_INVALID_VALUE;
   if (p->head_dim != 128 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;
-  if (p->dtype != ATREX_FA_BF16) return ATREX_FA_UNSUPPORTED;  // E4M3 belongs to the tcgen05 route
+  if (p->dtype != ATREX_FA_BF16 && p->dtype != ATREX_FA_E4M3) return ATREX_FA_UNSUPPORTED;
+  if (p->dtype == ATREX_FA_E4M3 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;  // FP8 runs on the HD256 tcgen05 kernel
   if (p->num_splits > kMaxSplits) return ATREX_FA_UNSUPPORTED;
   if (p->page_size > 0 && p->page_size % 64 != 0 && p->page_size != 16 && p->page_size != 32)
     return ATREX_FA_UNSUPPORTED;
   if (p->route != ATREX_FA_ROUTE_AUTO && p->route != ATREX_FA_ROUTE_MMA && p->route != ATREX_FA_ROUTE_UMMA)
     return ATREX_FA_INVALID_VALUE;
   // 16-byte alignment of everything the kernels touch with vectors or TMA
-  const uint64_t es = 2;
+  const uint64_t es = p->dtype == ATREX_FA_E4M3 ? 1 : 2;
   auto misaligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0; };
   if (misaligned(p->q) || misaligned(p->k) || misaligned(p->v) || misaligned(p->out)) return ATREX_FA_UNSUPPORTED;
   const int64_t strides[] = {p->q_row_stride, p->q_head_stride, p->k_row_stride, p->k_head_stride,
@@ -126,6 +129,8 @@ int check_params(const atrex_fa_sm100_params* p) {
                              p->page_size ? p->k_page_stride : 0, p->page_size ? p->v_page_stride : 0};
   for (int64_t s : strides)
     if (s < 0 || (static_cast<uint64_t>(s) * es) % 16 != 0) return ATREX_FA_UNSUPPORTED;
+  if ((static_cast<uint64_t>(p->out_row_stride) * 2) % 16 != 0 || (static_cast<uint64_t>(p->out_head_stride) * 2) % 16 != 0)
+    return ATREX_FA_UNSUPPORTED;
   return ATREX_FA_OK;
 }
 
@@ -135,14 +140,16 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   // The tcgen05 kernel takes prefill-shaped BF16 head_dim-128 calls (more packed rows than one
   // mma.sync row tile) whose GQA group divides its 128-row subtile; everything else, and every call
   // that asks for KV splits, runs on the mma.sync kernel.
-  const bool umma_ok = umma_supports(p->head_dim, group, p->dtype == ATREX_FA_BF16) && p->softcap == 0.f &&
-                       p->softmax_scale > 0.f && p->q_head_stride <= p->q_row_stride;
-  if (p->route == ATREX_FA_ROUTE_UMMA && !umma_ok) return ATREX_FA_UNSUPPORTED;
-  const bool use_umma = p->route == ATREX_FA_ROUTE_UMMA ||
+  const bool fp8 = p->dtype == ATREX_FA_E4M3;
+  const bool common_ok = p->softcap == 0.f && p->softmax_scale > 0.f && p->q_head_stride <= p->q_row_stride;
+  const bool umma_ok = common_ok && (umma_supports(p->head_dim, group, !fp8) || umma256_supports(p->head_dim, group));
+  if ((p->route == ATREX_FA_ROUTE_UMMA || fp8) && !umma_ok) return ATREX_FA_UNSUPPORTED;
+  if (fp8 && p->route == ATREX_FA_ROUTE_MMA) return ATREX_FA_UNSUPPORTED;   // the mma.sync kernel is BF16 only
+  const bool use_umma = p->route == ATREX_FA_ROUTE_UMMA || fp8 ||
                         (p->route == ATREX_FA_ROUTE_AUTO && umma_ok && packed_max > 64 && p->num_splits <= 1);
   if (use_umma) {
     r->route = ATREX_FA_ROUTE_UMMA;
-    r->m_rows = umma_rows_per_item();
+    r->m_rows = p->head_dim == 256 ? umma256_rows_per_item() : umma_rows_per_item();
     r->tiled = true;
     const int64_t bound = ((int64_t)p->total_q * group) / r->m_rows + p->batch;
     if (bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
@@ -205,13 +212,13 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
 // head stride above the row stride); perm[] tells the kernel where each went.
 int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64_t row_stride,
                   int64_t page_stride, int heads, int64_t rows, int64_t pages, int head_dim, int box_rows,
-                  int8_t perm[3]) {
+                  int8_t perm[3], int es = 2) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(ATREX_FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
   struct Dim { uint64_t extent, stride; uint32_t box; int which; };
-  Dim dims[3] = {{(uint64_t)heads, (uint64_t)head_stride * 2, 1u, 0},
-                 {(uint64_t)rows, (uint64_t)row_stride * 2, (uint32_t)box_rows, 1},
-                 {(uint64_t)pages, (uint64_t)page_stride * 2, 1u, 2}};
+  Dim dims[3] = {{(uint64_t)heads, (uint64_t)head_stride * es, 1u, 0},
+                 {(uint64_t)rows, (uint64_t)row_stride * es, (uint32_t)box_rows, 1},
+                 {(uint64_t)pages, (uint64_t)page_stride * es, 1u, 2}};
   for (int i = 0; i < 3; ++i)       // extent-1 dimensions never move: give them a harmless stride
     if (dims[i].extent <= 1) { dims[i].extent = 1; }
   for (int i = 0; i < 3; ++i)
@@ -219,7 +226,7 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
       if (dims[j].stride < dims[i].stride) { Dim t = dims[i]; dims[i] = dims[j]; dims[j] = t; }
   cuuint64_t extent[4] = {(cuuint64_t)head_dim, dims[0].extent, dims[1].extent, dims[2].extent};
   cuuint64_t stride[3] = {dims[0].stride, dims[1].stride, dims[2].stride};
-  cuuint32_t box[4] = {64u, dims[0].box, dims[1].box, dims[2].box};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / es), dims[0].box, dims[1].box, dims[2].box};   // 128 bytes wide
   cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
   for (int i = 0; i < 3; ++i) {
     if (stride[i] == 0) stride[i] = 16;  // extent-1 dimension with a zero stride
@@ -227,7 +234,8 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
       return fail(ATREX_FA_UNSUPPORTED, "K/V stride is not a multiple of 16 bytes below 2^40");
     perm[dims[i].which] = (int8_t)i;
   }
-  const CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), extent, stride, box,
+  const CUresult res = fn(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+                          const_cast<void*>(base), extent, stride, box,
                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return res == CUDA_SUCCESS ? ATREX_FA_OK : fail(ATREX_FA_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the K/V layout");
@@ -235,14 +243,15 @@ int encode_kv_map(CUtensorMap* map, const void* base, int64_t head_stride, int64
 
 // Q as (D, Hq, total_q); one box = 64 elements x `group` heads x 128/group rows = 128 packed GQA rows.
 int encode_q_map(CUtensorMap* map, const void* base, int64_t head_stride, int64_t row_stride, int heads,
-                 int64_t rows, int head_dim, int group) {
+                 int64_t rows, int head_dim, int group, int es) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(ATREX_FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
   cuuint64_t extent[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
-  cuuint64_t stride[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2};
-  cuuint32_t box[3] = {64u, (cuuint32_t)group, (cuuint32_t)(128 / group)};
+  cuuint64_t stride[2] = {(cuuint64_t)head_stride * es, (cuuint64_t)row_stride * es};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / es), (cuuint32_t)group, (cuuint32_t)(128 / group)};
   cuuint32_t elem[3] = {1u, 1u, 1u};
-  const CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), extent, stride, box,
+  const CUresult res = fn(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                          const_cast<void*>(base), extent, stride, box,
                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return res == CUDA_SUCCESS ? ATREX_FA_OK : fail(ATREX_FA_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the Q layout");
@@ -327,29 +336,32 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   const int64_t rows = paged ? p->page_size : p->total_k;
   const int64_t pages = paged ? p->num_pages : 1;
   // rows one TMA box covers: a whole KV tile of the chosen kernel, or a page if pages are smaller
-  const int kTileN = r.route == ATREX_FA_ROUTE_UMMA ? 128 : mma_tile_n(p->head_dim);
+  const bool fp8 = p->dtype == ATREX_FA_E4M3;
+  const int es = fp8 ? 1 : 2;
+  const int kTileN = r.route == ATREX_FA_ROUTE_UMMA ? (p->head_dim == 256 ? umma256_tile_n(fp8) : 128)
+                                                    : mma_tile_n(p->head_dim);
   const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
   const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
   int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
   if (empty_kv) {
     // No key exists: the kernels will not issue a copy, but the descriptors must still be valid.
-    st = encode_kv_map(&f.k_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, kperm);
+    st = encode_kv_map(&f.k_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, kperm, es);
     if (st == ATREX_FA_OK)
-      st = encode_kv_map(&f.v_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, vperm);
+      st = encode_kv_map(&f.v_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, vperm, es);
   } else {
     st = encode_kv_map(&f.k_map, p->k, p->k_head_stride, p->k_row_stride,
                        paged ? p->k_page_stride : p->k_row_stride * rows, p->num_kv_heads, rows, pages,
-                       p->head_dim, box_rows, kperm);
+                       p->head_dim, box_rows, kperm, es);
     if (st == ATREX_FA_OK)
       st = encode_kv_map(&f.v_map, p->v, p->v_head_stride, p->v_row_stride,
                          paged ? p->v_page_stride : p->v_row_stride * rows, p->num_kv_heads, rows, pages,
-                         p->head_dim, box_rows, vperm);
+                         p->head_dim, box_rows, vperm, es);
   }
   if (st != ATREX_FA_OK) return st;
   for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
   if (r.route == ATREX_FA_ROUTE_UMMA) {
     st = encode_q_map(&f.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
-                      p->num_q_heads / p->num_kv_heads);
+                      p->num_q_heads / p->num_kv_heads, es);
     if (st != ATREX_FA_OK) return st;
   }
 
@@ -396,8 +408,11 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   if (p->profile_event_begin != nullptr &&
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream)) != cudaSuccess)
     return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_begin)", e);
-  e = r.route == ATREX_FA_ROUTE_UMMA ? umma_launch(f, p->sm_count > 0 ? p->sm_count : info->sm_count, stream)
-                                     : mma_launch(f, p->head_dim, r.m_rows, stream);
+  const int sms = p->sm_count > 0 ? p->sm_count : info->sm_count;
+  if (r.route == ATREX_FA_ROUTE_UMMA)
+    e = p->head_dim == 256 ? umma256_launch(f, fp8, sms, stream) : umma_launch(f, sms, stream);
+  else
+    e = mma_launch(f, p->head_dim, r.m_rows, stream);
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
   if (p->profile_event_end != nullptr &&
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream)) != cudaSuccess)

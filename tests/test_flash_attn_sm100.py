@@ -64,7 +64,7 @@ def _golden_to_device(case):
     return dev
 
 
-@pytest.mark.parametrize("name", [n for n, s in golden_cases.GOLDEN_CASES.items() if not s["fp8"]])
+@pytest.mark.parametrize("name", [n for n, s in golden_cases.GOLDEN_CASES.items() if not s["fp8"] or s["d"] == 256])
 def test_golden_fixtures(name):
     """Kernel output against the stored outputs of the reference's own FP32 attention."""
     case = golden_cases.build(name)
@@ -73,7 +73,7 @@ def test_golden_fixtures(name):
     torch.cuda.synchronize()
     rows = gold["rows"]
     err = np.abs(out.float().cpu().numpy()[rows] - gold["out"]).max()
-    assert err <= T.BF16_O_ATOL, err
+    assert err <= (T.FP8_O_ATOL if case["fp8"] else T.BF16_O_ATOL), err
     cu = case["cu_seqlens_q"]
     live = np.concatenate([np.arange(cu[b], cu[b + 1]) for b in range(len(cu) - 1)]).astype(int)
     la, le = lse.cpu().numpy()[:, live], gold["lse"][:, live]
@@ -292,6 +292,50 @@ def test_umma_prefill_long_causal():
     """Several row tiles per request and many KV tiles; oracle on the whole (small-head) case."""
     case = T.make_case(64, [2048, 513], [2048, 3000], hq=4, hkv=1, std=0.5)
     T.check(case)
+
+
+@pytest.mark.parametrize("page", [16, 64, 128])
+def test_fp8_prefill_hd256(page):
+    """E4M3 inputs with per-(request, KV head) descales, BF16 output (BASELINE config 3 shape, scaled down)."""
+    case = T.make_case(page, [300, 70, 1, 513], [300, 900, 64, 513], hq=12, hkv=1, d=256, fp8=True, std=0.8,
+                       poison_tail=True)
+    T.check(case, fp8=True)
+
+
+def test_fp8_descales_matter_and_are_reread():
+    """A non-unit descale must change the result, and a descale mutated in place between calls must be read
+    again (reference: op_test/ppu/flash_attn/test_flash_attn_zwm890p.py:268-309)."""
+    case = T.make_case(128, [40, 200], [400, 200], hq=8, hkv=2, d=256, fp8=True, std=0.8)
+    T.check(case, fp8=True)
+    base, _ = T.run(case)
+    with torch.inference_mode():
+        case["v_descale"].mul_(2.0)
+        case["k_descale"][0, 1] = 0.3
+    T.check(case, fp8=True)
+    again, _ = T.run(case)
+    torch.cuda.synchronize()
+    assert not torch.allclose(base.float(), again.float(), atol=1e-2)
+    # broadcast (stride-0) descales are accepted without copying
+    flat = dict(case, q_descale=torch.full((1, 1), 0.5, device="cuda").expand(2, 2),
+                k_descale=torch.full((1, 1), 1.5, device="cuda").expand(2, 2),
+                v_descale=torch.full((1, 1), 0.75, device="cuda").expand(2, 2))
+    T.check(flat, fp8=True)
+
+
+def test_fp8_short_q_and_window_sink():
+    case = T.make_case(64, [1, 4, 2], [700, 64, 3000], hq=16, hkv=2, d=256, fp8=True, std=0.8)
+    T.check(case, fp8=True)
+    sink = torch.randn(16, generator=torch.Generator().manual_seed(9)).bfloat16().cuda()
+    T.check(case, fp8=True, s_aux=sink, window_size=(511, 0))
+
+
+def test_fp8_is_rejected_where_no_kernel_serves_it():
+    from atrex import can_use_flash_attn_varlen_func, flash_attn_varlen_func
+
+    case = T.make_case(64, [4], [100], hq=8, hkv=2, d=128, fp8=True)
+    assert not can_use_flash_attn_varlen_func(**case)
+    with pytest.raises(NotImplementedError, match="head_dim 256"):
+        flash_attn_varlen_func(**case)
 
 
 def test_baseline_decode_config_subsample():
