@@ -22,7 +22,7 @@ from atrex.utils.device_target import detect_device_target
 _TARGET_FA_VERSIONS = {("nvidia", "sm100"): frozenset({4})}
 
 _HEAD_DIMS = (128, 256)
-# E4M3 runs on the head_dim-256 tcgen05 kernel only (the mma.sync kernels are BF16).
+# E4M3 runs on the single-tile tcgen05 kernel (the mma.sync kernel is BF16 only, and it is the one with softcap).
 _FP8_ROUTE_BUILT = True
 _MAX_SPLITS = 256
 
@@ -131,13 +131,6 @@ def _validate_sm100_call(call, torch, batch, window, softcap):
     if q.dtype == torch.float8_e4m3fn:
         if not _FP8_ROUTE_BUILT:
             raise NotImplementedError("Atrex sm100 attention does not serve float8_e4m3fn yet (BF16 only)")
-        group = q.shape[-2] // k.shape[-2]
-        if q.shape[-1] != 256:
-            raise NotImplementedError("Atrex sm100 float8_e4m3fn attention requires head_dim 256")
-        if 128 % group:
-            raise NotImplementedError(
-                "Atrex sm100 float8_e4m3fn attention requires a GQA group (num_q_heads / num_kv_heads) dividing 128"
-            )
         if softcap:
             raise NotImplementedError("Atrex sm100 float8_e4m3fn attention does not support softcap")
         scale = call["softmax_scale"]

@@ -31,12 +31,13 @@ int umma_rows_per_item();                     // packed rows one work item cover
 cudaError_t umma_prepare();
 cudaError_t umma_launch(const FwdParams& p, int sm_count, cudaStream_t stream);
 
-// ---- fa_umma256.cu: tcgen05 prefill kernel for head_dim 256 (BF16 and FP8 E4M3) ----
-bool umma256_supports(int head_dim, int group);
-int umma256_rows_per_item();                  // 128
-int umma256_tile_n(bool fp8);                 // keys per KV tile: 128 (FP8) / 64 (BF16)
-cudaError_t umma256_prepare();
-cudaError_t umma256_launch(const FwdParams& p, bool fp8, int sm_count, cudaStream_t stream);
+// ---- fa_umma1.cu: single-row-tile tcgen05 kernel (head_dim 128 / 256, BF16 / FP8 E4M3, optional split-KV) ----
+bool umma1_supports(int head_dim);
+bool umma1_q_via_tma(int group);              // else the softmax warpgroup copies Q rows itself
+int umma1_rows_per_item();                    // 128
+int umma1_tile_n(int head_dim, bool fp8);     // keys per KV tile
+cudaError_t umma1_prepare();
+cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream);
 
 // ---- fa_combine.cu: merge split partials; tile plan ----
 cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream);

@@ -62,6 +62,7 @@ struct alignas(64) FwdParams {
   int32_t window_left, window_right;  // -1 = unbounded (after causal -> right = 0)
   int32_t num_splits;
   int32_t num_row_tiles;  // upper bound of row tiles (grid sizing); batch when order == null
+  int32_t q_via_tma;      // single-tile tcgen05 kernel: Q tile arrives by TMA (GQA group divides 128)
   float softmax_scale;
   float softcap;
   // position (1..3, minus 1) of the head / row / page coordinate in each tensor map

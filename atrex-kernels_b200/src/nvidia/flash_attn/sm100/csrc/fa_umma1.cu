@@ -1,21 +1,26 @@
-// Head-dimension-256 prefill on tcgen05 tensor cores: BF16 and FP8 E4M3 inputs, BF16 output.
+// Single-row-tile attention kernel on tcgen05 tensor cores: one 128-row tile of packed GQA rows per
+// work item, S double-buffered in TMEM, optional split-KV.  BF16 and FP8 E4M3 inputs, head_dim 128 and
+// 256, BF16 output (or FP32 partials for the combine kernel).
 //
-// This is the shape the reference's Blackwell prefill serves
-// (src/nvidia/flash_attn/sm103/prefill_cutedsl.py:146-4331: HD256, BF16 tile_n 64 / FP8 tile_n 128,
-// S ping-pong + O = all 512 TMEM columns, prefill_cutedsl.py:395-405), built single-CTA for B200:
+// It serves (a) head_dim-256 prefill, the shape of the reference's Blackwell prefill
+// (src/nvidia/flash_attn/sm103/prefill_cutedsl.py:146-4331: BF16 tile_n 64 / FP8 tile_n 128,
+// S ping-pong + O = all 512 TMEM columns, :395-405), (b) every FP8 call, (c) BF16 prefill whose GQA
+// group does not divide 128, and (d) short-query decode / speculative verify with 17..128 packed rows
+// (the reference's tcgen05 decode, src/nvidia/flash_attn/sm103/decode_cutedsl.py:453-2873, keeps K as
+// the M operand instead; here the packed rows are M and the spare rows are idle, which an HBM-bound
+// call can afford):
 //
-//   * one work item = 128 packed GQA rows of one (request, KV head); the accumulator O takes 256
-//     TMEM columns, so there is one row tile per CTA and S is double-buffered instead:
-//     TMEM = S0 | S1 | O (tile_n + tile_n + 256 columns);
-//   * warp 4 issues QK^T for tile j+1 into the other S buffer while the softmax warpgroup works
-//     on tile j, then P V for tile j as soon as its P is in TMEM, so the matrix work of one tile
-//     hides behind the softmax of the next;
-//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles
-//     (128 keys x 256 B for FP8, 64 keys x 512 B for BF16), no multicast;
-//   * FP8: scores carry q_descale * k_descale inside the softmax scale, P is written as E4M3
-//     shifted up by 2^4 with a lazy-rescale threshold of 2^4 (P <= 256 < 448, the scheme of
-//     prefill_cutedsl.py:2577-2593), V stays MN-major E4M3 in shared memory, O is multiplied by
-//     v_descale in the epilogue.
+//   * TMEM = S0 | S1 | O (tile_n + tile_n + head_dim columns); warp 4 issues QK^T for tile j+1 into
+//     the other S buffer while the softmax warpgroup works on tile j, then P V for tile j as soon as
+//     its P is in TMEM, so the matrix work of one tile hides behind the softmax of the next;
+//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles, no
+//     multicast; Q comes by TMA when the GQA group divides 128, otherwise the softmax warpgroup
+//     copies its own rows into the swizzled tile;
+//   * FP8: q_descale * k_descale ride in the softmax scale, P is written as E4M3 shifted up by 2^4
+//     with a lazy-rescale threshold of 2^4 (P <= 256 < 448, prefill_cutedsl.py:2577-2593), V stays
+//     MN-major E4M3 in shared memory, v_descale is applied in the epilogue;
+//   * split-KV: each split takes a balanced share of the tile's KV tiles and writes a normalised
+//     FP32 partial + log2 LSE; empty splits publish LSE = -inf.
 #include <cuda_fp8.h>
 
 #include "fa_kernels.cuh"
@@ -26,22 +31,22 @@ namespace atrex_sm100 {
 namespace {
 
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
-constexpr int kD = 256;             // head dimension
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
 constexpr int kSlotBytes = 32768;
-constexpr int kThreads256 = 256;
-constexpr uint32_t kTmemCols256 = 512;
+constexpr int kThreads1 = 256;
+constexpr uint32_t kTmemCols1 = 512;
 
-template <bool kFp8>
-struct Cfg256 {
+template <int D, bool kFp8>
+struct Cfg1 {
   static constexpr int kEsz = kFp8 ? 1 : 2;
-  static constexpr int kBN = kFp8 ? 128 : 64;                 // keys per tile
-  static constexpr int kNKB = kD * kEsz / 128;                // 128-byte column blocks per row
-  static constexpr int kQBytes = kRows * kD * kEsz;           // 32 KB / 64 KB
+  static constexpr int kRowBytes = D * kEsz;
+  static constexpr int kBN = (kSlotBytes / kRowBytes) < 128 ? (kSlotBytes / kRowBytes) : 128;   // keys per tile
+  static constexpr int kNKB = kRowBytes / 128;                // 128-byte column blocks per row
+  static constexpr int kQBytes = kRows * kRowBytes;
   static constexpr int kQBlock = kRows * 128;                 // bytes of one Q column block
   static constexpr int kKVBlock = kBN * 128;                  // bytes of one K/V column block
   static constexpr int kKStepsQK = kNKB * 4;                  // 32 bytes of the head dimension per UMMA
-  static constexpr int kKStepsPV = 4;                         // 32 bytes of P per row per UMMA
+  static constexpr int kKStepsPV = kBN * kEsz / 32;           // 32 bytes of P per row per UMMA
   static constexpr int kPVStepBytes = (32 / kEsz) * 128;      // V rows consumed per UMMA x 128 B
   static constexpr float kThreshold = kFp8 ? 4.f : 8.f;       // lazy-rescale threshold (log2 units)
   static constexpr float kShift = kFp8 ? 4.f : 0.f;           // P is stored as 2^shift * p
@@ -49,53 +54,68 @@ struct Cfg256 {
   static constexpr int kOffBar = kOffKV + kRing * kSlotBytes;
   static constexpr int kSmemBytes = kOffBar + 24 * 8 + 16;
   static constexpr uint32_t kFmt = kFp8 ? 0u : 1u;            // E4M3 (f8f6f4) / BF16 (f16)
+  static_assert(2 * kBN + D <= 512, "S0 | S1 | O must fit the 512 TMEM columns");
 };
 
 enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
 
 struct Item256 {
-  int b, kvh, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
+  int b, kvh, split, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
 };
 
+// Work item `item` -> (row tile, KV head, KV split), split fastest.  Row tiles come from the device-side plan
+// (heaviest request first, last row tile of a request first) or, when a request cannot have more than one
+// row tile, are simply the requests.  False when past the end.
 template <int BN>
 __device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Item256& it) {
-  const int total_tiles = p.tile_prefix[p.batch];
-  const int tile_rank = item / p.num_kv_heads;
-  if (tile_rank >= total_tiles) return false;
-  it.kvh = item % p.num_kv_heads;
-  int lo = 0, hi = p.batch;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (p.tile_prefix[mid] <= tile_rank) lo = mid; else hi = mid;
+  it.split = item % p.num_splits;
+  const int rest = item / p.num_splits;
+  it.kvh = rest % p.num_kv_heads;
+  const int tile_rank = rest / p.num_kv_heads;
+  if (p.order == nullptr) {
+    if (tile_rank >= p.batch) return false;
+    it.b = tile_rank;
+    it.row0 = 0;
+  } else {
+    if (tile_rank >= p.tile_prefix[p.batch]) return false;
+    int lo = 0, hi = p.batch;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.tile_prefix[mid] <= tile_rank) lo = mid; else hi = mid;
+    }
+    it.b = p.order[lo];
+    const int tiles_b = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
+    it.row0 = (tiles_b - 1 - (tile_rank - p.tile_prefix[lo])) * kRows;
   }
-  it.b = p.order[lo];
-  const int tiles_b = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
-  it.row0 = (tiles_b - 1 - (tile_rank - p.tile_prefix[lo])) * kRows;   // heaviest causal row tile first
   it.q_start = p.cu_seqlens_q[it.b];
   it.q_len = p.cu_seqlens_q[it.b + 1] - it.q_start;
   it.rows_total = it.q_len * p.group;
   request_kv(p, it.b, it.kv_len, it.k_start);
   it.off = it.kv_len - it.q_len;
+  it.tile_lo = 0;
+  it.n_tiles = 0;
+  if (it.row0 >= it.rows_total) return true;   // request without query rows: an item with no work
   const int qi_lo = it.row0 / p.group;
   const int qi_hi = min(it.q_len - 1, (it.row0 + kRows - 1) / p.group);
   int kv_end = it.kv_len, kv_begin = 0;
   if (p.window_right >= 0) kv_end = min(it.kv_len, qi_hi + it.off + p.window_right + 1);
   if (p.window_left >= 0) kv_begin = max(0, qi_lo + it.off - p.window_left);
-  it.tile_lo = 0;
-  it.n_tiles = 0;
   if (kv_end > kv_begin) {
-    it.tile_lo = kv_begin / BN;
-    it.n_tiles = (kv_end + BN - 1) / BN - it.tile_lo;
+    const int t0 = kv_begin / BN, n = (kv_end + BN - 1) / BN - t0;
+    const int lo_t = (int)(((long long)n * it.split) / p.num_splits);
+    const int hi_t = (int)(((long long)n * (it.split + 1)) / p.num_splits);
+    it.tile_lo = t0 + lo_t;
+    it.n_tiles = hi_t - lo_t;
   }
   return true;
 }
 
 // K or V tiles of one item, issued by one thread; NB boxes of (BN / NB) rows per tile, each box one
 // copy per 128-byte column block.  Page ids of tile j+1 are fetched before the wait for tile j's slot.
-template <bool kFp8, int NB>
+template <int D, bool kFp8, int NB>
 __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item256& it, int is_v, uint8_t* kv_smem,
                                                  uint64_t* bars, uint32_t& seq, int pshift) {
-  using C = Cfg256<kFp8>;
+  using C = Cfg1<D, kFp8>;
   constexpr int kBoxRows = C::kBN / NB;
   constexpr uint32_t kBoxBytes = kBoxRows * 128u;
   constexpr int kInner = 128 / C::kEsz;   // elements per 128-byte block
@@ -145,10 +165,10 @@ __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item2
 // One tile of keys for one row (= one thread).  Same lazy-rescale rule as the head_dim-128 kernel; P is
 // written over the first columns of the S buffer it came from (BF16 pairs, or four E4M3 per column).
 // l_run and P are in units of 2^kShift.
-template <bool kFp8, bool kMask>
+template <int D, bool kFp8, bool kMask>
 __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
                                                  float& m_run, float& l_run) {
-  using C = Cfg256<kFp8>;
+  using C = Cfg1<D, kFp8>;
   uint32_t s[C::kBN];
 #pragma unroll
   for (int c = 0; c < C::kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
@@ -213,10 +233,10 @@ __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_lo
     break;                                                        \
   }
 
-template <bool kFp8>
-__global__ void __launch_bounds__(kThreads256, 1)
-atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
-  using C = Cfg256<kFp8>;
+template <int D, bool kFp8>
+__global__ void __launch_bounds__(kThreads1, 1)
+atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
+  using C = Cfg1<D, kFp8>;
   constexpr int BN = C::kBN;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_smem = smem;
@@ -234,7 +254,7 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
   }
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(&bars[bQFull], 1);
+    mbar_init(&bars[bQFull], p.q_via_tma ? 1 : kRows);
     mbar_init(&bars[bQEmpty], 1);
     for (int s = 0; s < kRing; ++s) {
       mbar_init(&bars[bKVFull + s], 1);
@@ -248,7 +268,7 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
     fence_barrier_init();
   }
   if (warp == 4) {
-    tmem_alloc(tmem_slot, kTmemCols256);
+    tmem_alloc(tmem_slot, kTmemCols1);
     tmem_relinquish();
   }
   tcgen05_fence_before();
@@ -273,7 +293,7 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
         Item256 it;
         if (!decode_item256<BN>(p, item, it)) break;
         if (*(volatile int*)abort_flag) break;
-        if (!is_v) {
+        if (!is_v && p.q_via_tma) {
           if (it_count > 0) WAIT256(&bars[bQEmpty], (it_count - 1) & 1u, kWaitEmptyTimeout)
           mbar_arrive_expect_tx(&bars[bQFull], (uint32_t)C::kQBytes);
           q_issued = true;
@@ -284,10 +304,10 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
         }
         bool ok;
         switch (boxes) {
-          case 1: ok = produce_tiles256<kFp8, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 2: ok = produce_tiles256<kFp8, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 4: ok = produce_tiles256<kFp8, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          default: ok = produce_tiles256<kFp8, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 1: ok = produce_tiles256<D, kFp8, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 2: ok = produce_tiles256<D, kFp8, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 4: ok = produce_tiles256<D, kFp8, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          default: ok = produce_tiles256<D, kFp8, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
         }
         if (!ok) {
           if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
@@ -306,7 +326,7 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
   } else if (warp == 4) {
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t kIdescQK = umma_idesc(kRows, BN, C::kFmt, C::kFmt, 0, 0);
-    constexpr uint32_t kIdescPV = umma_idesc(kRows, kD, C::kFmt, C::kFmt, 0, 1);
+    constexpr uint32_t kIdescPV = umma_idesc(kRows, D, C::kFmt, C::kFmt, 0, 1);
     const uint64_t q_desc0 = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
     const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_smem), 16, 1024);
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_smem), C::kKVBlock, 1024);
@@ -400,15 +420,36 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
     const int r = warp * 32 + lane;                       // row = TMEM lane
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const uint32_t o_tmem = tmem_base + lane_off + o_col;
-    uint32_t cs[2] = {0, 0}, co = 0;
+    uint32_t cs[2] = {0, 0}, co = 0, it_count = 0;
     bool dead = false;
-    for (int item = blockIdx.x; !dead; item += step) {
+    for (int item = blockIdx.x; !dead; item += step, ++it_count) {
       Item256 it;
       if (!decode_item256<BN>(p, item, it)) break;
       if (*(volatile int*)abort_flag) break;
       const int row = it.row0 + r;
       const int qi = min(row / p.group, max(it.q_len - 1, 0));
       const int hd = it.kvh * p.group + row % p.group;
+      if (!p.q_via_tma) {
+        // The GQA group does not tile the 128 rows as one TMA box: every thread copies its own row of Q
+        // into the swizzled tile (zeros past the request's rows).
+        if (it_count > 0 && !mbar_wait(&bars[bQEmpty], (it_count - 1) & 1u)) { dead = true; }
+        if (!dead) {
+          const bool valid = row < it.rows_total;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                               ((int64_t)(it.q_start + row / p.group) * p.q_row_stride +
+                                (int64_t)hd * p.q_head_stride) * C::kEsz;
+#pragma unroll
+          for (int kb = 0; kb < C::kNKB; ++kb)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 val = valid ? __ldg(reinterpret_cast<const uint4*>(src + kb * 128 + c * 16))
+                                      : make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(q_smem + kb * C::kQBlock + swz128(r, c)) = val;
+            }
+          fence_proxy_async();
+          mbar_arrive(&bars[bQFull]);
+        }
+      }
       const int vis_hi = p.window_right >= 0 ? min(it.kv_len, qi + it.off + p.window_right + 1) : it.kv_len;
       const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
       const int sqi_lo = it.row0 / p.group;
@@ -431,15 +472,15 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
         ++cs[buf];
         tcgen05_fence_after();
         const float alpha =
-            need_mask ? softmax_tile256<kFp8, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
-                      : softmax_tile256<kFp8, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+            need_mask ? softmax_tile256<D, kFp8, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
+                      : softmax_tile256<D, kFp8, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
         if (j > 0) {
           if (!mbar_wait(&bars[bOFull], co & 1u)) { dead = true; break; }
           ++co;
           tcgen05_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-            for (int c = 0; c < kD / 32; ++c) {
+            for (int c = 0; c < D / 32; ++c) {
               uint32_t v[32];
               tmem_ld32(o_tmem + c * 32, v);
               tmem_ld_wait();
@@ -464,8 +505,9 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
         break;
       }
       // ---- epilogue ----
+      const bool split_mode = p.num_splits > 1;   // the combine kernel adds the sink and converts to BF16
       float sink_l2 = -INFINITY;
-      if (p.sink != nullptr && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
+      if (p.sink != nullptr && !split_mode && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
       const float m_f = fmaxf(m_run, sink_l2);
       const float m_use = m_f == -INFINITY ? 0.f : m_f;
       const float resc = fast_exp2(m_run - m_use);
@@ -475,8 +517,10 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
       const int64_t q_row = it.q_start + row / p.group;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
                            (int64_t)hd * p.out_head_stride;
+      const int64_t slot = ((int64_t)it.split * p.total_q + q_row) * p.num_q_heads + hd;
+      float* part = split_mode ? p.part_o + slot * D : nullptr;
 #pragma unroll
-      for (int c = 0; c < kD / 32; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
         if (it.n_tiles > 0) {
           tmem_ld32(o_tmem + c * 32, v);
@@ -485,7 +529,13 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
-        if (row < it.rows_total) {
+        if (row < it.rows_total && split_mode) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(part + c * 32 + i) =
+                make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                            __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+        } else if (row < it.rows_total) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 pk;
@@ -497,8 +547,11 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
           }
         }
       }
-      if (row < it.rows_total && p.lse != nullptr)
-        p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l) - C::kShift) * kLn2 : -INFINITY;
+      if (row < it.rows_total) {
+        const float lse_l2 = l > 0.f ? m_use + log2f(l) - C::kShift : -INFINITY;
+        if (split_mode) p.part_lse[slot] = lse_l2;
+        else if (p.lse != nullptr) p.lse[(int64_t)hd * p.total_q + q_row] = lse_l2 * kLn2;
+      }
       tcgen05_fence_before();
     }
   }
@@ -507,34 +560,43 @@ atrex_sm100_fwd_umma256_kernel(const __grid_constant__ FwdParams p) {
   __syncthreads();
   if (warp == 4) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols256);
+    tmem_dealloc(tmem_base, kTmemCols1);
   }
 }
 
 }  // namespace
 
-bool umma256_supports(int head_dim, int group) {
-  return head_dim == kD && group >= 1 && group <= kRows && (kRows % group) == 0;
-}
-int umma256_rows_per_item() { return kRows; }
-int umma256_tile_n(bool fp8) { return fp8 ? Cfg256<true>::kBN : Cfg256<false>::kBN; }
-
-cudaError_t umma256_prepare() {
-  cudaError_t e = cudaFuncSetAttribute(atrex_sm100_fwd_umma256_kernel<true>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg256<true>::kSmemBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(atrex_sm100_fwd_umma256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Cfg256<false>::kSmemBytes);
+bool umma1_supports(int head_dim) { return head_dim == 128 || head_dim == 256; }
+bool umma1_q_via_tma(int group) { return group >= 1 && group <= kRows && (kRows % group) == 0; }
+int umma1_rows_per_item() { return kRows; }
+int umma1_tile_n(int head_dim, bool fp8) {
+  if (head_dim == 256) return fp8 ? Cfg1<256, true>::kBN : Cfg1<256, false>::kBN;
+  return fp8 ? Cfg1<128, true>::kBN : Cfg1<128, false>::kBN;
 }
 
-cudaError_t umma256_launch(const FwdParams& p, bool fp8, int sm_count, cudaStream_t stream) {
-  const long long items = (long long)p.num_row_tiles * p.num_kv_heads;
+#define ATREX_UMMA1_VARIANTS(X) X(128, false) X(128, true) X(256, false) X(256, true)
+
+cudaError_t umma1_prepare() {
+  cudaError_t e;
+#define X(D, F)                                                                                              \
+  if ((e = cudaFuncSetAttribute(atrex_sm100_fwd_umma1_kernel<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                Cfg1<D, F>::kSmemBytes)) != cudaSuccess)                                     \
+    return e;
+  ATREX_UMMA1_VARIANTS(X)
+#undef X
+  return cudaSuccess;
+}
+
+cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream) {
+  const long long items = (long long)p.num_row_tiles * p.num_kv_heads * p.num_splits;
   const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
-  if (fp8)
-    return launch_kernel(atrex_sm100_fwd_umma256_kernel<true>, dim3(grid), dim3(kThreads256),
-                         Cfg256<true>::kSmemBytes, stream, p);
-  return launch_kernel(atrex_sm100_fwd_umma256_kernel<false>, dim3(grid), dim3(kThreads256),
-                       Cfg256<false>::kSmemBytes, stream, p);
+#define X(D, F)                                                                                                \
+  if (head_dim == D && fp8 == F)                                                                               \
+    return launch_kernel(atrex_sm100_fwd_umma1_kernel<D, F>, dim3(grid), dim3(kThreads1), Cfg1<D, F>::kSmemBytes, \
+                         stream, p);
+  ATREX_UMMA1_VARIANTS(X)
+#undef X
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace atrex_sm100

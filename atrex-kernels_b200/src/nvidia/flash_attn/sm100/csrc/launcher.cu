@@ -80,8 +80,8 @@ int prepare_device(DeviceInfo& d) {
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (mma kernels)", e);
   e = umma_prepare();
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 kernel)", e);
-  e = umma256_prepare();
-  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 head_dim-256 kernels)", e);
+  e = umma1_prepare();
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (tcgen05 single-tile kernels)", e);
   d.prepared.store(1, std::memory_order_release);
   return ATREX_FA_OK;
 }
@@ -89,7 +89,7 @@ int prepare_device(DeviceInfo& d) {
 inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 struct Resolved {
-  int route, m_rows, splits, launches;
+  int route, kernel, m_rows, tile_n, splits, launches;
   bool tiled;          // more than one row tile per request possible -> device plan
   int num_row_tiles;   // grid upper bound
   uint64_t off_order, off_prefix, off_lse, off_o, bytes;
@@ -114,7 +114,6 @@ int check_params(const atrex_fa_sm100_params* p) {
   if (p->softcap < 0.f) return ATREX_FA_INVALID_VALUE;
   if (p->head_dim != 128 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;
   if (p->dtype != ATREX_FA_BF16 && p->dtype != ATREX_FA_E4M3) return ATREX_FA_UNSUPPORTED;
-  if (p->dtype == ATREX_FA_E4M3 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;  // FP8 runs on the HD256 tcgen05 kernel
   if (p->num_splits > kMaxSplits) return ATREX_FA_UNSUPPORTED;
   if (p->page_size > 0 && p->page_size % 64 != 0 && p->page_size != 16 && p->page_size != 32)
     return ATREX_FA_UNSUPPORTED;
@@ -134,58 +133,72 @@ int check_params(const atrex_fa_sm100_params* p) {
   return ATREX_FA_OK;
 }
 
+enum Kernel { kKernelMma = 0, kKernelUmma2 = 1, kKernelUmma1 = 2 };
+
+// Which kernel, how many splits, how much scratch - from graph-static sizes only.
+//   mma.sync kernel   : BF16 calls with at most 16 packed rows per (request, KV head) (plain decode), softcap,
+//                       a non-positive scale, or a caller that pins the route;
+//   tcgen05, 2 subtiles: BF16 head_dim-128 prefill whose GQA group divides 128, no explicit KV split;
+//   tcgen05, 1 tile    : everything else - FP8, head_dim 256, other groups, 17..128 packed rows (speculative
+//                       decode, wide GQA decode) with split-KV, prefill with an explicit split count.
 int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   const int group = p->num_q_heads / p->num_kv_heads;
   const int64_t packed_max = (int64_t)p->max_seqlen_q * group;
-  // The tcgen05 kernel takes prefill-shaped BF16 head_dim-128 calls (more packed rows than one
-  // mma.sync row tile) whose GQA group divides its 128-row subtile; everything else, and every call
-  // that asks for KV splits, runs on the mma.sync kernel.
   const bool fp8 = p->dtype == ATREX_FA_E4M3;
-  const bool common_ok = p->softcap == 0.f && p->softmax_scale > 0.f && p->q_head_stride <= p->q_row_stride;
-  const bool umma_ok = common_ok && (umma_supports(p->head_dim, group, !fp8) || umma256_supports(p->head_dim, group));
-  if ((p->route == ATREX_FA_ROUTE_UMMA || fp8) && !umma_ok) return ATREX_FA_UNSUPPORTED;
+  const bool tensor_ok = p->softcap == 0.f && p->softmax_scale > 0.f && umma1_supports(p->head_dim);
+  const bool umma2_ok = tensor_ok && umma_supports(p->head_dim, group, !fp8) && p->q_head_stride <= p->q_row_stride;
+  if ((p->route == ATREX_FA_ROUTE_UMMA || fp8) && !tensor_ok) return ATREX_FA_UNSUPPORTED;
   if (fp8 && p->route == ATREX_FA_ROUTE_MMA) return ATREX_FA_UNSUPPORTED;   // the mma.sync kernel is BF16 only
-  const bool use_umma = p->route == ATREX_FA_ROUTE_UMMA || fp8 ||
-                        (p->route == ATREX_FA_ROUTE_AUTO && umma_ok && packed_max > 64 && p->num_splits <= 1);
-  if (use_umma) {
-    r->route = ATREX_FA_ROUTE_UMMA;
-    r->m_rows = p->head_dim == 256 ? umma256_rows_per_item() : umma_rows_per_item();
-    r->tiled = true;
-    const int64_t bound = ((int64_t)p->total_q * group) / r->m_rows + p->batch;
-    if (bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
-    r->num_row_tiles = (int)bound;
-    r->splits = 1;
-    r->launches = 2;
-    r->off_order = 0;
-    r->off_prefix = align_up(4ull * p->batch, 256);
-    r->off_lse = r->off_o = r->bytes = align_up(r->off_prefix + 4ull * (p->batch + 1), 256);
-    return ATREX_FA_OK;
+  int kernel;
+  if (p->route == ATREX_FA_ROUTE_MMA) kernel = kKernelMma;
+  else if (fp8) kernel = kKernelUmma1;
+  else if (p->route == ATREX_FA_ROUTE_AUTO && (!tensor_ok || packed_max <= 16)) kernel = kKernelMma;
+  else if (packed_max > 128 && umma2_ok && p->num_splits <= 1) kernel = kKernelUmma2;
+  else kernel = kKernelUmma1;
+  r->kernel = kernel;
+  r->route = kernel == kKernelMma ? ATREX_FA_ROUTE_MMA : ATREX_FA_ROUTE_UMMA;
+
+  int tile_n;
+  if (kernel == kKernelMma) {
+    r->m_rows = mma_rows_for((int)(packed_max > 64 ? 64 : packed_max));
+    tile_n = mma_tile_n(p->head_dim);
+  } else if (kernel == kKernelUmma2) {
+    r->m_rows = umma_rows_per_item();
+    tile_n = 128;
+  } else {
+    r->m_rows = umma1_rows_per_item();
+    tile_n = umma1_tile_n(p->head_dim, fp8);
   }
-  r->route = ATREX_FA_ROUTE_MMA;
-  r->m_rows = mma_rows_for((int)(packed_max > 64 ? 64 : packed_max));
-  r->tiled = packed_max > r->m_rows;
+  r->tile_n = tile_n;
+  r->tiled = kernel == kKernelUmma2 || packed_max > r->m_rows;
   const int64_t tiles_bound =
       r->tiled ? ((int64_t)p->total_q * group) / r->m_rows + p->batch : (int64_t)p->batch;
-  if (tiles_bound * p->num_kv_heads > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
+  if (tiles_bound * p->num_kv_heads * kMaxSplits > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
   r->num_row_tiles = (int)tiles_bound;
 
-  const int kTileN = mma_tile_n(p->head_dim);
   // keys one row tile can see, at the upper bound (a two-sided window limits it)
   int64_t span = p->max_seqlen_k;
   if (p->window_left >= 0 && (p->causal || p->window_right >= 0)) {
     const int64_t rows_q = r->tiled ? (r->m_rows + group - 1) / group + 1 : p->max_seqlen_q;
-    const int64_t w = (int64_t)p->window_left + rows_q + (p->causal ? 0 : p->window_right) + 1 + kTileN;
+    const int64_t w = (int64_t)p->window_left + rows_q + (p->causal ? 0 : p->window_right) + 1 + tile_n;
     if (w < span) span = w;  // + one tile above: the window need not start on a tile edge
   }
-  const int kv_tiles = (int)((span + kTileN - 1) / kTileN);
-  int splits;
-  if (p->num_splits > 0) {
+  const int kv_tiles = (int)((span + tile_n - 1) / tile_n);
+  int splits = 1;
+  if (kernel == kKernelUmma2) {
+    splits = 1;
+  } else if (p->num_splits > 0) {
     splits = p->num_splits;
-  } else {
+  } else if (kernel == kKernelMma || !r->tiled) {
+    // decode-shaped: enough CTAs to fill the machine several times over, at least 512 keys per split
     const int64_t items = (int64_t)r->num_row_tiles * p->num_kv_heads;
-    const int64_t slots = (int64_t)sm_count * (p->head_dim == 128 ? (r->m_rows == 16 ? 3 : 2) : 1);
-    const int64_t want = items > 0 ? (slots * 8 + items - 1) / items : 1;  // about eight waves of CTAs
-    const int64_t cap = (int64_t)kv_tiles * kTileN / 512;                  // >= 512 keys per split
+    const int64_t slots = kernel == kKernelMma
+                              ? (int64_t)sm_count * (p->head_dim == 128 ? (r->m_rows == 16 ? 3 : 2) : 1)
+                              : (int64_t)sm_count;
+    // The tcgen05 kernel is persistent and its split partials are wide (128 rows): split only to fill the SMs.
+    const int64_t waves = kernel == kKernelMma ? 8 : 2;
+    const int64_t want = items > 0 ? (slots * waves + items - 1) / items : 1;
+    const int64_t cap = (int64_t)kv_tiles * tile_n / 512;
     splits = (int)(want < cap ? want : cap);
   }
   if (splits > kv_tiles) splits = kv_tiles;
@@ -338,8 +351,7 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   // rows one TMA box covers: a whole KV tile of the chosen kernel, or a page if pages are smaller
   const bool fp8 = p->dtype == ATREX_FA_E4M3;
   const int es = fp8 ? 1 : 2;
-  const int kTileN = r.route == ATREX_FA_ROUTE_UMMA ? (p->head_dim == 256 ? umma256_tile_n(fp8) : 128)
-                                                    : mma_tile_n(p->head_dim);
+  const int kTileN = r.tile_n;
   const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
   const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
   int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
@@ -359,7 +371,9 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   }
   if (st != ATREX_FA_OK) return st;
   for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
-  if (r.route == ATREX_FA_ROUTE_UMMA) {
+  f.q_via_tma = r.kernel == kKernelUmma2 || (r.kernel == kKernelUmma1 && umma1_q_via_tma(p->num_q_heads / p->num_kv_heads) &&
+                                             p->q_head_stride <= p->q_row_stride);
+  if (f.q_via_tma) {
     st = encode_q_map(&f.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
                       p->num_q_heads / p->num_kv_heads, es);
     if (st != ATREX_FA_OK) return st;
@@ -409,10 +423,9 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_begin), stream)) != cudaSuccess)
     return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_begin)", e);
   const int sms = p->sm_count > 0 ? p->sm_count : info->sm_count;
-  if (r.route == ATREX_FA_ROUTE_UMMA)
-    e = p->head_dim == 256 ? umma256_launch(f, fp8, sms, stream) : umma_launch(f, sms, stream);
-  else
-    e = mma_launch(f, p->head_dim, r.m_rows, stream);
+  if (r.kernel == kKernelUmma2) e = umma_launch(f, sms, stream);
+  else if (r.kernel == kKernelUmma1) e = umma1_launch(f, p->head_dim, fp8, sms, stream);
+  else e = mma_launch(f, p->head_dim, r.m_rows, stream);
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
   if (p->profile_event_end != nullptr &&
       (e = cudaEventRecord(static_cast<cudaEvent_t>(p->profile_event_end), stream)) != cudaSuccess)

@@ -55,6 +55,9 @@ WORKLOADS = {
                           clip=(1024, 131072), window=None, sink=False, lse=False, scaling="weak"),
     "prefill_small": dict(kind="prefill", batch=4, hq=64, hkv=8, d=128, page=64, median=4096, sigma=0.5,
                           clip=(1024, 16384), window=None, sink=False, lse=False, scaling="weak"),
+    # FP8 E4M3 causal paged prefill with a cached prefix, head_dim 256, per-(request, KV head) descales = amax / 448
+    "prefill_fp8_hd256": dict(kind="prefill", batch=16, hq=24, hkv=2, d=256, page=128, q_range=(512, 4096),
+                              prefix_range=(0, 4096), fp8=True, window=None, sink=False, lse=False, scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
 }
@@ -80,6 +83,10 @@ def draw_lengths(spec, seed):
     if spec["kind"] == "decode":
         kv = rng.integers(spec["kv_lo"], spec["kv_hi"] + 1, size=spec["batch"]).tolist()
         return [spec["q_len"]] * spec["batch"], kv
+    if "q_range" in spec:
+        q = rng.integers(spec["q_range"][0], spec["q_range"][1] + 1, size=spec["batch"])
+        prefix = rng.integers(spec["prefix_range"][0], spec["prefix_range"][1] + 1, size=spec["batch"])
+        return q.tolist(), (q + prefix).tolist()
     raw = np.exp(rng.normal(np.log(spec["median"]), spec["sigma"], spec["batch"]))
     kv = np.clip(np.round(raw), *spec["clip"]).astype(int).tolist()
     return list(kv), list(kv)
@@ -196,11 +203,33 @@ def build_device_case(spec, q_lens, kv_lens, seed, device):
         seqused_k=torch.tensor(kv_lens, dtype=torch.int32).pin_memory(),
         block_table=torch.from_numpy(table).pin_memory(),
     )
+    descales = {}
+    if spec.get("fp8"):
+        # quantise as a serving stack would: one scale per (request, KV head) from that request's own tokens
+        group = spec["hq"] // hkv
+        table_d = torch.from_numpy(table).to(device)
+        kq, vq = torch.empty_like(k, dtype=torch.float8_e4m3fn), torch.empty_like(v, dtype=torch.float8_e4m3fn)
+        qq = torch.empty_like(q, dtype=torch.float8_e4m3fn)
+        for name in ("q_descale", "k_descale", "v_descale"):
+            descales[name] = torch.empty((len(q_lens), hkv), dtype=torch.float32, device=device)
+        for r, n in enumerate(counts):
+            ids = table_d[r, :n].long()
+            for src, dst, name in ((k, kq, "k_descale"), (v, vq, "v_descale")):
+                block = src[ids].float()
+                scale = block.abs().amax(dim=(0, 1, 3)).clamp_min(1e-6) / 448.0
+                dst[ids] = (block / scale[None, None, :, None]).to(torch.float8_e4m3fn)
+                descales[name][r] = scale
+            rows = q[cu[r]:cu[r + 1]].float().view(q_lens[r], hkv, group, d)
+            scale = rows.abs().amax(dim=(0, 2, 3)).clamp_min(1e-6) / 448.0
+            qq[cu[r]:cu[r + 1]] = (rows / scale[None, :, None, None]).view(q_lens[r], spec["hq"], d).to(torch.float8_e4m3fn)
+            descales["q_descale"][r] = scale
+        k, v, q = kq, vq, qq
+        host["q"] = q.view(torch.uint8).cpu().pin_memory().view(torch.float8_e4m3fn)
     case = dict(q=q, k=k, v=v, max_seqlen_q=max(q_lens + [0]), cu_seqlens_q=host["cu_seqlens_q"].to(device),
                 max_seqlen_k=width * page, seqused_k=host["seqused_k"].to(device),
                 block_table=host["block_table"].to(device), softmax_scale=d ** -0.5, causal=True,
                 window_size=spec["window"], num_splits=0, return_softmax_lse=spec["lse"],
-                out=torch.empty_like(q))
+                out=torch.empty(q.shape, dtype=torch.bfloat16, device=device), **descales)
     if spec["sink"]:
         case["s_aux"] = torch.randn(spec["hq"], generator=g, device=device).bfloat16()
     return case, host
@@ -349,7 +378,8 @@ def main():
     # ---------------- dominant kernel alone (events recorded by the launcher around it) ----------------
     window = spec["window"] or (-1, -1)
     plan_args = [case["q"], case["k"], case["v"], case["out"], None, case["cu_seqlens_q"], None, case["seqused_k"],
-                 case["block_table"], None, None, None, case.get("s_aux"), None, case["max_seqlen_q"],
+                 case["block_table"], case.get("q_descale"), case.get("k_descale"), case.get("v_descale"),
+                 case.get("s_aux"), None, case["max_seqlen_q"],
                  case["max_seqlen_k"], case["softmax_scale"], 0.0, True, window[0], window[1], args.num_splits, route]
     if spec["lse"]:
         plan_args[4] = torch.empty((spec["hq"], case["q"].shape[0]), dtype=torch.float32, device=device)
@@ -419,7 +449,9 @@ def main():
         peak = peaks[kind["bound"]]
         value = total * args.steps / (elapsed_ms * 1e-3) / kind["scale"]
         achieved = my_work / (kernel_ms_avg * 1e-3) / kind["scale"]
-        kernel_name = "atrex_sm100_fwd_umma_kernel" if info.route == runtime.ROUTE_UMMA else "atrex_sm100_fwd_mma_kernel"
+        kernel_name = "atrex_sm100_fwd_mma_kernel"
+        if info.route == runtime.ROUTE_UMMA:
+            kernel_name = "atrex_sm100_fwd_umma_kernel" if info.m_rows == 256 else "atrex_sm100_fwd_umma1_kernel"
         roofline = dict(bound=kind["bound"], achieved=achieved, peak=peak, unit=kind["unit"], frac=achieved / peak,
                         traffic=None, peak_source=peaks["source"], kernel=kernel_name, kernel_ms=kernel_ms_avg)
         if kind["bound"] == "hbm":
@@ -428,10 +460,13 @@ def main():
             roofline["peak_kind"] = "sustained cuBLAS bf16 (kernel timed inside a long step)"
             roofline["frac_of_burst_peak"] = achieved / peaks["tensor_burst"]
             roofline["frac_of_nominal_2250"] = achieved / 2250.0
+            if spec.get("fp8"):
+                roofline["note"] = "no measured FP8 peak on this pool: frac is against the measured BF16 rate"
+                roofline["frac_of_nominal_fp8_4500"] = achieved / 4500.0
         line = dict(
             metric=kind["metric"], value=value, unit=kind["unit"], n_gpus=world, steps=args.steps, warmup=warmup,
             ms_per_step=elapsed_ms / args.steps, higher_is_better=True, scaling=spec["scaling"], vs_baseline=None,
-            dtype="bf16", data="synthetic",
+            dtype="fp8_e4m3" if spec.get("fp8") else "bf16", data="synthetic",
             config=dict(workload=args.workload, requests_on_rank0=len(q_lens), batch=spec["batch"],
                         num_q_heads=spec["hq"], num_kv_heads=spec["hkv"], head_dim=spec["d"], page_size=spec["page"],
                         q_tokens_rank0=sum(q_lens), kv_tokens_rank0=sum(kv_lens), max_kv_len=max(kv_lens),

@@ -57,9 +57,12 @@ def make_case(page, q_lens, kv_lens, *, hq=8, hkv=2, d=128, fp8=False, layout="p
         for r, n in enumerate(kv_lens):
             for j in range(counts[r]):
                 used[table[r, j], : min(page, n - j * page)] = True
-        bad = torch.tensor(float("nan")).to(dtype)
-        k[~used] = bad
-        v[~used] = bad
+        if fp8:  # masked writes are not implemented for float8: poke the NaN encoding 0x7F through a byte view
+            k.view(torch.uint8)[~used] = 0x7F
+            v.view(torch.uint8)[~used] = 0x7F
+        else:
+            k[~used] = float("nan")
+            v[~used] = float("nan")
     cu = torch.zeros(len(q_lens) + 1, dtype=torch.int32)
     cu[1:] = torch.cumsum(torch.tensor(q_lens, dtype=torch.int64), 0)
     q = pool((int(cu[-1]), hq, d))

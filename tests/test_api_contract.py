@@ -140,10 +140,11 @@ def _call(fp8=False, paged=True, hq=8, hkv=2, d=128, page=64):
 def test_good_calls_are_eligible(as_b200):
     fp8_ok = as_b200._FP8_ROUTE_BUILT
     assert atrex.can_use_flash_attn_varlen_func(**_call(fp8=True, d=256)) == fp8_ok
-    # FP8 is served by the head_dim-256 tcgen05 kernel only
-    assert not atrex.can_use_flash_attn_varlen_func(**_call(fp8=True, d=128))
-    assert not atrex.can_use_flash_attn_varlen_func(**_call(fp8=True, d=256, hq=6, hkv=2))
+    assert atrex.can_use_flash_attn_varlen_func(**_call(fp8=True, d=128)) == fp8_ok
+    assert atrex.can_use_flash_attn_varlen_func(**_call(fp8=True, d=256, hq=6, hkv=2)) == fp8_ok
+    # FP8 runs on the tcgen05 kernel, which has no softcap and needs a positive scale
     assert not atrex.can_use_flash_attn_varlen_func(**dict(_call(fp8=True, d=256), softcap=10.0))
+    assert not atrex.can_use_flash_attn_varlen_func(**dict(_call(fp8=True, d=256), softmax_scale=-1.0))
     for kwargs in (dict(), dict(paged=False), dict(d=256), dict(page=16), dict(page=4224),
                    dict(hq=64, hkv=4)):
         assert atrex.can_use_flash_attn_varlen_func(**_call(**kwargs)), kwargs
@@ -225,8 +226,8 @@ def test_shape_and_dtype_rejections(as_b200):
     for bad in (torch.ones(2, 3), torch.ones(2, 2, dtype=torch.float64)):
         with pytest.raises(ValueError, match="descales"):
             atrex.flash_attn_varlen_func(**dict(fp8, v_descale=bad))
-    with pytest.raises(NotImplementedError, match="head_dim 256"):
-        atrex.flash_attn_varlen_func(**_call(fp8=True, d=128))
+    with pytest.raises(NotImplementedError, match="softcap"):
+        atrex.flash_attn_varlen_func(**dict(_call(fp8=True, d=128), softcap=5.0))
 
 
 def test_other_devices_are_rejected():
@@ -336,21 +337,28 @@ def test_plan_is_a_pure_function_of_static_sizes():
     umma = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=256)[1])
     assert umma.route == runtime.ROUTE_UMMA and umma.m_rows == 256 and umma.num_splits == 1
     assert umma.kernel_launches == 2 and umma.workspace_bytes > 0
-    # ... unless the caller asks for splits or the group does not divide 128
-    assert runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=4096, num_splits=4)[1]).route == runtime.ROUTE_MMA
-    assert runtime.plan(_plan(_call(hq=12, hkv=4), max_seqlen_q=64, max_seqlen_k=256)[1]).route == runtime.ROUTE_MMA
-    with pytest.raises(NotImplementedError):
-        runtime.plan(_plan(_call(hq=12, hkv=4), max_seqlen_q=64, max_seqlen_k=256, route=runtime.ROUTE_UMMA)[1])
-    # head_dim 256 has its own tcgen05 kernel: 128 packed rows per item
+    # explicit splits, other GQA groups and head_dim 256 run on the single-tile tcgen05 kernel (128 rows per item)
+    split4 = runtime.plan(_plan(call, max_seqlen_q=64, max_seqlen_k=4096, num_splits=4)[1])
+    assert split4.route == runtime.ROUTE_UMMA and split4.m_rows == 128 and split4.num_splits == 4
+    assert split4.kernel_launches == 3
+    odd = runtime.plan(_plan(_call(hq=12, hkv=4), max_seqlen_q=64, max_seqlen_k=256)[1])
+    assert odd.route == runtime.ROUTE_UMMA and odd.m_rows == 128
     hd256 = runtime.plan(_plan(_call(d=256), max_seqlen_q=64, max_seqlen_k=256)[1])
     assert hd256.route == runtime.ROUTE_UMMA and hd256.m_rows == 128
+    # speculative decode (17..128 packed rows) goes there too, with automatic splits and no plan kernel
+    spec = runtime.plan(_plan(_call(hq=64, hkv=4), max_seqlen_q=4, max_seqlen_k=32768)[1])
+    assert spec.route == runtime.ROUTE_UMMA and spec.m_rows == 128 and spec.num_splits > 1
+    assert spec.kernel_launches == 2
+    # softcap keeps a call on the mma.sync kernel
+    _, capped = _plan(call, max_seqlen_q=64, max_seqlen_k=256)
+    capped.softcap = 10.0
+    assert runtime.plan(capped).route == runtime.ROUTE_MMA
     # FP8 always runs there, whatever the query length; the mma.sync kernel cannot take it
     fp8 = _call(fp8=True, d=256)
     assert runtime.plan(_plan(fp8, max_seqlen_q=1, max_seqlen_k=4096)[1]).route == runtime.ROUTE_UMMA
     with pytest.raises(NotImplementedError):
         runtime.plan(_plan(fp8, max_seqlen_q=1, max_seqlen_k=4096, route=runtime.ROUTE_MMA)[1])
-    with pytest.raises(NotImplementedError):
-        runtime.plan(_plan(_call(fp8=True, d=128), max_seqlen_q=64, max_seqlen_k=256)[1])
+    assert runtime.plan(_plan(_call(fp8=True, d=128), max_seqlen_q=64, max_seqlen_k=256)[1]).route == runtime.ROUTE_UMMA
 
 
 def test_launcher_rejects_bad_blocks_before_any_launch():

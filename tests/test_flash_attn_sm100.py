@@ -64,7 +64,7 @@ def _golden_to_device(case):
     return dev
 
 
-@pytest.mark.parametrize("name", [n for n, s in golden_cases.GOLDEN_CASES.items() if not s["fp8"] or s["d"] == 256])
+@pytest.mark.parametrize("name", sorted(golden_cases.GOLDEN_CASES))
 def test_golden_fixtures(name):
     """Kernel output against the stored outputs of the reference's own FP32 attention."""
     case = golden_cases.build(name)
@@ -329,13 +329,34 @@ def test_fp8_short_q_and_window_sink():
     T.check(case, fp8=True, s_aux=sink, window_size=(511, 0))
 
 
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_fp8_decode_with_splits(d, splits):
+    """FP8 short-query calls run on the single-tile tcgen05 kernel, with or without split-KV."""
+    case = T.make_case(64, [1, 4, 2, 1], [3000, 64, 700, 1], hq=16, hkv=2, d=d, fp8=True, std=0.8, poison_tail=True)
+    T.check(case, fp8=True, num_splits=splits)
+
+
 def test_fp8_is_rejected_where_no_kernel_serves_it():
     from atrex import can_use_flash_attn_varlen_func, flash_attn_varlen_func
 
     case = T.make_case(64, [4], [100], hq=8, hkv=2, d=128, fp8=True)
-    assert not can_use_flash_attn_varlen_func(**case)
-    with pytest.raises(NotImplementedError, match="head_dim 256"):
-        flash_attn_varlen_func(**case)
+    assert not can_use_flash_attn_varlen_func(**case, softcap=5.0)
+    with pytest.raises(NotImplementedError, match="softcap"):
+        flash_attn_varlen_func(**case, softcap=5.0)
+
+
+@pytest.mark.parametrize("hq,hkv,q_len", [(64, 4, 4), (24, 2, 3), (32, 2, 2), (40, 8, 5)])
+@pytest.mark.parametrize("splits", [0, 1, 5])
+def test_bf16_wide_short_q_on_tcgen05(hq, hkv, q_len, splits):
+    """17..128 packed rows per KV head (speculative decode, wide GQA): single-tile tcgen05 kernel, any group."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    case = T.make_case(128, [q_len, 1, q_len, q_len], [5000, 300, 128, 2100], hq=hq, hkv=hkv, poison_tail=True)
+    assert _planned_route(case) == runtime.ROUTE_UMMA
+    sink = torch.randn(hq, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    T.check(case, num_splits=splits)
+    T.check(case, num_splits=splits, s_aux=sink, window_size=(1023, 0))
 
 
 def test_baseline_decode_config_subsample():
