@@ -12,7 +12,7 @@
 //     GQA rows: row r <-> query r / group, head kv_head*group + r % group
 //     (same order as decode_cutedsl.py:97-110);
 //   * a producer warp walks the block table and issues one TMA box per page
-//     slice into a ring of 128-byte-swizzled K/V stages (no multicast);
+//     slice into a ring of 128-byte-swizzled K/V stages (each CTA loads its own copy);
 //   * WT warp groups of WM warps each take alternate KV tiles with private
 //     online-softmax state (log2 domain) and merge once at the end, so there is
 //     no per-tile block barrier;

@@ -8,7 +8,7 @@
 //     (two 128-row Q subtiles) of one (request, KV head), heaviest requests first;
 //   * warp 9 is the TMA producer: Q subtiles once per item, then K and V tiles of
 //     128 tokens gathered page by page through the block table into a 4-slot ring of
-//     128-byte-swizzled tiles (no multicast);
+//     128-byte-swizzled tiles (each CTA loads its own copy);
 //   * warp 8 issues tcgen05.mma: S = Q K^T (both operands K-major in shared memory)
 //     into TMEM, then O_tile = P V with P read straight from TMEM and V MN-major in
 //     shared memory, alternating between the two subtiles so that one subtile's
@@ -46,6 +46,15 @@ constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
 enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kNumBars = 16 };
 constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (u32), abort flag (int)
 constexpr int kUmmaSmemBytes = kOffMisc + 16;
+
+#ifdef ATREX_UMMA_TRACE
+__device__ long long g_umma_trace[8192];
+#define TRACE(slot, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_umma_trace[(slot) * 256 + (idx)] = clock64(); } while (0)
+__device__ int g_trace_idx;
+#else
+#define g_trace_idx 0
+#define TRACE(slot, idx) do { } while (0)
+#endif
 
 struct Item {
   int b, kvh, row0, q_start, q_len, rows_total, kv_len, k_start, off;
@@ -85,13 +94,6 @@ __device__ __forceinline__ bool decode_item(const FwdParams& p, int item, Item& 
   }
   return true;
 }
-
-#ifdef ATREX_UMMA_TRACE
-__device__ long long g_umma_trace[8192];
-#define TRACE(slot, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_umma_trace[(slot) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(slot, idx) do { } while (0)
-#endif
 
 #define UMMA_WAIT(bar_ptr, parity, code)                          \
   if (!mbar_wait((bar_ptr), (parity))) {                          \
@@ -164,6 +166,7 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
 #pragma unroll
   for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
   tmem_ld_wait();
+  if (threadIdx.x == 0) TRACE(24, g_trace_idx);
   // Several independent chains: with two softmax warps per scheduler there is little thread-level
   // parallelism to hide the latency of one long max / add dependency chain.
   float mxv[8];
@@ -185,6 +188,7 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
     alpha = fast_exp2(m_run - mx);
     m_run = mx;
   }
+  if (threadIdx.x == 0) TRACE(25, g_trace_idx);
   const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
   float sumv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -446,6 +450,9 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
         if (!mbar_wait(&bars[kSFull + w], cs & 1u)) { dead = true; break; }
         ++cs;
         tcgen05_fence_after();
+#ifdef ATREX_UMMA_TRACE
+        if (tid == 0 && blockIdx.x == 0) g_trace_idx = cs - 1;
+#endif
         if (tid == 0) TRACE(0, cs - 1);
         if (tid == 128) TRACE(4, cs - 1);
         const float alpha = need_mask ? softmax_tile<true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)

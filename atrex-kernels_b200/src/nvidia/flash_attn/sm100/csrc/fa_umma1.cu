@@ -13,8 +13,8 @@
 //   * TMEM = S0 | S1 | O (tile_n + tile_n + head_dim columns); warp 4 issues QK^T for tile j+1 into
 //     the other S buffer while the softmax warpgroup works on tile j, then P V for tile j as soon as
 //     its P is in TMEM, so the matrix work of one tile hides behind the softmax of the next;
-//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles, no
-//     multicast; Q comes by TMA when the GQA group divides 128, otherwise the softmax warpgroup
+//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles; every CTA
+//     loads its own copy; Q comes by TMA when the GQA group divides 128, otherwise the softmax warpgroup
 //     copies its own rows into the swizzled tile;
 //   * FP8: q_descale * k_descale ride in the softmax scale, P is written as E4M3 shifted up by 2^4
 //     with a lazy-rescale threshold of 2^4 (P <= 256 < 448, prefill_cutedsl.py:2577-2593), V stays
@@ -32,15 +32,18 @@ namespace {
 
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
-constexpr int kSlotBytes = 32768;
 constexpr int kThreads1 = 256;
-constexpr uint32_t kTmemCols1 = 512;
 
-template <int D, bool kFp8>
+// kHalf: half-size K/V tiles and half the TMEM so that two CTAs share an SM; their softmax warps then
+// interleave on the MUFU pipe, which one warp per scheduler cannot keep busy on its own.
+template <int D, bool kFp8, bool kHalf = false>
 struct Cfg1 {
   static constexpr int kEsz = kFp8 ? 1 : 2;
   static constexpr int kRowBytes = D * kEsz;
+  static constexpr int kSlotBytes = kHalf ? 16384 : 32768;
+  static constexpr int kMinBlocks = kHalf ? 2 : 1;
   static constexpr int kBN = (kSlotBytes / kRowBytes) < 128 ? (kSlotBytes / kRowBytes) : 128;   // keys per tile
+  static constexpr uint32_t kTmemCols = (2 * kBN + D) <= 256 ? 256u : 512u;
   static constexpr int kNKB = kRowBytes / 128;                // 128-byte column blocks per row
   static constexpr int kQBytes = kRows * kRowBytes;
   static constexpr int kQBlock = kRows * 128;                 // bytes of one Q column block
@@ -52,6 +55,7 @@ struct Cfg1 {
   static constexpr float kShift = kFp8 ? 4.f : 0.f;           // P is stored as 2^shift * p
   static constexpr int kOffKV = kQBytes;
   static constexpr int kOffBar = kOffKV + kRing * kSlotBytes;
+  static_assert(!kHalf || (2 * kBN + D) <= 256, "two CTAs per SM need at most 256 TMEM columns each");
   static constexpr int kSmemBytes = kOffBar + 24 * 8 + 16;
   static constexpr uint32_t kFmt = kFp8 ? 0u : 1u;            // E4M3 (f8f6f4) / BF16 (f16)
   static_assert(2 * kBN + D <= 512, "S0 | S1 | O must fit the 512 TMEM columns");
@@ -112,10 +116,10 @@ __device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Ite
 
 // K or V tiles of one item, issued by one thread; NB boxes of (BN / NB) rows per tile, each box one
 // copy per 128-byte column block.  Page ids of tile j+1 are fetched before the wait for tile j's slot.
-template <int D, bool kFp8, int NB>
+template <int D, bool kFp8, bool kHalf, int NB>
 __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item256& it, int is_v, uint8_t* kv_smem,
                                                  uint64_t* bars, uint32_t& seq, int pshift) {
-  using C = Cfg1<D, kFp8>;
+  using C = Cfg1<D, kFp8, kHalf>;
   constexpr int kBoxRows = C::kBN / NB;
   constexpr uint32_t kBoxBytes = kBoxRows * 128u;
   constexpr int kInner = 128 / C::kEsz;   // elements per 128-byte block
@@ -140,7 +144,7 @@ __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item2
     }
     const uint32_t slot = seq % kRing;
     if (seq >= (uint32_t)kRing && !mbar_wait(&bars[bKVEmpty + slot], ((seq / kRing) - 1) & 1u)) return false;
-    uint8_t* dst = kv_smem + slot * kSlotBytes;
+    uint8_t* dst = kv_smem + slot * C::kSlotBytes;
     int live = 0;
 #pragma unroll
     for (int x = 0; x < NB; ++x) live += (cur[x] >= 0 && tok0 + x * kBoxRows < it.kv_len) ? 1 : 0;
@@ -165,10 +169,10 @@ __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item2
 // One tile of keys for one row (= one thread).  Same lazy-rescale rule as the head_dim-128 kernel; P is
 // written over the first columns of the S buffer it came from (BF16 pairs, or four E4M3 per column).
 // l_run and P are in units of 2^kShift.
-template <int D, bool kFp8, bool kMask>
+template <int D, bool kFp8, bool kHalf, bool kMask>
 __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
                                                  float& m_run, float& l_run) {
-  using C = Cfg1<D, kFp8>;
+  using C = Cfg1<D, kFp8, kHalf>;
   uint32_t s[C::kBN];
 #pragma unroll
   for (int c = 0; c < C::kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
@@ -233,10 +237,10 @@ __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_lo
     break;                                                        \
   }
 
-template <int D, bool kFp8>
-__global__ void __launch_bounds__(kThreads1, 1)
+template <int D, bool kFp8, bool kHalf>
+__global__ void __launch_bounds__(kThreads1, (Cfg1<D, kFp8, kHalf>::kMinBlocks))
 atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
-  using C = Cfg1<D, kFp8>;
+  using C = Cfg1<D, kFp8, kHalf>;
   constexpr int BN = C::kBN;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_smem = smem;
@@ -268,7 +272,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     fence_barrier_init();
   }
   if (warp == 4) {
-    tmem_alloc(tmem_slot, kTmemCols1);
+    tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
   tcgen05_fence_before();
@@ -304,10 +308,10 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         }
         bool ok;
         switch (boxes) {
-          case 1: ok = produce_tiles256<D, kFp8, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 2: ok = produce_tiles256<D, kFp8, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 4: ok = produce_tiles256<D, kFp8, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          default: ok = produce_tiles256<D, kFp8, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 1: ok = produce_tiles256<D, kFp8, kHalf, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 2: ok = produce_tiles256<D, kFp8, kHalf, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 4: ok = produce_tiles256<D, kFp8, kHalf, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          default: ok = produce_tiles256<D, kFp8, kHalf, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
         }
         if (!ok) {
           if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
@@ -335,7 +339,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     bool dead = false;
     auto issue_qk = [&](int buf, uint32_t slot) {
       if (lane == 0) {
-        const uint64_t kd = k_desc0 + (uint64_t)((slot * kSlotBytes) >> 4);
+        const uint64_t kd = k_desc0 + (uint64_t)((slot * C::kSlotBytes) >> 4);
 #pragma unroll
         for (int ks = 0; ks < C::kKStepsQK; ++ks) {
           const uint32_t qoff = ((ks >> 2) * C::kQBlock + (ks & 3) * 32) >> 4;
@@ -378,7 +382,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         if (tok0 + BN > it.kv_len) {
           // V rows past the end of the request may hold NaN: P is 0 there but 0 * NaN is NaN.
           const int first = max(0, it.kv_len - tok0);
-          uint8_t* v_ptr = kv_smem + slot_v * kSlotBytes;
+          uint8_t* v_ptr = kv_smem + slot_v * C::kSlotBytes;
           constexpr int kChunks = C::kNKB * 8;   // 16-byte chunks per row
           for (int idx = lane; idx < (BN - first) * kChunks; idx += 32) {
             const int r = first + idx / kChunks, c = idx % kChunks;
@@ -392,7 +396,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++cp[buf];
         tcgen05_fence_after();
         if (lane == 0) {
-          const uint64_t vd = v_desc0 + (uint64_t)((slot_v * kSlotBytes) >> 4);
+          const uint64_t vd = v_desc0 + (uint64_t)((slot_v * C::kSlotBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < C::kKStepsPV; ++ks) {
             const uint32_t voff = (ks * C::kPVStepBytes) >> 4;
@@ -472,8 +476,8 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++cs[buf];
         tcgen05_fence_after();
         const float alpha =
-            need_mask ? softmax_tile256<D, kFp8, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
-                      : softmax_tile256<D, kFp8, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+            need_mask ? softmax_tile256<D, kFp8, kHalf, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
+                      : softmax_tile256<D, kFp8, kHalf, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
         if (j > 0) {
           if (!mbar_wait(&bars[bOFull], co & 1u)) { dead = true; break; }
           ++co;
@@ -560,40 +564,44 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
   __syncthreads();
   if (warp == 4) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols1);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
 }  // namespace
 
 bool umma1_supports(int head_dim) { return head_dim == 128 || head_dim == 256; }
+bool umma1_has_half(int head_dim, bool fp8) { return head_dim == 128 && !fp8; }
 bool umma1_q_via_tma(int group) { return group >= 1 && group <= kRows && (kRows % group) == 0; }
 int umma1_rows_per_item() { return kRows; }
-int umma1_tile_n(int head_dim, bool fp8) {
+int umma1_tile_n(int head_dim, bool fp8, bool half) {
+  if (half) return Cfg1<128, false, true>::kBN;
   if (head_dim == 256) return fp8 ? Cfg1<256, true>::kBN : Cfg1<256, false>::kBN;
   return fp8 ? Cfg1<128, true>::kBN : Cfg1<128, false>::kBN;
 }
 
-#define ATREX_UMMA1_VARIANTS(X) X(128, false) X(128, true) X(256, false) X(256, true)
+#define ATREX_UMMA1_VARIANTS(X) X(128, false, false) X(128, true, false) X(256, false, false) X(256, true, false) \
+  X(128, false, true)
 
 cudaError_t umma1_prepare() {
   cudaError_t e;
-#define X(D, F)                                                                                              \
-  if ((e = cudaFuncSetAttribute(atrex_sm100_fwd_umma1_kernel<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                Cfg1<D, F>::kSmemBytes)) != cudaSuccess)                                     \
+#define X(D, F, H)                                                                                               \
+  if ((e = cudaFuncSetAttribute(atrex_sm100_fwd_umma1_kernel<D, F, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                Cfg1<D, F, H>::kSmemBytes)) != cudaSuccess)                                      \
     return e;
   ATREX_UMMA1_VARIANTS(X)
 #undef X
   return cudaSuccess;
 }
 
-cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream) {
+cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, bool half, int sm_count, cudaStream_t stream) {
   const long long items = (long long)p.num_row_tiles * p.num_kv_heads * p.num_splits;
-  const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
-#define X(D, F)                                                                                                \
-  if (head_dim == D && fp8 == F)                                                                               \
-    return launch_kernel(atrex_sm100_fwd_umma1_kernel<D, F>, dim3(grid), dim3(kThreads1), Cfg1<D, F>::kSmemBytes, \
-                         stream, p);
+  const long long ctas = (long long)sm_count * (half ? 2 : 1);
+  const unsigned grid = (unsigned)(items < ctas ? (items < 1 ? 1 : items) : ctas);
+#define X(D, F, H)                                                                                            \
+  if (head_dim == D && fp8 == F && half == H)                                                                 \
+    return launch_kernel(atrex_sm100_fwd_umma1_kernel<D, F, H>, dim3(grid), dim3(kThreads1),                    \
+                         Cfg1<D, F, H>::kSmemBytes, stream, p);
   ATREX_UMMA1_VARIANTS(X)
 #undef X
   return cudaErrorInvalidValue;

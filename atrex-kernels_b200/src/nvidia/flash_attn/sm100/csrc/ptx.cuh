@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
-// 4-D tiled TMA load, no multicast.  Coordinates are innermost first.
+// 4-D tiled TMA load into this CTA only.  Coordinates are innermost first.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tensor_map, uint64_t* bar, int c0,
                                             int c1, int c2, int c3) {
   asm volatile(

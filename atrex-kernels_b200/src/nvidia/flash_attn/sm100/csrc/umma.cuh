@@ -162,7 +162,7 @@ __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// 3-D tiled TMA load (Q tiles: D x heads x rows), no multicast.
+// 3-D tiled TMA load (Q tiles: D x heads x rows) into this CTA only.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tensor_map, uint64_t* bar, int c0, int c1,
                                             int c2) {
   asm volatile(
