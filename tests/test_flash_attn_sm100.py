@@ -9,6 +9,7 @@ pins their numerics; for them the oracle in oracle/fa_oracle.py is the definitio
 """
 
 import os
+import re
 
 import numpy as np
 import pytest
@@ -388,3 +389,125 @@ def test_linearity_in_v_at_full_size():
     torch.cuda.synchronize()
     assert torch.equal(l1, l2) and torch.equal(l1, l12)
     assert (o12.float() - (o1.float() + o2.float())).abs().max().item() <= 3e-2
+
+
+# ------------------------------------------------------------------ cross-kernel and operational checks
+def test_prefill_last_row_equals_decode_at_full_length():
+    """Size-independent property at lengths too large for the oracle: the last query row of a causal prefill
+    (tcgen05 kernel) sees exactly the keys a Q1 decode call (mma.sync split-KV kernel + combine) sees."""
+    from atrex import flash_attn_varlen_func
+
+    lens = [16384, 9000, 4097]
+    case = T.make_case(64, lens, lens, hq=32, hkv=8, std=0.7, spare_pages=4)
+    out_p, lse_p = T.run(case)
+    cu = T.to_numpy(case["cu_seqlens_q"])
+    last = torch.tensor([int(cu[i + 1]) - 1 for i in range(len(lens))], device="cuda")
+    decode = dict(case, q=case["q"][last].contiguous(), max_seqlen_q=1,
+                  cu_seqlens_q=torch.arange(len(lens) + 1, dtype=torch.int32, device="cuda"))
+    out_d, lse_d = T.run(decode)
+    torch.cuda.synchronize()
+    assert (out_p[last].float() - out_d.float()).abs().max().item() <= T.BF16_O_ATOL
+    assert torch.allclose(lse_p[:, last], lse_d, rtol=1e-3, atol=1e-3)
+
+
+def test_baseline_multi_gpu_prefill_shape_subsample():
+    """BASELINE config 5 shape (64/8 heads, head_dim 128, page 64, q = kv) on a few requests; oracle on the
+    shortest one (the others are covered by the cross-kernel property above)."""
+    lens = [1024, 6000, 2500]
+    case = T.make_case(64, lens, lens, hq=64, hkv=8, std=0.7)
+    T.check(case, requests=[0])
+
+
+@pytest.mark.parametrize("kind", ["umma2", "umma1_fp8", "umma1_splits"])
+def test_graph_replay_on_tcgen05_routes(kind):
+    """Capture once; then change lengths, Q and (FP8) descales in place and replay: everything is re-read on the
+    device (reference: op_test/utils/flash_attn_contract.py:125-142, test_flash_attn_zwm890p.py:884-905)."""
+    from atrex import flash_attn_varlen_func
+
+    if kind == "umma2":
+        case, extra, fp8 = T.make_case(64, [300, 150], [700, 150], hq=8, hkv=2, std=0.6), {}, False
+    elif kind == "umma1_fp8":
+        case, extra, fp8 = T.make_case(128, [300, 4], [700, 900], hq=12, hkv=1, d=256, fp8=True, std=0.8), {}, True
+    else:
+        case, extra, fp8 = T.make_case(128, [4, 4, 2], [3000, 500, 128], hq=64, hkv=4), dict(num_splits=3), False
+    out = torch.empty(case["q"].shape, dtype=torch.bfloat16, device="cuda")
+    kwargs = dict(case, out=out, return_softmax_lse=True, **extra)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            flash_attn_varlen_func(**kwargs)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g_out, g_lse = flash_attn_varlen_func(**kwargs)
+    q_lens = case["cu_seqlens_q"][1:] - case["cu_seqlens_q"][:-1]
+    case["seqused_k"].copy_(torch.maximum(case["seqused_k"] - 37, q_lens))
+    if fp8:
+        with torch.inference_mode():
+            case["k_descale"].mul_(0.5)
+            case["v_descale"].add_(0.25)
+    else:
+        case["q"].copy_(torch.randn_like(case["q"].float()).mul_(0.6).bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    eo, el = T.oracle_for(case)
+    T.compare(g_out, g_lse, eo, el, T.to_numpy(case["cu_seqlens_q"]), fp8=fp8)
+
+
+def test_scratch_is_call_local():
+    """Repeated calls of several shapes keep allocated memory flat: scratch comes from the allocator per call and
+    nothing is cached per layer (reference: op_test/utils/flash_attn_contract.py:145-175)."""
+    from atrex import flash_attn_varlen_func
+
+    shapes = [T.make_case(64, [1] * 8, [2000] * 8, hq=32, hkv=8),
+              T.make_case(64, [300, 100], [300, 400], hq=8, hkv=2),
+              T.make_case(128, [4] * 4, [3000] * 4, hq=64, hkv=4)]
+    calls = [dict(c, out=torch.empty_like(c["q"]), return_softmax_lse=False) for c in shapes]
+    for kw in calls:
+        for _ in range(3):
+            flash_attn_varlen_func(**kw)
+    torch.cuda.synchronize()
+    baseline = torch.cuda.memory_allocated()
+    for _ in range(50):
+        for kw in calls:
+            flash_attn_varlen_func(**kw)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() <= baseline + 256 * 1024
+
+
+def test_only_atrex_kernels_run():
+    """Every compute kernel the public call launches carries the atrex_ prefix (reference:
+    op_test/utils/flash_attn_contract.py:178-212)."""
+    from atrex import flash_attn_varlen_func
+
+    cases = [T.make_case(64, [1] * 4, [3000] * 4, hq=32, hkv=8),                     # mma.sync + combine
+             T.make_case(64, [400, 100], [400, 400], hq=8, hkv=2),                    # plan + tcgen05 two-subtile
+             T.make_case(128, [300, 4], [700, 900], hq=12, hkv=1, d=256, fp8=True)]   # plan + tcgen05 single tile
+    seen = set()
+    for case in cases:
+        kw = dict(case, out=torch.empty(case["q"].shape, dtype=torch.bfloat16, device="cuda"))
+        for _ in range(2):
+            flash_attn_varlen_func(**kw)
+        torch.cuda.synchronize()
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+            flash_attn_varlen_func(**kw)
+            torch.cuda.synchronize()
+        names = [e.name for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+        kernels = [n for n in names if not n.lower().startswith(("memcpy", "memset"))]
+        assert kernels, "profiler exposed no kernels"
+        assert all("atrex_" in n for n in kernels), kernels
+        seen.update(re.search(r"atrex_sm100_[a-z0-9_]+", n).group(0) for n in kernels)
+    assert {"atrex_sm100_fwd_mma_kernel", "atrex_sm100_combine_kernel", "atrex_sm100_plan_kernel",
+            "atrex_sm100_fwd_umma_kernel", "atrex_sm100_fwd_umma1_kernel"} <= seen, seen
+
+
+def test_poisoned_scratch_on_split_tcgen05_path():
+    """Split partials of the single-tile tcgen05 kernel: splits without keys publish -inf and their (NaN) scratch
+    is never read."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    case = T.make_case(128, [4, 4, 1], [6000, 10, 0], hq=64, hkv=4)
+    poison = torch.full((64 << 20,), 0xFF, dtype=torch.uint8, device="cuda")
+    del poison
+    T.check(case, num_splits=8)
