@@ -169,19 +169,22 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
   if (threadIdx.x == 0) TRACE(24, g_trace_idx);
   // Several independent chains: with two softmax warps per scheduler there is little thread-level
   // parallelism to hide the latency of one long max / add dependency chain.
-  float mxv[8];
+  if (kMask) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) mxv[k] = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < kBN; ++i) {
-    if (kMask) {
+    for (int i = 0; i < kBN; ++i) {
       const int col = tok0 + i;
       if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
     }
-    mxv[i & 7] = fmaxf(mxv[i & 7], __uint_as_float(s[i]));
   }
-  float mx = fmaxf(fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3])),
-                   fmaxf(fmaxf(mxv[4], mxv[5]), fmaxf(mxv[6], mxv[7])));
+  float mxv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < kBN; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
+    mxv[0] = fmax3(mxv[0], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    mxv[1] = fmax3(mxv[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    mxv[2] = fmax3(mxv[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+    mxv[3] = fmax3(mxv[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+  }
+  float mx = fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3]));
   mx *= scale_log2;
   float alpha = 1.f;
   if (mx > m_run + kRescaleThreshold) {  // also the first finite maximum of the row

@@ -177,19 +177,22 @@ __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_lo
 #pragma unroll
   for (int c = 0; c < C::kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
   tmem_ld_wait();
-  float mxv[8];
+  if (kMask) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) mxv[k] = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < C::kBN; ++i) {
-    if (kMask) {
+    for (int i = 0; i < C::kBN; ++i) {
       const int col = tok0 + i;
       if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
     }
-    mxv[i & 7] = fmaxf(mxv[i & 7], __uint_as_float(s[i]));
   }
-  float mx = fmaxf(fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3])),
-                   fmaxf(fmaxf(mxv[4], mxv[5]), fmaxf(mxv[6], mxv[7])));
+  float mxv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < C::kBN; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
+    mxv[0] = fmax3(mxv[0], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    mxv[1] = fmax3(mxv[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    mxv[2] = fmax3(mxv[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+    mxv[3] = fmax3(mxv[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+  }
+  float mx = fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3]));
   mx *= scale_log2;
   float alpha = 1.f;
   if (mx > m_run + C::kThreshold) {  // also the first finite maximum of the row
