@@ -35,10 +35,9 @@ cudaError_t umma_launch(const FwdParams& p, int sm_count, cudaStream_t stream);
 bool umma1_supports(int head_dim);
 bool umma1_q_via_tma(int group);              // else the softmax warpgroup copies Q rows itself
 int umma1_rows_per_item();                    // 128
-bool umma1_has_half(int head_dim, bool fp8);  // a two-CTAs-per-SM variant with half-size tiles exists
-int umma1_tile_n(int head_dim, bool fp8, bool half);     // keys per KV tile
+int umma1_tile_n(int head_dim, bool fp8);     // keys per KV tile
 cudaError_t umma1_prepare();
-cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, bool half, int sm_count, cudaStream_t stream);
+cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream);
 
 // ---- fa_combine.cu: merge split partials; tile plan ----
 cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream);

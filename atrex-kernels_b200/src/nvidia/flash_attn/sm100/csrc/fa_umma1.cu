@@ -32,18 +32,17 @@ namespace {
 
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
-constexpr int kThreads1 = 256;
+constexpr int kSoftmaxWarps1 = 8;                 // two threads per row: 2 x 4 warps
+constexpr int kMmaWarp1 = 8, kKWarp1 = 9, kVWarp1 = 10;   // warp 11 idles
+constexpr int kThreads1 = (kSoftmaxWarps1 + 4) * 32;       // 384 threads, up to 168 registers each
 
-// kHalf: half-size K/V tiles and half the TMEM so that two CTAs share an SM; their softmax warps then
-// interleave on the MUFU pipe, which one warp per scheduler cannot keep busy on its own.
-template <int D, bool kFp8, bool kHalf = false>
+template <int D, bool kFp8>
 struct Cfg1 {
   static constexpr int kEsz = kFp8 ? 1 : 2;
   static constexpr int kRowBytes = D * kEsz;
-  static constexpr int kSlotBytes = kHalf ? 16384 : 32768;
-  static constexpr int kMinBlocks = kHalf ? 2 : 1;
+  static constexpr int kSlotBytes = 32768;
   static constexpr int kBN = (kSlotBytes / kRowBytes) < 128 ? (kSlotBytes / kRowBytes) : 128;   // keys per tile
-  static constexpr uint32_t kTmemCols = (2 * kBN + D) <= 256 ? 256u : 512u;
+  static constexpr uint32_t kTmemCols = 512;
   static constexpr int kNKB = kRowBytes / 128;                // 128-byte column blocks per row
   static constexpr int kQBytes = kRows * kRowBytes;
   static constexpr int kQBlock = kRows * 128;                 // bytes of one Q column block
@@ -55,10 +54,11 @@ struct Cfg1 {
   static constexpr float kShift = kFp8 ? 4.f : 0.f;           // P is stored as 2^shift * p
   static constexpr int kOffKV = kQBytes;
   static constexpr int kOffBar = kOffKV + kRing * kSlotBytes;
-  static_assert(!kHalf || (2 * kBN + D) <= 256, "two CTAs per SM need at most 256 TMEM columns each");
-  static constexpr int kSmemBytes = kOffBar + 24 * 8 + 16;
+  static constexpr int kOffXchg = kOffBar + 256;              // [parity][half][row] floats for the row max / sum
+  static constexpr int kSmemBytes = kOffXchg + 2 * 2 * kRows * 4;
   static constexpr uint32_t kFmt = kFp8 ? 0u : 1u;            // E4M3 (f8f6f4) / BF16 (f16)
   static_assert(2 * kBN + D <= 512, "S0 | S1 | O must fit the 512 TMEM columns");
+  static_assert(kBN / 2 >= 32, "each softmax thread takes at least one 32-column chunk");
 };
 
 enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
@@ -116,10 +116,10 @@ __device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Ite
 
 // K or V tiles of one item, issued by one thread; NB boxes of (BN / NB) rows per tile, each box one
 // copy per 128-byte column block.  Page ids of tile j+1 are fetched before the wait for tile j's slot.
-template <int D, bool kFp8, bool kHalf, int NB>
+template <int D, bool kFp8, int NB>
 __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item256& it, int is_v, uint8_t* kv_smem,
                                                  uint64_t* bars, uint32_t& seq, int pshift) {
-  using C = Cfg1<D, kFp8, kHalf>;
+  using C = Cfg1<D, kFp8>;
   constexpr int kBoxRows = C::kBN / NB;
   constexpr uint32_t kBoxBytes = kBoxRows * 128u;
   constexpr int kInner = 128 / C::kEsz;   // elements per 128-byte block
@@ -166,43 +166,44 @@ __device__ __forceinline__ bool produce_tiles256(const FwdParams& p, const Item2
   return true;
 }
 
-// One tile of keys for one row (= one thread).  Same lazy-rescale rule as the head_dim-128 kernel; P is
-// written over the first columns of the S buffer it came from (BF16 pairs, or four E4M3 per column).
-// l_run and P are in units of 2^kShift.
-template <int D, bool kFp8, bool kHalf, bool kMask>
-__device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
-                                                 float& m_run, float& l_run) {
-  using C = Cfg1<D, kFp8, kHalf>;
-  uint32_t s[C::kBN];
+// One tile of keys for half a row: the 128 rows of a tile are served by 8 softmax warps, two threads per
+// row with half of the tile's key columns each, so that two softmax warps per scheduler interleave on the
+// MUFU pipe (one warp alone cannot keep it busy).  Step 1 loads the thread's scores from TMEM, masks
+// them and returns their (unscaled) maximum.
+template <int D, bool kFp8, bool kMask>
+__device__ __forceinline__ float half_max(uint32_t s_tmem, uint32_t (&s)[Cfg1<D, kFp8>::kBN / 2], int col0, int vis_lo,
+                                          int vis_hi) {
+  constexpr int N = Cfg1<D, kFp8>::kBN / 2;
 #pragma unroll
-  for (int c = 0; c < C::kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+  for (int c = 0; c < N / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
   tmem_ld_wait();
   if (kMask) {
 #pragma unroll
-    for (int i = 0; i < C::kBN; ++i) {
-      const int col = tok0 + i;
+    for (int i = 0; i < N; ++i) {
+      const int col = col0 + i;
       if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
     }
   }
   float mxv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-  for (int i = 0; i < C::kBN; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
+  for (int i = 0; i < N; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
     mxv[0] = fmax3(mxv[0], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
     mxv[1] = fmax3(mxv[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
     mxv[2] = fmax3(mxv[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
     mxv[3] = fmax3(mxv[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
   }
-  float mx = fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3]));
-  mx *= scale_log2;
-  float alpha = 1.f;
-  if (mx > m_run + C::kThreshold) {  // also the first finite maximum of the row
-    alpha = fast_exp2(m_run - mx);
-    m_run = mx;
-  }
-  const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + C::kShift;
+  return fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3]));
+}
+
+// Step 2: P = 2^(s * scale + neg_m) (neg_m includes the FP8 shift) written over the first columns of the
+// thread's OWN score columns (BF16 pairs, or four E4M3 per column); returns the sum of the probabilities.
+template <int D, bool kFp8>
+__device__ __forceinline__ float half_exp(uint32_t s_tmem, const uint32_t (&s)[Cfg1<D, kFp8>::kBN / 2], float scale_log2,
+                                          float neg_m) {
+  constexpr int N = Cfg1<D, kFp8>::kBN / 2;
   float sumv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int c = 0; c < C::kBN / 32; ++c) {
+  for (int c = 0; c < N / 32; ++c) {
     if constexpr (kFp8) {
       uint32_t packed[8];
 #pragma unroll
@@ -229,8 +230,27 @@ __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_lo
       tmem_st16(s_tmem + c * 16, packed);
     }
   }
-  l_run = l_run * alpha + ((sumv[0] + sumv[1]) + (sumv[2] + sumv[3]));
-  return alpha;
+  return (sumv[0] + sumv[1]) + (sumv[2] + sumv[3]);
+}
+
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Barrier that also ORs a predicate over the group: a bounded wait that expired in one thread takes the
+// whole group out of its loop together (a plain bar.sync would strand the others).
+__device__ __forceinline__ bool group_barrier_or(int id, int threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.or.pred p, %2, %3, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"((uint32_t)pred), "r"(id), "r"(threads)
+      : "memory");
+  return out != 0;
 }
 
 #define WAIT256(bar_ptr, parity, code)                            \
@@ -240,10 +260,10 @@ __device__ __forceinline__ float softmax_tile256(uint32_t s_tmem, float scale_lo
     break;                                                        \
   }
 
-template <int D, bool kFp8, bool kHalf>
-__global__ void __launch_bounds__(kThreads1, (Cfg1<D, kFp8, kHalf>::kMinBlocks))
+template <int D, bool kFp8>
+__global__ void __launch_bounds__(kThreads1, 1)
 atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
-  using C = Cfg1<D, kFp8, kHalf>;
+  using C = Cfg1<D, kFp8>;
   constexpr int BN = C::kBN;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_smem = smem;
@@ -261,7 +281,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
   }
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(&bars[bQFull], p.q_via_tma ? 1 : kRows);
+    mbar_init(&bars[bQFull], p.q_via_tma ? 1 : 2 * kRows);
     mbar_init(&bars[bQEmpty], 1);
     for (int s = 0; s < kRing; ++s) {
       mbar_init(&bars[bKVFull + s], 1);
@@ -269,12 +289,12 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars[bSFull + b], 1);
-      mbar_init(&bars[bPFull + b], kRows);
+      mbar_init(&bars[bPFull + b], 2 * kRows);
     }
     mbar_init(&bars[bOFull], 1);
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp1) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
@@ -285,10 +305,10 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
   const uint32_t o_col = 2 * BN;
   const int step = gridDim.x;
 
-  if (warp == 5 || warp == 6) {
+  if (warp == kKWarp1 || warp == kVWarp1) {
     // ------------------------------- TMA producers: K (+Q) and V -------------------------------
     if (lane == 0) {
-      const int is_v = warp == 6;
+      const int is_v = warp == kVWarp1;
       if (!is_v) prefetch_tensormap(&p.q_map);
       prefetch_tensormap(is_v ? &p.v_map : &p.k_map);
       const int boxes = BN / p.box_rows;
@@ -311,10 +331,10 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         }
         bool ok;
         switch (boxes) {
-          case 1: ok = produce_tiles256<D, kFp8, kHalf, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 2: ok = produce_tiles256<D, kFp8, kHalf, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          case 4: ok = produce_tiles256<D, kFp8, kHalf, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
-          default: ok = produce_tiles256<D, kFp8, kHalf, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 1: ok = produce_tiles256<D, kFp8, 1>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 2: ok = produce_tiles256<D, kFp8, 2>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          case 4: ok = produce_tiles256<D, kFp8, 4>(p, it, is_v, kv_smem, bars, seq, pshift); break;
+          default: ok = produce_tiles256<D, kFp8, 8>(p, it, is_v, kv_smem, bars, seq, pshift); break;
         }
         if (!ok) {
           if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
@@ -330,7 +350,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       }
     }
     __syncwarp();
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp1) {
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t kIdescQK = umma_idesc(kRows, BN, C::kFmt, C::kFmt, 0, 0);
     constexpr uint32_t kIdescPV = umma_idesc(kRows, D, C::kFmt, C::kFmt, 0, 1);
@@ -403,10 +423,13 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
           for (int ks = 0; ks < C::kKStepsPV; ++ks) {
             const uint32_t voff = (ks * C::kPVStepBytes) >> 4;
+            // P of key half h sits over the first columns of that half's own score columns
+            constexpr int kPerHalf = C::kKStepsPV / 2;
+            const uint32_t pcol = buf * BN + (ks / kPerHalf) * (BN / 2) + (ks % kPerHalf) * 8;
             if constexpr (kFp8)
-              umma_ts_f8(tmem_base + o_col, tmem_base + buf * BN + ks * 8, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+              umma_ts_f8(tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
             else
-              umma_ts_f16(tmem_base + o_col, tmem_base + buf * BN + ks * 8, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+              umma_ts_f16(tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
           }
           umma_commit(&bars[bOFull]);
           umma_commit(&bars[bKVEmpty + slot_v]);
@@ -422,40 +445,44 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       atomicExch(abort_flag, 1);
     }
     __syncwarp();
-  } else if (warp < 4) {
-    // ------------------------------- softmax warpgroup -------------------------------
-    const int r = warp * 32 + lane;                       // row = TMEM lane
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    const uint32_t o_tmem = tmem_base + lane_off + o_col;
-    uint32_t cs[2] = {0, 0}, co = 0, it_count = 0;
+  } else if (warp < kSoftmaxWarps1) {
+    // ------------- softmax warps: two threads per row, half of each tile's key columns each -------------
+    constexpr int N = BN / 2;                              // key columns per thread and tile
+    const int h = warp >> 2;                               // which half of the key columns
+    const int r = (warp & 3) * 32 + lane;                  // row = TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_off + o_col + h * (D / 2);   // this thread's half of the O columns
+    float* xchg = reinterpret_cast<float*>(smem + C::kOffXchg);            // [parity][half][row]
+    constexpr int kGroupBar = 1, kGroup = kSoftmaxWarps1 * 32;
+    uint32_t cs[2] = {0, 0}, co = 0, it_count = 0, cx = 0;
     bool dead = false;
     for (int item = blockIdx.x; !dead; item += step, ++it_count) {
       Item256 it;
       if (!decode_item256<BN>(p, item, it)) break;
-      if (*(volatile int*)abort_flag) break;
+      if (group_barrier_or(kGroupBar, kGroup, *(volatile int*)abort_flag != 0)) break;   // leave together
       const int row = it.row0 + r;
       const int qi = min(row / p.group, max(it.q_len - 1, 0));
       const int hd = it.kvh * p.group + row % p.group;
       if (!p.q_via_tma) {
-        // The GQA group does not tile the 128 rows as one TMA box: every thread copies its own row of Q
-        // into the swizzled tile (zeros past the request's rows).
-        if (it_count > 0 && !mbar_wait(&bars[bQEmpty], (it_count - 1) & 1u)) { dead = true; }
+        // The GQA group does not tile the 128 rows as one TMA box: the two threads of a row copy half of
+        // it each into the swizzled tile (zeros past the request's rows).
+        if (it_count > 0 && !mbar_wait(&bars[bQEmpty], (it_count - 1) & 1u)) dead = true;
         if (!dead) {
           const bool valid = row < it.rows_total;
           const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
                                ((int64_t)(it.q_start + row / p.group) * p.q_row_stride +
                                 (int64_t)hd * p.q_head_stride) * C::kEsz;
+          constexpr int kChunksHalf = C::kNKB * 4;         // 16-byte chunks each thread copies
 #pragma unroll
-          for (int kb = 0; kb < C::kNKB; ++kb)
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const uint4 val = valid ? __ldg(reinterpret_cast<const uint4*>(src + kb * 128 + c * 16))
-                                      : make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4*>(q_smem + kb * C::kQBlock + swz128(r, c)) = val;
-            }
+          for (int i = 0; i < kChunksHalf; ++i) {
+            const int chunk = h * kChunksHalf + i, kb = chunk >> 3, c = chunk & 7;
+            const uint4 val = valid ? __ldg(reinterpret_cast<const uint4*>(src + kb * 128 + c * 16))
+                                    : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(q_smem + kb * C::kQBlock + swz128(r, c)) = val;
+          }
           fence_proxy_async();
-          mbar_arrive(&bars[bQFull]);
         }
+        mbar_arrive(&bars[bQFull]);   // also when dead: the issuer must not be left waiting for this phase
       }
       const int vis_hi = p.window_right >= 0 ? min(it.kv_len, qi + it.off + p.window_right + 1) : it.kv_len;
       const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
@@ -469,25 +496,41 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       if (p.v_descale) dv = p.v_descale[it.b * p.v_descale_bs + it.kvh * p.v_descale_hs];
       const float scale_log2 = p.softmax_scale * dq * dk * kLog2e;   // > 0 on this route
 
-      float m_run = -INFINITY, l_run = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;   // l_run: this thread's half of the row sum, in units of 2^kShift
       for (int j = 0; j < it.n_tiles; ++j) {
         const int buf = j & 1;
-        const uint32_t s_tmem = tmem_base + lane_off + buf * BN;
+        const uint32_t s_tmem = tmem_base + lane_off + buf * BN + h * N;   // own scores; P goes over them
         const int tok0 = (it.tile_lo + j) * BN;
         const bool need_mask = tok0 < full_lo || tok0 + BN > full_hi;
-        if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) { dead = true; break; }
+        if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) dead = true;
         ++cs[buf];
         tcgen05_fence_after();
-        const float alpha =
-            need_mask ? softmax_tile256<D, kFp8, kHalf, true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
-                      : softmax_tile256<D, kFp8, kHalf, false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+        uint32_t s[N];
+        float mx = -INFINITY;
+        if (!dead)
+          mx = need_mask ? half_max<D, kFp8, true>(s_tmem, s, tok0 + h * N, vis_lo, vis_hi)
+                         : half_max<D, kFp8, false>(s_tmem, s, tok0 + h * N, vis_lo, vis_hi);
+        // row maximum = max of the two halves, exchanged through shared memory (double-buffered)
+        float* slot = xchg + (cx & 1u) * (2 * kRows);
+        ++cx;
+        slot[h * kRows + r] = mx;
+        if (group_barrier_or(kGroupBar, kGroup, dead)) { dead = true; break; }
+        mx = fmaxf(mx, slot[(h ^ 1) * kRows + r]) * scale_log2;
+        float alpha = 1.f;
+        if (mx > m_run + C::kThreshold) {  // also the first finite maximum of the row
+          alpha = fast_exp2(m_run - mx);
+          m_run = mx;
+        }
+        const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + C::kShift;
+        l_run = l_run * alpha + half_exp<D, kFp8>(s_tmem, s, scale_log2, neg_m);
         if (j > 0) {
-          if (!mbar_wait(&bars[bOFull], co & 1u)) { dead = true; break; }
+          // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.
+          if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;   // reported at the next group barrier
           ++co;
           tcgen05_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!dead && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / 64; ++c) {
               uint32_t v[32];
               tmem_ld32(o_tmem + c * 32, v);
               tmem_ld_wait();
@@ -506,28 +549,33 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++co;
         tcgen05_fence_after();
       }
-      if (dead) {
+      // ---- epilogue: row sum = both halves; each thread normalises and stores its half of the O columns ----
+      float* slot = xchg + (cx & 1u) * (2 * kRows);
+      ++cx;
+      slot[h * kRows + r] = l_run;
+      if (group_barrier_or(kGroupBar, kGroup, dead)) {
         if (p.status) atomicExch(p.status, kWaitMmaTimeout);
         atomicExch(abort_flag, 1);
+        dead = true;
         break;
       }
-      // ---- epilogue ----
+      const float l_row = l_run + slot[(h ^ 1) * kRows + r];
       const bool split_mode = p.num_splits > 1;   // the combine kernel adds the sink and converts to BF16
       float sink_l2 = -INFINITY;
       if (p.sink != nullptr && !split_mode && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
       const float m_f = fmaxf(m_run, sink_l2);
       const float m_use = m_f == -INFINITY ? 0.f : m_f;
       const float resc = fast_exp2(m_run - m_use);
-      float l = l_run * resc;                                        // in units of 2^kShift
+      float l = l_row * resc;                                        // in units of 2^kShift
       if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use + C::kShift);
       const float inv = (l > 0.f && it.n_tiles > 0) ? dv * resc / l : 0.f;
       const int64_t q_row = it.q_start + row / p.group;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
-                           (int64_t)hd * p.out_head_stride;
-      const int64_t slot = ((int64_t)it.split * p.total_q + q_row) * p.num_q_heads + hd;
-      float* part = split_mode ? p.part_o + slot * D : nullptr;
+                           (int64_t)hd * p.out_head_stride + h * (D / 2);
+      const int64_t part_slot = ((int64_t)it.split * p.total_q + q_row) * p.num_q_heads + hd;
+      float* part = split_mode ? p.part_o + part_slot * D + h * (D / 2) : nullptr;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
         if (it.n_tiles > 0) {
           tmem_ld32(o_tmem + c * 32, v);
@@ -554,9 +602,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
           }
         }
       }
-      if (row < it.rows_total) {
+      if (h == 0 && row < it.rows_total) {
         const float lse_l2 = l > 0.f ? m_use + log2f(l) - C::kShift : -INFINITY;
-        if (split_mode) p.part_lse[slot] = lse_l2;
+        if (split_mode) p.part_lse[part_slot] = lse_l2;
         else if (p.lse != nullptr) p.lse[(int64_t)hd * p.total_q + q_row] = lse_l2 * kLn2;
       }
       tcgen05_fence_before();
@@ -565,7 +613,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
 
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kMmaWarp1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
@@ -574,37 +622,33 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
 }  // namespace
 
 bool umma1_supports(int head_dim) { return head_dim == 128 || head_dim == 256; }
-bool umma1_has_half(int head_dim, bool fp8) { return head_dim == 128 && !fp8; }
 bool umma1_q_via_tma(int group) { return group >= 1 && group <= kRows && (kRows % group) == 0; }
 int umma1_rows_per_item() { return kRows; }
-int umma1_tile_n(int head_dim, bool fp8, bool half) {
-  if (half) return Cfg1<128, false, true>::kBN;
+int umma1_tile_n(int head_dim, bool fp8) {
   if (head_dim == 256) return fp8 ? Cfg1<256, true>::kBN : Cfg1<256, false>::kBN;
   return fp8 ? Cfg1<128, true>::kBN : Cfg1<128, false>::kBN;
 }
 
-#define ATREX_UMMA1_VARIANTS(X) X(128, false, false) X(128, true, false) X(256, false, false) X(256, true, false) \
-  X(128, false, true)
+#define ATREX_UMMA1_VARIANTS(X) X(128, false) X(128, true) X(256, false) X(256, true)
 
 cudaError_t umma1_prepare() {
   cudaError_t e;
-#define X(D, F, H)                                                                                               \
-  if ((e = cudaFuncSetAttribute(atrex_sm100_fwd_umma1_kernel<D, F, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                Cfg1<D, F, H>::kSmemBytes)) != cudaSuccess)                                      \
+#define X(D, F)                                                                                               \
+  if ((e = cudaFuncSetAttribute(atrex_sm100_fwd_umma1_kernel<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                Cfg1<D, F>::kSmemBytes)) != cudaSuccess)                                      \
     return e;
   ATREX_UMMA1_VARIANTS(X)
 #undef X
   return cudaSuccess;
 }
 
-cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, bool half, int sm_count, cudaStream_t stream) {
+cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream) {
   const long long items = (long long)p.num_row_tiles * p.num_kv_heads * p.num_splits;
-  const long long ctas = (long long)sm_count * (half ? 2 : 1);
-  const unsigned grid = (unsigned)(items < ctas ? (items < 1 ? 1 : items) : ctas);
-#define X(D, F, H)                                                                                            \
-  if (head_dim == D && fp8 == F && half == H)                                                                 \
-    return launch_kernel(atrex_sm100_fwd_umma1_kernel<D, F, H>, dim3(grid), dim3(kThreads1),                    \
-                         Cfg1<D, F, H>::kSmemBytes, stream, p);
+  const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
+#define X(D, F)                                                                                            \
+  if (head_dim == D && fp8 == F)                                                                           \
+    return launch_kernel(atrex_sm100_fwd_umma1_kernel<D, F>, dim3(grid), dim3(kThreads1), Cfg1<D, F>::kSmemBytes, \
+                         stream, p);
   ATREX_UMMA1_VARIANTS(X)
 #undef X
   return cudaErrorInvalidValue;

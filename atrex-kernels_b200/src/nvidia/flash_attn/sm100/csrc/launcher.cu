@@ -7,7 +7,6 @@
 // synchronises or reads device memory.
 #include <atomic>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "atrex_fa_sm100.h"
@@ -134,14 +133,7 @@ int check_params(const atrex_fa_sm100_params* p) {
   return ATREX_FA_OK;
 }
 
-enum Kernel { kKernelMma = 0, kKernelUmma2 = 1, kKernelUmma1 = 2, kKernelUmma1Half = 3 };
-
-// Development knob: ATREX_SM100_PREFILL_KERNEL=half sends BF16 head_dim-128 prefill to the two-CTAs-per-SM
-// variant of the single-tile kernel instead of the two-subtile kernel.
-bool prefer_half_prefill() {
-  static const bool v = [] { const char* e = std::getenv("ATREX_SM100_PREFILL_KERNEL"); return e != nullptr && std::strcmp(e, "half") == 0; }();
-  return v;
-}
+enum Kernel { kKernelMma = 0, kKernelUmma2 = 1, kKernelUmma1 = 2 };
 
 // Which kernel, how many splits, how much scratch - from graph-static sizes only.
 //   mma.sync kernel   : BF16 calls with at most 16 packed rows per (request, KV head) (plain decode), softcap,
@@ -161,9 +153,7 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   if (p->route == ATREX_FA_ROUTE_MMA) kernel = kKernelMma;
   else if (fp8) kernel = kKernelUmma1;
   else if (p->route == ATREX_FA_ROUTE_AUTO && (!tensor_ok || packed_max <= 16)) kernel = kKernelMma;
-  else if (packed_max > 128 && umma2_ok && p->num_splits <= 1 && !prefer_half_prefill()) kernel = kKernelUmma2;
-  else if (packed_max > 128 && p->num_splits <= 1 && umma1_has_half(p->head_dim, fp8) && prefer_half_prefill())
-    kernel = kKernelUmma1Half;
+  else if (packed_max > 128 && umma2_ok && p->num_splits <= 1) kernel = kKernelUmma2;
   else kernel = kKernelUmma1;
   r->kernel = kernel;
   r->route = kernel == kKernelMma ? ATREX_FA_ROUTE_MMA : ATREX_FA_ROUTE_UMMA;
@@ -177,7 +167,7 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
     tile_n = 128;
   } else {
     r->m_rows = umma1_rows_per_item();
-    tile_n = umma1_tile_n(p->head_dim, fp8, kernel == kKernelUmma1Half);
+    tile_n = umma1_tile_n(p->head_dim, fp8);
   }
   r->tile_n = tile_n;
   r->tiled = kernel == kKernelUmma2 || packed_max > r->m_rows;
@@ -381,7 +371,7 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   }
   if (st != ATREX_FA_OK) return st;
   for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
-  f.q_via_tma = r.kernel == kKernelUmma2 || (r.kernel >= kKernelUmma1 && umma1_q_via_tma(p->num_q_heads / p->num_kv_heads) &&
+  f.q_via_tma = r.kernel == kKernelUmma2 || (r.kernel == kKernelUmma1 && umma1_q_via_tma(p->num_q_heads / p->num_kv_heads) &&
                                              p->q_head_stride <= p->q_row_stride);
   if (f.q_via_tma) {
     st = encode_q_map(&f.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
@@ -434,7 +424,7 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
     return fail(ATREX_FA_CUDA_ERROR, "cudaEventRecord(profile_event_begin)", e);
   const int sms = p->sm_count > 0 ? p->sm_count : info->sm_count;
   if (r.kernel == kKernelUmma2) e = umma_launch(f, sms, stream);
-  else if (r.kernel >= kKernelUmma1) e = umma1_launch(f, p->head_dim, fp8, r.kernel == kKernelUmma1Half, sms, stream);
+  else if (r.kernel == kKernelUmma1) e = umma1_launch(f, p->head_dim, fp8, sms, stream);
   else e = mma_launch(f, p->head_dim, r.m_rows, stream);
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "launch of the attention kernel", e);
   if (p->profile_event_end != nullptr &&
