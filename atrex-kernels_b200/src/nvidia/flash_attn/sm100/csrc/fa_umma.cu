@@ -22,6 +22,7 @@
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a code, drains its
 // copies, frees TMEM and returns.
+#define ATREX_MBAR_SPIN_INLINE
 #include "fa_kernels.cuh"
 #include "umma.cuh"
 

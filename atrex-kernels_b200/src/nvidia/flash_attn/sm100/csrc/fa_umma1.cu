@@ -61,6 +61,14 @@ struct Cfg1 {
   static_assert(kBN / 2 >= 32, "each softmax thread takes at least one 32-column chunk");
 };
 
+// Development timeline: with -DATREX_UMMA1_TRACE CTA 0 records clock64() at the marked points.
+#ifdef ATREX_UMMA1_TRACE
+__device__ long long g_umma1_trace[8192];
+#define TRACE1(slot, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_umma1_trace[(slot) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE1(slot, idx) do { } while (0)
+#endif
+
 enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
 
 struct Item256 {
@@ -359,6 +367,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_smem), C::kKVBlock, 1024);
     // ring numbering: tile t of the CTA's whole run has K number 2t and V number 2t + 1
     uint32_t it_count = 0, base = 0, cp[2] = {0, 0};
+    [[maybe_unused]] uint32_t tt = 0;
     bool dead = false;
     auto issue_qk = [&](int buf, uint32_t slot) {
       if (lane == 0) {
@@ -379,6 +388,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       if (!decode_item256<BN>(p, item, it)) break;
       if (*(volatile int*)abort_flag) break;
       if (!mbar_wait(&bars[bQFull], it_count & 1u)) { dead = true; break; }
+      if (lane == 0) TRACE1(14, it_count);
       if (it.n_tiles == 0) {
         if (lane == 0) mbar_arrive(&bars[bQEmpty]);
         ++it_count;
@@ -397,10 +407,13 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
           const uint32_t slot_k = n_k % kRing;
           if (!mbar_wait(&bars[bKVFull + slot_k], (n_k / kRing) & 1u)) { dead = true; break; }
           tcgen05_fence_after();
+          if (lane == 0) TRACE1(8, tt);
           issue_qk((j + 1) & 1, slot_k);         // its S buffer held P(j-1), consumed by the earlier P V
         }
+        if (lane == 0) TRACE1(15, tt);
         const uint32_t slot_v = n_v % kRing;
         if (!mbar_wait(&bars[bKVFull + slot_v], (n_v / kRing) & 1u)) { dead = true; break; }
+        if (lane == 0) TRACE1(9, tt);
         const int tok0 = (it.tile_lo + j) * BN;
         if (tok0 + BN > it.kv_len) {
           // V rows past the end of the request may hold NaN: P is 0 there but 0 * NaN is NaN.
@@ -418,6 +431,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         if (!mbar_wait(&bars[bPFull + buf], cp[buf] & 1u)) { dead = true; break; }
         ++cp[buf];
         tcgen05_fence_after();
+        if (lane == 0) TRACE1(10, tt);
         if (lane == 0) {
           const uint64_t vd = v_desc0 + (uint64_t)((slot_v * C::kSlotBytes) >> 4);
 #pragma unroll
@@ -433,7 +447,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
           }
           umma_commit(&bars[bOFull]);
           umma_commit(&bars[bKVEmpty + slot_v]);
+          TRACE1(11, tt);
         }
+        ++tt;
       }
       if (dead) break;
       if (lane == 0) umma_commit(&bars[bQEmpty]);
@@ -455,11 +471,13 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     float* xchg = reinterpret_cast<float*>(smem + C::kOffXchg);            // [parity][half][row]
     constexpr int kGroupBar = 1, kGroup = kSoftmaxWarps1 * 32;
     uint32_t cs[2] = {0, 0}, co = 0, it_count = 0, cx = 0;
+    [[maybe_unused]] uint32_t tt = 0;   // tiles so far (trace index)
     bool dead = false;
     for (int item = blockIdx.x; !dead; item += step, ++it_count) {
       Item256 it;
       if (!decode_item256<BN>(p, item, it)) break;
       if (group_barrier_or(kGroupBar, kGroup, *(volatile int*)abort_flag != 0)) break;   // leave together
+      if (tid == 0) TRACE1(12, it_count);
       const int row = it.row0 + r;
       const int qi = min(row / p.group, max(it.q_len - 1, 0));
       const int hd = it.kvh * p.group + row % p.group;
@@ -502,19 +520,24 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         const uint32_t s_tmem = tmem_base + lane_off + buf * BN + h * N;   // own scores; P goes over them
         const int tok0 = (it.tile_lo + j) * BN;
         const bool need_mask = tok0 < full_lo || tok0 + BN > full_hi;
+        if (tid == 0) TRACE1(16, tt);
         if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) dead = true;
         ++cs[buf];
         tcgen05_fence_after();
+        if (tid == 0) TRACE1(0, tt);
+        if (tid == 128) TRACE1(6, tt);
         uint32_t s[N];
         float mx = -INFINITY;
         if (!dead)
           mx = need_mask ? half_max<D, kFp8, true>(s_tmem, s, tok0 + h * N, vis_lo, vis_hi)
                          : half_max<D, kFp8, false>(s_tmem, s, tok0 + h * N, vis_lo, vis_hi);
         // row maximum = max of the two halves, exchanged through shared memory (double-buffered)
+        if (tid == 0) TRACE1(1, tt);
         float* slot = xchg + (cx & 1u) * (2 * kRows);
         ++cx;
         slot[h * kRows + r] = mx;
         if (group_barrier_or(kGroupBar, kGroup, dead)) { dead = true; break; }
+        if (tid == 0) TRACE1(2, tt);
         mx = fmaxf(mx, slot[(h ^ 1) * kRows + r]) * scale_log2;
         float alpha = 1.f;
         if (mx > m_run + C::kThreshold) {  // also the first finite maximum of the row
@@ -523,6 +546,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         }
         const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + C::kShift;
         l_run = l_run * alpha + half_exp<D, kFp8>(s_tmem, s, scale_log2, neg_m);
+        if (tid == 0) TRACE1(3, tt);
         if (j > 0) {
           // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.
           if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;   // reported at the next group barrier
@@ -540,9 +564,13 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
             }
           }
         }
+        if (tid == 0) TRACE1(4, tt);
         tmem_st_wait();
         tcgen05_fence_before();
         mbar_arrive(&bars[bPFull + buf]);
+        if (tid == 0) TRACE1(5, tt);
+        if (tid == 128) TRACE1(7, tt);
+        ++tt;
       }
       if (!dead && it.n_tiles > 0) {
         if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;
@@ -608,6 +636,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         else if (p.lse != nullptr) p.lse[(int64_t)hd * p.total_q + q_row] = lse_l2 * kLn2;
       }
       tcgen05_fence_before();
+      if (tid == 0) TRACE1(13, it_count);
     }
   }
 
@@ -620,6 +649,12 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
 }
 
 }  // namespace
+
+#ifdef ATREX_UMMA1_TRACE
+extern "C" __attribute__((visibility("default"))) int atrex_fa_sm100_debug_trace1(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_umma1_trace, sizeof(long long) * n);
+}
+#endif
 
 bool umma1_supports(int head_dim) { return head_dim == 128 || head_dim == 256; }
 bool umma1_q_via_tma(int group) { return group >= 1 && group <= kRows && (kRows % group) == 0; }

@@ -43,7 +43,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
+#ifdef ATREX_MBAR_TEST_WAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#endif
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(done)
@@ -57,12 +61,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // kernel instead of hanging the GPU.  Each failed try_wait already blocks for a
 // hardware-defined slice, so the limit is seconds, far above any real wait.
 constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// The spinning part is kept out of line and rolled: a wait has a dozen call sites per kernel, and an
+// inlined, unrolled spin loop at each of them pushes the hot loops of the MMA-issuing and TMA-issuing
+// warps out of the instruction cache.
+#ifdef ATREX_MBAR_SPIN_INLINE   // for kernels that use setmaxnreg: no calls with their own register ABI
+__device__ __forceinline__
+#else
+static __device__ __noinline__   // one copy per translation unit
+#endif
+bool mbar_wait_slow(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 4096) __nanosleep(64);
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
 }
 
 // 4-D tiled TMA load into this CTA only.  Coordinates are innermost first.
