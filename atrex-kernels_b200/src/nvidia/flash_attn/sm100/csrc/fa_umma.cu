@@ -24,6 +24,7 @@
 // copies, frees TMEM and returns.
 #define ATREX_MBAR_SPIN_INLINE
 #include "fa_kernels.cuh"
+#include "softmax_math.cuh"
 #include "umma.cuh"
 
 namespace atrex_sm100 {
@@ -157,6 +158,12 @@ __device__ __forceinline__ bool produce_tiles(const FwdParams& p, const Item& it
 // reaches at most 2^8, harmless in BF16 / FP32, and the TMEM-resident O needs no rescale.
 constexpr float kRescaleThreshold = 8.f;
 
+// Pairs of every 8 whose exponential is a polynomial on the FMA pipe (the rest use the MUFU pipe).
+#ifndef ATREX_UMMA2_POLY_OF8
+#define ATREX_UMMA2_POLY_OF8 2
+#endif
+constexpr int kPolyOf8 = ATREX_UMMA2_POLY_OF8;
+
 // One 128-key tile for one row (= one thread): scores from TMEM, running max with the lazy-rescale
 // rule, P = 2^(s*scale - m) written back over the S columns as BF16 pairs, row sum folded into l.
 // Returns the factor the caller must apply to the O accumulated so far (1 when the max was kept).
@@ -194,20 +201,28 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
   }
   if (threadIdx.x == 0) TRACE(25, g_trace_idx);
   const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-  float sumv[4] = {0.f, 0.f, 0.f, 0.f};
+  const f32x2 scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
+  f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#ifdef ATREX_UMMA2_STORE_LAST
 #pragma unroll
   for (int c = 0; c < kBN / 32; ++c) {
     uint32_t packed[16];
+    exp32_bf16<kMask ? 0 : kPolyOf8>(&s[c * 32], scale2, negm2, sum2, packed);
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
-      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
-      sumv[(i >> 1) & 3] += p0 + p1;
-      packed[i >> 1] = pack_bf16(p0, p1);
-    }
+    for (int i = 0; i < 16; ++i) s[c * 16 + i] = packed[i];   // those scores are already consumed
+  }
+#pragma unroll
+  for (int c = 0; c < kBN / 64; ++c) tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+#else
+#pragma unroll
+  for (int c = 0; c < kBN / 32; ++c) {
+    uint32_t packed[16];
+    // masked scores are -inf and need ex2.approx's exact zero; elsewhere part of the work goes to the FMA pipe
+    exp32_bf16<kMask ? 0 : kPolyOf8>(&s[c * 32], scale2, negm2, sum2, packed);
     tmem_st16(s_tmem + c * 16, packed);
   }
-  const float sum = (sumv[0] + sumv[1]) + (sumv[2] + sumv[3]);
+#endif
+  const float sum = sum_of(sum2);
   l_run = l_run * alpha + sum;
   return alpha;
 }
@@ -323,17 +338,17 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       const uint64_t q_desc0 = umma_desc_sw128(q_addr, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(kv_addr, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(kv_addr, kBlockBytes, 1024);
+      // The whole warp runs the issue code and lane 0 issues: all operands are warp-uniform.
+      const uint32_t lead = lane == 0;
       auto issue_qk = [&](int w, uint32_t slot) {
-        if (lane == 0) {
-          const uint64_t qd = q_desc0 + (uint64_t)((w * kTileBytes) >> 4);
-          const uint64_t kd = k_desc0 + (uint64_t)((slot * kTileBytes) >> 4);
+        const uint64_t qd = q_desc0 + (uint64_t)((w * kTileBytes) >> 4);
+        const uint64_t kd = k_desc0 + (uint64_t)((slot * kTileBytes) >> 4);
 #pragma unroll
-          for (int ks = 0; ks < kHD / 16; ++ks) {
-            const uint32_t koff = ((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4;
-            umma_ss_f16(tmem_base + w * kBN, qd + koff, kd + koff, kIdescQK, ks > 0);
-          }
-          umma_commit(&bars[kSFull + w]);
+        for (int ks = 0; ks < kHD / 16; ++ks) {
+          const uint32_t koff = ((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4;
+          umma_ss_f16_lead(lead, tmem_base + w * kBN, qd + koff, kd + koff, kIdescQK, ks > 0);
         }
+        umma_commit_lead(lead, &bars[kSFull + w]);
       };
       for (int item = blockIdx.x; !dead; item += n_items_step) {
         Item it;
@@ -348,7 +363,7 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
             tcgen05_fence_after();
             issue_qk(0, slot_k);
             issue_qk(1, slot_k);
-            if (lane == 0) umma_commit(&bars[kKVEmpty + slot_k]);
+            umma_commit_lead(lead, &bars[kKVEmpty + slot_k]);
             for (int j = 0; j < it.n_tiles && !dead; ++j) {
               const bool more = j + 1 < it.n_tiles;
               const uint32_t slot_v = seq % kSlots;
@@ -380,25 +395,23 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
                 if (lane == 0) TRACE(8 + 2 * w, cp[w]);
                 ++cp[w];
                 tcgen05_fence_after();
-                if (lane == 0) {
+                {
+                  const uint64_t vd = v_desc0 + (uint64_t)((slot_v * kTileBytes) >> 4);
 #pragma unroll
                   for (int ks = 0; ks < kBN / 16; ++ks)
-                    umma_ts_f16(tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
-                                v_desc0 + (uint64_t)((slot_v * kTileBytes + ks * 2048) >> 4), kIdescPV,
-                                (j > 0) | (ks > 0));
-                  umma_commit(&bars[kOFull + w]);
+                    umma_ts_f16_lead(lead, tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
+                                     vd + (uint64_t)((ks * 2048) >> 4), kIdescPV, (j > 0) | (ks > 0));
+                  umma_commit_lead(lead, &bars[kOFull + w]);
                 }
                 if (more) issue_qk(w, slot_k2);
                 if (lane == 0) TRACE(9 + 2 * w, cp[w] - 1);
               }
               if (dead) break;
-              if (lane == 0) {
-                umma_commit(&bars[kKVEmpty + slot_v]);
-                if (more) umma_commit(&bars[kKVEmpty + slot_k2]);
-                TRACE(18, cp[0] - 1);
-              }
+              umma_commit_lead(lead, &bars[kKVEmpty + slot_v]);
+              if (more) umma_commit_lead(lead, &bars[kKVEmpty + slot_k2]);
+              if (lane == 0) TRACE(18, cp[0] - 1);
             }
-            if (!dead && lane == 0) umma_commit(&bars[kQEmpty]);
+            if (!dead) umma_commit_lead(lead, &bars[kQEmpty]);
           } while (false);
           if (dead || *(volatile int*)abort_flag) {
             if (dead && lane == 0) {

@@ -24,6 +24,7 @@
 #include <cuda_fp8.h>
 
 #include "fa_kernels.cuh"
+#include "softmax_math.cuh"
 #include "umma.cuh"
 
 namespace atrex_sm100 {
@@ -32,6 +33,10 @@ namespace {
 
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
+#ifndef ATREX_UMMA1_POLY_OF8
+#define ATREX_UMMA1_POLY_OF8 3
+#endif
+constexpr int kPolyOf8_1 = ATREX_UMMA1_POLY_OF8;   // pairs of every 8 whose exponential runs on the FMA pipe
 constexpr int kSoftmaxWarps1 = 8;                 // two threads per row: 2 x 4 warps
 constexpr int kMmaWarp1 = 8, kKWarp1 = 9, kVWarp1 = 10;   // warp 11 idles
 constexpr int kThreads1 = (kSoftmaxWarps1 + 4) * 32;       // 384 threads, up to 168 registers each
@@ -205,40 +210,25 @@ __device__ __forceinline__ float half_max(uint32_t s_tmem, uint32_t (&s)[Cfg1<D,
 
 // Step 2: P = 2^(s * scale + neg_m) (neg_m includes the FP8 shift) written over the first columns of the
 // thread's OWN score columns (BF16 pairs, or four E4M3 per column); returns the sum of the probabilities.
-template <int D, bool kFp8>
+template <int D, bool kFp8, int kPoly>
 __device__ __forceinline__ float half_exp(uint32_t s_tmem, const uint32_t (&s)[Cfg1<D, kFp8>::kBN / 2], float scale_log2,
                                           float neg_m) {
   constexpr int N = Cfg1<D, kFp8>::kBN / 2;
-  float sumv[4] = {0.f, 0.f, 0.f, 0.f};
+  const f32x2 scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
+  f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
   for (int c = 0; c < N / 32; ++c) {
     if constexpr (kFp8) {
       uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 2]), scale_log2, neg_m));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 3]), scale_log2, neg_m));
-        sumv[(i >> 2) & 3] += (p0 + p1) + (p2 + p3);
-        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
-        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(p2, p3), __NV_SATFINITE, __NV_E4M3);
-        packed[i >> 2] = lo | (hi << 16);
-      }
+      exp32_e4m3<kPoly>(&s[c * 32], scale2, negm2, sum2, packed);
       tmem_st8(s_tmem + c * 8, packed);
     } else {
       uint32_t packed[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i]), scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), scale_log2, neg_m));
-        sumv[(i >> 1) & 3] += p0 + p1;
-        packed[i >> 1] = pack_bf16(p0, p1);
-      }
+      exp32_bf16<kPoly>(&s[c * 32], scale2, negm2, sum2, packed);
       tmem_st16(s_tmem + c * 16, packed);
     }
   }
-  return (sumv[0] + sumv[1]) + (sumv[2] + sumv[3]);
+  return sum_of(sum2);
 }
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
@@ -369,19 +359,19 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     uint32_t it_count = 0, base = 0, cp[2] = {0, 0};
     [[maybe_unused]] uint32_t tt = 0;
     bool dead = false;
+    // The whole warp runs the issue code and lane 0 issues: all operands are warp-uniform.
+    const uint32_t lead = lane == 0;
     auto issue_qk = [&](int buf, uint32_t slot) {
-      if (lane == 0) {
-        const uint64_t kd = k_desc0 + (uint64_t)((slot * C::kSlotBytes) >> 4);
+      const uint64_t kd = k_desc0 + (uint64_t)((slot * C::kSlotBytes) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < C::kKStepsQK; ++ks) {
-          const uint32_t qoff = ((ks >> 2) * C::kQBlock + (ks & 3) * 32) >> 4;
-          const uint32_t koff = ((ks >> 2) * C::kKVBlock + (ks & 3) * 32) >> 4;
-          if constexpr (kFp8) umma_ss_f8(tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
-          else umma_ss_f16(tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
-        }
-        umma_commit(&bars[bSFull + buf]);
-        umma_commit(&bars[bKVEmpty + slot]);
+      for (int ks = 0; ks < C::kKStepsQK; ++ks) {
+        const uint32_t qoff = ((ks >> 2) * C::kQBlock + (ks & 3) * 32) >> 4;
+        const uint32_t koff = ((ks >> 2) * C::kKVBlock + (ks & 3) * 32) >> 4;
+        if constexpr (kFp8) umma_ss_f8_lead(lead, tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
+        else umma_ss_f16_lead(lead, tmem_base + buf * BN, q_desc0 + qoff, kd + koff, kIdescQK, ks > 0);
       }
+      umma_commit_lead(lead, &bars[bSFull + buf]);
+      umma_commit_lead(lead, &bars[bKVEmpty + slot]);
     };
     for (int item = blockIdx.x; !dead; item += step) {
       Item256 it;
@@ -432,7 +422,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++cp[buf];
         tcgen05_fence_after();
         if (lane == 0) TRACE1(10, tt);
-        if (lane == 0) {
+        {
           const uint64_t vd = v_desc0 + (uint64_t)((slot_v * C::kSlotBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < C::kKStepsPV; ++ks) {
@@ -441,18 +431,18 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
             constexpr int kPerHalf = C::kKStepsPV / 2;
             const uint32_t pcol = buf * BN + (ks / kPerHalf) * (BN / 2) + (ks % kPerHalf) * 8;
             if constexpr (kFp8)
-              umma_ts_f8(tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+              umma_ts_f8_lead(lead, tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
             else
-              umma_ts_f16(tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
+              umma_ts_f16_lead(lead, tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
           }
-          umma_commit(&bars[bOFull]);
-          umma_commit(&bars[bKVEmpty + slot_v]);
-          TRACE1(11, tt);
+          umma_commit_lead(lead, &bars[bOFull]);
+          umma_commit_lead(lead, &bars[bKVEmpty + slot_v]);
+          if (lane == 0) TRACE1(11, tt);
         }
         ++tt;
       }
       if (dead) break;
-      if (lane == 0) umma_commit(&bars[bQEmpty]);
+      umma_commit_lead(lead, &bars[bQEmpty]);
       base += 2u * (uint32_t)it.n_tiles;
       ++it_count;
     }
@@ -545,7 +535,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
           m_run = mx;
         }
         const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + C::kShift;
-        l_run = l_run * alpha + half_exp<D, kFp8>(s_tmem, s, scale_log2, neg_m);
+        // masked scores are -inf and need ex2.approx's exact zero; elsewhere part of the work goes to the FMA pipe
+        l_run = l_run * alpha + (need_mask ? half_exp<D, kFp8, 0>(s_tmem, s, scale_log2, neg_m)
+                                           : half_exp<D, kFp8, kPolyOf8_1>(s_tmem, s, scale_log2, neg_m));
         if (tid == 0) TRACE1(3, tt);
         if (j > 0) {
           // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.

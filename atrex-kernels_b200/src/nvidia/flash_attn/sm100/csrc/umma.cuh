@@ -84,6 +84,39 @@ __device__ __forceinline__ void umma_ts_f8(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
+// Warp-converged forms: every lane executes the call (so the compiler may keep the descriptors, which are
+// the same in all lanes, in uniform registers and do their address arithmetic once per warp), and the
+// lane whose `lead` is non-zero issues.  Exactly one lane of the warp must pass a non-zero `lead`.
+#define ATREX_UMMA_LEAD_FORM(NAME, KIND, A_CONSTRAINT, A_TYPE, A_OPERAND)                                        \
+  __device__ __forceinline__ void NAME(uint32_t lead, uint32_t d_tmem, A_TYPE a, uint64_t b_desc, uint32_t idesc, \
+                                       uint32_t accumulate) {                                                    \
+    asm volatile(                                                                                                \
+        "{\n"                                                                                                    \
+        ".reg .pred p, q;\n"                                                                                     \
+        "setp.ne.b32 p, %4, 0;\n"                                                                                \
+        "setp.ne.b32 q, %5, 0;\n"                                                                                \
+        "@q tcgen05.mma.cta_group::1.kind::" KIND " [%0], " A_OPERAND ", %2, %3, p;\n"                           \
+        "}\n" ::"r"(d_tmem),                                                                                     \
+        A_CONSTRAINT(a), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)                                     \
+        : "memory");                                                                                             \
+  }
+ATREX_UMMA_LEAD_FORM(umma_ss_f16_lead, "f16", "l", uint64_t, "%1")
+ATREX_UMMA_LEAD_FORM(umma_ts_f16_lead, "f16", "r", uint32_t, "[%1]")
+ATREX_UMMA_LEAD_FORM(umma_ss_f8_lead, "f8f6f4", "l", uint64_t, "%1")
+ATREX_UMMA_LEAD_FORM(umma_ts_f8_lead, "f8f6f4", "r", uint32_t, "[%1]")
+#undef ATREX_UMMA_LEAD_FORM
+
+__device__ __forceinline__ void umma_commit_lead(uint32_t lead, uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred q;\n"
+      "setp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(smem_u32(bar)),
+      "r"(lead)
+      : "memory");
+}
+
 // The mbarrier gets one arrival when every tcgen05.mma this thread issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
