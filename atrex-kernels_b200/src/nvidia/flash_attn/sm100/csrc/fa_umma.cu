@@ -45,7 +45,7 @@ constexpr int kOffQ = 0;
 constexpr int kOffKV = 2 * kTileBytes;
 constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
 // barriers (8 bytes each)
-enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kNumBars = 16 };
+enum Bar { kQFull = 0, kQEmpty = 1, kKVFull = 2, kKVEmpty = 6, kSFull = 10, kPFull = 12, kOFull = 14, kPLast = 16, kNumBars = 18 };
 constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (u32), abort flag (int)
 constexpr int kUmmaSmemBytes = kOffMisc + 16;
 
@@ -163,20 +163,18 @@ constexpr float kRescaleThreshold = 8.f;
 #define ATREX_UMMA2_POLY_OF8 2
 #endif
 constexpr int kPolyOf8 = ATREX_UMMA2_POLY_OF8;
+constexpr int kPFirstChunks = 3;   // 32-key chunks of P in the first hand-over (of 4)
 
-// One 128-key tile for one row (= one thread): scores from TMEM, running max with the lazy-rescale
-// rule, P = 2^(s*scale - m) written back over the S columns as BF16 pairs, row sum folded into l.
-// Returns the factor the caller must apply to the O accumulated so far (1 when the max was kept).
+// First step of a 128-key tile for one row (= one thread): the scores come from TMEM into registers,
+// masked columns become -inf, and the running maximum follows the lazy-rescale rule.  Returns the
+// factor the caller must apply to the O and the row sum accumulated so far (1 when the max was kept).
 template <bool kMask>
-__device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2, int tok0, int vis_lo, int vis_hi,
-                                              float& m_run, float& l_run) {
-  uint32_t s[kBN];
+__device__ __forceinline__ float tile_max(uint32_t s_tmem, uint32_t (&s)[kBN], float scale_log2, int tok0, int vis_lo,
+                                          int vis_hi, float& m_run) {
 #pragma unroll
   for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
   tmem_ld_wait();
   if (threadIdx.x == 0) TRACE(24, g_trace_idx);
-  // Several independent chains: with two softmax warps per scheduler there is little thread-level
-  // parallelism to hide the latency of one long max / add dependency chain.
   if (kMask) {
 #pragma unroll
     for (int i = 0; i < kBN; ++i) {
@@ -184,6 +182,8 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
       if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
     }
   }
+  // Several independent chains: with two softmax warps per scheduler there is little thread-level
+  // parallelism to hide the latency of one long dependency chain.
   float mxv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
   for (int i = 0; i < kBN; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
@@ -200,31 +200,22 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_tmem, float scale_log2,
     m_run = mx;
   }
   if (threadIdx.x == 0) TRACE(25, g_trace_idx);
-  const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-  const f32x2 scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
-  f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-#ifdef ATREX_UMMA2_STORE_LAST
+  return alpha;
+}
+
+// Second step, for the 32-key chunks [c0, c1): P = 2^(s*scale - m) written over the S columns as BF16
+// pairs; the probabilities add into sum2.
+template <bool kMask>
+__device__ __forceinline__ void tile_exp(uint32_t s_tmem, const uint32_t (&s)[kBN], int c0, int c1, f32x2 scale2,
+                                         f32x2 negm2, f32x2 (&sum2)[2]) {
 #pragma unroll
-  for (int c = 0; c < kBN / 32; ++c) {
-    uint32_t packed[16];
-    exp32_bf16<kMask ? 0 : kPolyOf8>(&s[c * 32], scale2, negm2, sum2, packed);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) s[c * 16 + i] = packed[i];   // those scores are already consumed
-  }
-#pragma unroll
-  for (int c = 0; c < kBN / 64; ++c) tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-#else
-#pragma unroll
-  for (int c = 0; c < kBN / 32; ++c) {
+  for (int c = c0; c < c1; ++c) {
     uint32_t packed[16];
     // masked scores are -inf and need ex2.approx's exact zero; elsewhere part of the work goes to the FMA pipe
     exp32_bf16<kMask ? 0 : kPolyOf8>(&s[c * 32], scale2, negm2, sum2, packed);
     tmem_st16(s_tmem + c * 16, packed);
+    if (threadIdx.x == 0) TRACE(26 + c, g_trace_idx);
   }
-#endif
-  const float sum = sum_of(sum2);
-  l_run = l_run * alpha + sum;
-  return alpha;
 }
 
 }  // namespace
@@ -259,6 +250,7 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
     for (int w = 0; w < 2; ++w) {
       mbar_init(&bars[kSFull + w], 1);
       mbar_init(&bars[kPFull + w], kBM);
+      mbar_init(&bars[kPLast + w], kBM);
       mbar_init(&bars[kOFull + w], 1);
     }
     fence_barrier_init();
@@ -398,9 +390,15 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
                 {
                   const uint64_t vd = v_desc0 + (uint64_t)((slot_v * kTileBytes) >> 4);
 #pragma unroll
-                  for (int ks = 0; ks < kBN / 16; ++ks)
+                  for (int ks = 0; ks < kPFirstChunks * 2; ++ks)
                     umma_ts_f16_lead(lead, tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
                                      vd + (uint64_t)((ks * 2048) >> 4), kIdescPV, (j > 0) | (ks > 0));
+                  if (!mbar_wait(&bars[kPLast + w], (cp[w] - 1) & 1u)) { dead = true; break; }
+                  tcgen05_fence_after();
+#pragma unroll
+                  for (int ks = kPFirstChunks * 2; ks < kBN / 16; ++ks)
+                    umma_ts_f16_lead(lead, tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
+                                     vd + (uint64_t)((ks * 2048) >> 4), kIdescPV, 1u);
                   umma_commit_lead(lead, &bars[kOFull + w]);
                 }
                 if (more) issue_qk(w, slot_k2);
@@ -472,30 +470,45 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
 #endif
         if (tid == 0) TRACE(0, cs - 1);
         if (tid == 128) TRACE(4, cs - 1);
-        const float alpha = need_mask ? softmax_tile<true>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run)
-                                      : softmax_tile<false>(s_tmem, scale_log2, tok0, vis_lo, vis_hi, m_run, l_run);
+        uint32_t s[kBN];
+        const float alpha = need_mask ? tile_max<true>(s_tmem, s, scale_log2, tok0, vis_lo, vis_hi, m_run)
+                                      : tile_max<false>(s_tmem, s, scale_log2, tok0, vis_lo, vis_hi, m_run);
         if (j > 0) {
-          // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.
+          // O(j-1) must be complete before it is rescaled, and rescaled before the first part of P V(j) adds to it.
           if (!mbar_wait(&bars[kOFull + w], co & 1u)) { dead = true; break; }
           ++co;
           tcgen05_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            // narrow chunks: the tile's 128 scores stay in registers across this rare step
 #pragma unroll
-            for (int c = 0; c < kHD / 32; ++c) {
-              uint32_t v[32];
-              tmem_ld32(o_tmem + c * 32, v);
+            for (int c = 0; c < kHD / 16; ++c) {
+              uint32_t v[16];
+              tmem_ld16(o_tmem + c * 16, v);
               tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-              tmem_st32(o_tmem + c * 32, v);
+              for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tmem_st16(o_tmem + c * 16, v);
             }
           }
         }
+        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+        const f32x2 scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
+        f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+        // P is handed over in two parts, so that the tensor core multiplies the first three quarters
+        // by V while the last quarter's exponentials are still being computed.
+        if (need_mask) tile_exp<true>(s_tmem, s, 0, kPFirstChunks, scale2, negm2, sum2);
+        else tile_exp<false>(s_tmem, s, 0, kPFirstChunks, scale2, negm2, sum2);
+        tmem_st_wait();
+        tcgen05_fence_before();
+        mbar_arrive(&bars[kPFull + w]);
         if (tid == 0) TRACE(1, cs - 1);
+        if (need_mask) tile_exp<true>(s_tmem, s, kPFirstChunks, kBN / 32, scale2, negm2, sum2);
+        else tile_exp<false>(s_tmem, s, kPFirstChunks, kBN / 32, scale2, negm2, sum2);
+        l_run = l_run * alpha + sum_of(sum2);
         tmem_st_wait();
         if (tid == 0) TRACE(2, cs - 1);
         tcgen05_fence_before();
-        mbar_arrive(&bars[kPFull + w]);
+        mbar_arrive(&bars[kPLast + w]);
         if (tid == 0) TRACE(3, cs - 1);
         if (tid == 128) TRACE(7, cs - 1);
       }
