@@ -327,14 +327,14 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       uint32_t it_count = 0, seq = 0, cp[2] = {0, 0};
       bool dead = false;
       // Descriptors are built once; per instruction only the start-address field (bytes >> 4) moves.
-      const uint64_t q_desc0 = umma_desc_sw128(q_addr, 16, 1024);
-      const uint64_t k_desc0 = umma_desc_sw128(kv_addr, 16, 1024);
-      const uint64_t v_desc0 = umma_desc_sw128(kv_addr, kBlockBytes, 1024);
+      const UmmaDesc q_desc0 = umma_desc_split(umma_desc_sw128(q_addr, 16, 1024));
+      const UmmaDesc k_desc0 = umma_desc_split(umma_desc_sw128(kv_addr, 16, 1024));
+      const UmmaDesc v_desc0 = umma_desc_split(umma_desc_sw128(kv_addr, kBlockBytes, 1024));
       // The whole warp runs the issue code and lane 0 issues: all operands are warp-uniform.
       const uint32_t lead = lane == 0;
       auto issue_qk = [&](int w, uint32_t slot) {
-        const uint64_t qd = q_desc0 + (uint64_t)((w * kTileBytes) >> 4);
-        const uint64_t kd = k_desc0 + (uint64_t)((slot * kTileBytes) >> 4);
+        const UmmaDesc qd = q_desc0 + (uint32_t)((w * kTileBytes) >> 4);
+        const UmmaDesc kd = k_desc0 + (uint32_t)((slot * kTileBytes) >> 4);
 #pragma unroll
         for (int ks = 0; ks < kHD / 16; ++ks) {
           const uint32_t koff = ((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4;
@@ -388,17 +388,17 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
                 ++cp[w];
                 tcgen05_fence_after();
                 {
-                  const uint64_t vd = v_desc0 + (uint64_t)((slot_v * kTileBytes) >> 4);
+                  const UmmaDesc vd = v_desc0 + (uint32_t)((slot_v * kTileBytes) >> 4);
 #pragma unroll
                   for (int ks = 0; ks < kPFirstChunks * 2; ++ks)
                     umma_ts_f16_lead(lead, tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
-                                     vd + (uint64_t)((ks * 2048) >> 4), kIdescPV, (j > 0) | (ks > 0));
+                                     vd + (uint32_t)((ks * 2048) >> 4), kIdescPV, (j > 0) | (ks > 0));
                   if (!mbar_wait(&bars[kPLast + w], (cp[w] - 1) & 1u)) { dead = true; break; }
                   tcgen05_fence_after();
 #pragma unroll
                   for (int ks = kPFirstChunks * 2; ks < kBN / 16; ++ks)
                     umma_ts_f16_lead(lead, tmem_base + 2 * kBN + w * kHD, tmem_base + w * kBN + ks * 8,
-                                     vd + (uint64_t)((ks * 2048) >> 4), kIdescPV, 1u);
+                                     vd + (uint32_t)((ks * 2048) >> 4), kIdescPV, 1u);
                   umma_commit_lead(lead, &bars[kOFull + w]);
                 }
                 if (more) issue_qk(w, slot_k2);

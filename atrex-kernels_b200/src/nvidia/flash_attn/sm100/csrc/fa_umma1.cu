@@ -352,9 +352,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t kIdescQK = umma_idesc(kRows, BN, C::kFmt, C::kFmt, 0, 0);
     constexpr uint32_t kIdescPV = umma_idesc(kRows, D, C::kFmt, C::kFmt, 0, 1);
-    const uint64_t q_desc0 = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
-    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_smem), 16, 1024);
-    const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_smem), C::kKVBlock, 1024);
+    const UmmaDesc q_desc0 = umma_desc_split(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
+    const UmmaDesc k_desc0 = umma_desc_split(umma_desc_sw128(smem_u32(kv_smem), 16, 1024));
+    const UmmaDesc v_desc0 = umma_desc_split(umma_desc_sw128(smem_u32(kv_smem), C::kKVBlock, 1024));
     // ring numbering: tile t of the CTA's whole run has K number 2t and V number 2t + 1
     uint32_t it_count = 0, base = 0, cp[2] = {0, 0};
     [[maybe_unused]] uint32_t tt = 0;
@@ -362,7 +362,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     // The whole warp runs the issue code and lane 0 issues: all operands are warp-uniform.
     const uint32_t lead = lane == 0;
     auto issue_qk = [&](int buf, uint32_t slot) {
-      const uint64_t kd = k_desc0 + (uint64_t)((slot * C::kSlotBytes) >> 4);
+      const UmmaDesc kd = k_desc0 + (uint32_t)((slot * C::kSlotBytes) >> 4);
 #pragma unroll
       for (int ks = 0; ks < C::kKStepsQK; ++ks) {
         const uint32_t qoff = ((ks >> 2) * C::kQBlock + (ks & 3) * 32) >> 4;
@@ -423,7 +423,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         tcgen05_fence_after();
         if (lane == 0) TRACE1(10, tt);
         {
-          const uint64_t vd = v_desc0 + (uint64_t)((slot_v * C::kSlotBytes) >> 4);
+          const UmmaDesc vd = v_desc0 + (uint32_t)((slot_v * C::kSlotBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < C::kKStepsPV; ++ks) {
             const uint32_t voff = (ks * C::kPVStepBytes) >> 4;

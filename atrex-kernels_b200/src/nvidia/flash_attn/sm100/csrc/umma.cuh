@@ -87,24 +87,53 @@ __device__ __forceinline__ void umma_ts_f8(uint32_t d_tmem, uint32_t a_tmem, uin
 // Warp-converged forms: every lane executes the call (so the compiler may keep the descriptors, which are
 // the same in all lanes, in uniform registers and do their address arithmetic once per warp), and the
 // lane whose `lead` is non-zero issues.  Exactly one lane of the warp must pass a non-zero `lead`.
-#define ATREX_UMMA_LEAD_FORM(NAME, KIND, A_CONSTRAINT, A_TYPE, A_OPERAND)                                        \
-  __device__ __forceinline__ void NAME(uint32_t lead, uint32_t d_tmem, A_TYPE a, uint64_t b_desc, uint32_t idesc, \
-                                       uint32_t accumulate) {                                                    \
-    asm volatile(                                                                                                \
-        "{\n"                                                                                                    \
-        ".reg .pred p, q;\n"                                                                                     \
-        "setp.ne.b32 p, %4, 0;\n"                                                                                \
-        "setp.ne.b32 q, %5, 0;\n"                                                                                \
-        "@q tcgen05.mma.cta_group::1.kind::" KIND " [%0], " A_OPERAND ", %2, %3, p;\n"                           \
-        "}\n" ::"r"(d_tmem),                                                                                     \
-        A_CONSTRAINT(a), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)                                     \
-        : "memory");                                                                                             \
+// A shared-memory descriptor is passed as its two 32-bit halves: only the low half (start address >> 4 in
+// bits 0-13) changes between the instructions of a tile, so stepping through a tile is one 32-bit add per
+// operand instead of 64-bit arithmetic -- the issuing warp shares its scheduler with two softmax warps,
+// and every instruction it needs per MMA delays the next MMA.
+struct UmmaDesc {
+  uint32_t lo, hi;
+  __device__ __forceinline__ UmmaDesc operator+(uint32_t bytes_shr4) const { return UmmaDesc{lo + bytes_shr4, hi}; }
+};
+__device__ __forceinline__ UmmaDesc umma_desc_split(uint64_t d) { return UmmaDesc{(uint32_t)d, (uint32_t)(d >> 32)}; }
+
+#define ATREX_UMMA_SS_LEAD(NAME, KIND)                                                                        \
+  __device__ __forceinline__ void NAME(uint32_t lead, uint32_t d_tmem, UmmaDesc a, UmmaDesc b, uint32_t idesc, \
+                                       uint32_t accumulate) {                                                 \
+    asm volatile(                                                                                             \
+        "{\n"                                                                                                 \
+        ".reg .pred p, q;\n"                                                                                  \
+        ".reg .b64 da, db;\n"                                                                                 \
+        "mov.b64 da, {%1, %2};\n"                                                                             \
+        "mov.b64 db, {%3, %4};\n"                                                                             \
+        "setp.ne.b32 p, %6, 0;\n"                                                                             \
+        "setp.ne.b32 q, %7, 0;\n"                                                                             \
+        "@q tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %5, p;\n"                                   \
+        "}\n" ::"r"(d_tmem),                                                                                  \
+        "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate), "r"(lead)                    \
+        : "memory");                                                                                          \
   }
-ATREX_UMMA_LEAD_FORM(umma_ss_f16_lead, "f16", "l", uint64_t, "%1")
-ATREX_UMMA_LEAD_FORM(umma_ts_f16_lead, "f16", "r", uint32_t, "[%1]")
-ATREX_UMMA_LEAD_FORM(umma_ss_f8_lead, "f8f6f4", "l", uint64_t, "%1")
-ATREX_UMMA_LEAD_FORM(umma_ts_f8_lead, "f8f6f4", "r", uint32_t, "[%1]")
-#undef ATREX_UMMA_LEAD_FORM
+#define ATREX_UMMA_TS_LEAD(NAME, KIND)                                                                         \
+  __device__ __forceinline__ void NAME(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, UmmaDesc b, uint32_t idesc, \
+                                       uint32_t accumulate) {                                                  \
+    asm volatile(                                                                                              \
+        "{\n"                                                                                                  \
+        ".reg .pred p, q;\n"                                                                                   \
+        ".reg .b64 db;\n"                                                                                      \
+        "mov.b64 db, {%2, %3};\n"                                                                              \
+        "setp.ne.b32 p, %5, 0;\n"                                                                              \
+        "setp.ne.b32 q, %6, 0;\n"                                                                              \
+        "@q tcgen05.mma.cta_group::1.kind::" KIND " [%0], [%1], db, %4, p;\n"                                  \
+        "}\n" ::"r"(d_tmem),                                                                                   \
+        "r"(a_tmem), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate), "r"(lead)                              \
+        : "memory");                                                                                           \
+  }
+ATREX_UMMA_SS_LEAD(umma_ss_f16_lead, "f16")
+ATREX_UMMA_TS_LEAD(umma_ts_f16_lead, "f16")
+ATREX_UMMA_SS_LEAD(umma_ss_f8_lead, "f8f6f4")
+ATREX_UMMA_TS_LEAD(umma_ts_f8_lead, "f8f6f4")
+#undef ATREX_UMMA_SS_LEAD
+#undef ATREX_UMMA_TS_LEAD
 
 __device__ __forceinline__ void umma_commit_lead(uint32_t lead, uint64_t* bar) {
   asm volatile(
