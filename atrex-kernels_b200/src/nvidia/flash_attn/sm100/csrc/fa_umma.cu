@@ -163,7 +163,10 @@ constexpr float kRescaleThreshold = 8.f;
 #define ATREX_UMMA2_POLY_OF8 2
 #endif
 constexpr int kPolyOf8 = ATREX_UMMA2_POLY_OF8;
-constexpr int kPFirstChunks = 3;   // 32-key chunks of P in the first hand-over (of 4)
+#ifndef ATREX_UMMA2_P_FIRST_CHUNKS
+#define ATREX_UMMA2_P_FIRST_CHUNKS 3
+#endif
+constexpr int kPFirstChunks = ATREX_UMMA2_P_FIRST_CHUNKS;   // 32-key chunks of P in the first hand-over (of 4)
 
 // First step of a 128-key tile for one row (= one thread): the scores come from TMEM into registers,
 // masked columns become -inf, and the running maximum follows the lazy-rescale rule.  Returns the
@@ -171,27 +174,41 @@ constexpr int kPFirstChunks = 3;   // 32-key chunks of P in the first hand-over 
 template <bool kMask>
 __device__ __forceinline__ float tile_max(uint32_t s_tmem, uint32_t (&s)[kBN], float scale_log2, int tok0, int vis_lo,
                                           int vis_hi, float& m_run) {
+  // The second half of the row loads while the first half is reduced.  Eight independent chains: with one
+  // softmax warp per scheduler active at a time there is no thread-level parallelism to hide the latency of
+  // a long dependency chain.
+  float mxv[8];
 #pragma unroll
-  for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-  tmem_ld_wait();
-  if (threadIdx.x == 0) TRACE(24, g_trace_idx);
-  if (kMask) {
+  for (int i = 0; i < 8; ++i) mxv[i] = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kBN; ++i) {
-      const int col = tok0 + i;
-      if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
+  for (int half = 0; half < 2; ++half) {
+    if (half == 0) {
+#pragma unroll
+      for (int c = 0; c < kBN / 64; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+    }
+    tmem_ld_wait();
+    if (half == 0) {
+#pragma unroll
+      for (int c = kBN / 64; c < kBN / 32; ++c)
+        tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+    }
+    if (kMask) {
+#pragma unroll
+      for (int i = half * (kBN / 2); i < (half + 1) * (kBN / 2); ++i) {
+        const int col = tok0 + i;
+        if (col < vis_lo || col >= vis_hi) s[i] = 0xff800000u;  // -inf
+      }
+    }
+#pragma unroll
+    for (int i = half * (kBN / 2); i < (half + 1) * (kBN / 2); i += 16) {   // 3-input max: half the instructions
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        mxv[u] = fmax3(mxv[u], __uint_as_float(s[i + 2 * u]), __uint_as_float(s[i + 2 * u + 1]));
     }
   }
-  // Several independent chains: with two softmax warps per scheduler there is little thread-level
-  // parallelism to hide the latency of one long dependency chain.
-  float mxv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int i = 0; i < kBN; i += 8) {   // 3-input max: half the instructions of a pairwise reduction
-    mxv[0] = fmax3(mxv[0], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-    mxv[1] = fmax3(mxv[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-    mxv[2] = fmax3(mxv[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-    mxv[3] = fmax3(mxv[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-  }
+  if (threadIdx.x == 0) TRACE(24, g_trace_idx);
+  mxv[0] = fmaxf(mxv[0], mxv[4]); mxv[1] = fmaxf(mxv[1], mxv[5]);
+  mxv[2] = fmaxf(mxv[2], mxv[6]); mxv[3] = fmaxf(mxv[3], mxv[7]);
   float mx = fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3]));
   mx *= scale_log2;
   float alpha = 1.f;
@@ -356,6 +373,9 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
             issue_qk(0, slot_k);
             issue_qk(1, slot_k);
             umma_commit_lead(lead, &bars[kKVEmpty + slot_k]);
+            // Q is last read by the item's last S = Q K^T: releasing it there, not after the last P V, lets the
+            // next item's Q tiles load under this item's last tile and epilogue.
+            if (it.n_tiles == 1) umma_commit_lead(lead, &bars[kQEmpty]);
             for (int j = 0; j < it.n_tiles && !dead; ++j) {
               const bool more = j + 1 < it.n_tiles;
               const uint32_t slot_v = seq % kSlots;
@@ -407,9 +427,9 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
               if (dead) break;
               umma_commit_lead(lead, &bars[kKVEmpty + slot_v]);
               if (more) umma_commit_lead(lead, &bars[kKVEmpty + slot_k2]);
+              if (j + 2 == it.n_tiles) umma_commit_lead(lead, &bars[kQEmpty]);
               if (lane == 0) TRACE(18, cp[0] - 1);
             }
-            if (!dead) umma_commit_lead(lead, &bars[kQEmpty]);
           } while (false);
           if (dead || *(volatile int*)abort_flag) {
             if (dead && lane == 0) {

@@ -389,6 +389,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         if (!mbar_wait(&bars[bKVFull + slot_k], (base / kRing) & 1u)) { dead = true; break; }
         tcgen05_fence_after();
         issue_qk(0, slot_k);
+        // Q is last read by the item's last S = Q K^T: releasing it there, not after the last P V, lets the
+        // next item's Q load under this item's last tile and epilogue.
+        if (it.n_tiles == 1) umma_commit_lead(lead, &bars[bQEmpty]);
       }
       for (int j = 0; j < it.n_tiles && !dead; ++j) {
         const uint32_t n_v = base + 2 * j + 1;   // V(j)
@@ -399,6 +402,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
           tcgen05_fence_after();
           if (lane == 0) TRACE1(8, tt);
           issue_qk((j + 1) & 1, slot_k);         // its S buffer held P(j-1), consumed by the earlier P V
+          if (j + 2 == it.n_tiles) umma_commit_lead(lead, &bars[bQEmpty]);
         }
         if (lane == 0) TRACE1(15, tt);
         const uint32_t slot_v = n_v % kRing;
@@ -442,7 +446,6 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++tt;
       }
       if (dead) break;
-      umma_commit_lead(lead, &bars[bQEmpty]);
       base += 2u * (uint32_t)it.n_tiles;
       ++it_count;
     }
