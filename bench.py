@@ -70,7 +70,7 @@ WORKLOADS = {
 # DRAM bytes per algorithmic byte of the dominant kernel, from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum on the small case of the same kernel; traffic grows in proportion
 # to the K/V bytes a launch reads, so the ratio carries to the full-size launch).
-NCU_TRAFFIC_RATIO = {"decode_q1": 1.0247, "decode_q1_small": 1.0247, "decode_q4_window": 1.0585, "decode_q4_small": 1.0585}
+NCU_TRAFFIC_RATIO = {"decode_q1": 1.0241, "decode_q1_small": 1.0241, "decode_q4_window": 1.0588, "decode_q4_small": 1.0588}
 E2E_MAX_BYTES = 8 << 30   # largest Q the end-to-end leg stages in pinned host memory
 KIND = {
     "decode": dict(metric="paged_decode_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
