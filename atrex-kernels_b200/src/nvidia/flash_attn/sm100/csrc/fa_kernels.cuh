@@ -1,5 +1,6 @@
 // Entry points each kernel translation unit gives the C-ABI launcher.
 #pragma once
+#include <cuda_bf16.h>
 
 #include "fa_params.cuh"
 
@@ -44,5 +45,22 @@ cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream
 // order[batch], tile_prefix[batch + 1] for row tiles of m_rows packed rows
 cudaError_t plan_launch(const FwdParams& p, int m_rows, int32_t* order, int32_t* tile_prefix,
                         cudaStream_t stream);
+
+// ---- kv_write.cu: scatter of new K/V rows into the paged pools (optional BF16 -> E4M3 quantisation) ----
+// Strides in elements of the respective tensor; scales are per KV head (head stride 0 = one scale per tensor).
+struct KvWriteParams {
+  const __nv_bfloat16* key;
+  const __nv_bfloat16* value;
+  void* key_cache;
+  void* value_cache;
+  const long long* slot_mapping;
+  const float* k_scale;
+  const float* v_scale;
+  long long k_token_stride, k_head_stride, v_token_stride, v_head_stride;
+  long long kc_page_stride, kc_row_stride, kc_head_stride, vc_page_stride, vc_row_stride, vc_head_stride;
+  long long k_scale_head_stride, v_scale_head_stride;
+  int num_tokens, num_kv_heads, head_dim, page_size;
+};
+cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cudaStream_t stream);
 
 }  // namespace atrex_sm100

@@ -64,17 +64,24 @@ WORKLOADS = {
     "decode_q4_small": dict(kind="decode", batch=32, q_len=4, hq=64, hkv=4, d=128, page=128, kv_lo=32768,
                             kv_hi=32768, pool=32 * 256 + 64, window=(4095, 0), sink=True, lse=True,
                             scaling="weak"),
+    # KV-cache write path (the step before attention): one prefill chunk of new tokens scattered into the paged
+    # pools, BF16 cache and FP8 E4M3 cache (per-head scales); 0.5 GB of K/V rows per step (4x L2)
+    "kv_write": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=False, scaling="weak"),
+    "kv_write_fp8": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=True, scaling="weak"),
+    "kv_write_small": dict(kind="kv_write", tokens=65536, hkv=8, d=128, page=64, fp8=False, scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
 }
 # DRAM bytes per algorithmic byte of the dominant kernel, from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum on the small case of the same kernel; traffic grows in proportion
 # to the K/V bytes a launch reads, so the ratio carries to the full-size launch).
-NCU_TRAFFIC_RATIO = {"decode_q1": 1.0241, "decode_q1_small": 1.0241, "decode_q4_window": 1.0588, "decode_q4_small": 1.0588}
+NCU_TRAFFIC_RATIO = {"kv_write": 1.0, "kv_write_small": 1.0, "kv_write_fp8": 1.0,
+                     "decode_q1": 1.0241, "decode_q1_small": 1.0241, "decode_q4_window": 1.0588, "decode_q4_small": 1.0588}
 E2E_MAX_BYTES = 8 << 30   # largest Q the end-to-end leg stages in pinned host memory
 KIND = {
     "decode": dict(metric="paged_decode_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
     "prefill": dict(metric="paged_prefill_tensor_throughput", unit="TFLOP/s", scale=1e12, bound="tensor"),
+    "kv_write": dict(metric="kv_cache_write_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
 }
 
 
@@ -296,9 +303,25 @@ def run_reference(args, spec, rank, world):
     if rank != 0:
         return
     kind = KIND[spec["kind"]]
-    q_lens, kv_lens = draw_lengths(spec, 1729)
     steps, warm = max(1, args.steps), max(0, args.warmup)
     per_step = max(2.0, min(20.0, 120.0 / (steps + warm)))
+    if spec["kind"] == "kv_write":
+        values, sample, total_t = [], None, 0.0
+        for _ in range(min(steps, 8)):
+            sample, t = kv_write_cpu(spec, 1729, per_step)
+            values.append(sample["value"])
+            total_t += t
+        value = statistics.median(values)
+        print(json.dumps(dict(
+            impl="reference", metric=kind["metric"], value=value, unit=kind["unit"], n_gpus=args.gpus,
+            steps=len(values), warmup=0, ms_per_step=total_t / len(values) * 1e3, higher_is_better=True,
+            scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+            config=dict(workload=args.workload, new_tokens=spec["tokens"], num_kv_heads=spec["hkv"],
+                        head_dim=spec["d"], page_size=spec["page"]),
+            cpu_baseline=dict(sample, value=value),
+            e2e=dict(value=value, unit=kind["unit"], h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
+        return
+    q_lens, kv_lens = draw_lengths(spec, 1729)
     for _ in range(min(warm, 1)):
         cpu_baseline(spec, q_lens, kv_lens, 1729, budget_s=1.0)
     values, sample, total_t = [], None, 0.0
@@ -314,6 +337,155 @@ def run_reference(args, spec, rank, world):
                 cpu_baseline=dict(sample, value=value),
                 e2e=dict(value=value, unit=kind["unit"], h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
+
+
+def kv_write_inputs(spec, seed, device, torch):
+    """One step's new K/V rows, empty pools and a slot mapping that fills random pages (a block table's order)."""
+    tokens, hkv, d, page = spec["tokens"], spec["hkv"], spec["d"], spec["page"]
+    pages = tokens // page + 64
+    g = torch.Generator(device=device).manual_seed(seed)
+    key = torch.randn(tokens, hkv, d, device=device, generator=g).bfloat16()
+    value = torch.randn(tokens, hkv, d, device=device, generator=g).bfloat16()
+    dtype = torch.float8_e4m3fn if spec["fp8"] else torch.bfloat16
+    cache = torch.zeros(pages, 2, page, hkv, d, dtype=torch.uint8 if spec["fp8"] else dtype, device=device)
+    if spec["fp8"]:
+        cache = cache.view(dtype)
+    page_order = torch.randperm(pages, device=device, generator=g)[: tokens // page]
+    slots = (page_order[:, None] * page + torch.arange(page, device=device)[None, :]).reshape(-1).to(torch.int64)
+    scales = None
+    if spec["fp8"]:
+        scales = (0.5 + 0.125 * torch.arange(hkv, dtype=torch.float32, device=device),
+                  1.0 + 0.0625 * torch.arange(hkv, dtype=torch.float32, device=device))
+    return key, value, cache[:, 0], cache[:, 1], slots, scales
+
+
+def kv_write_cpu(spec, seed, budget_s):
+    """The oracle's scatter (numpy, one thread) over a bounded sample of the step's tokens."""
+    import numpy as np
+    from oracle import kv_cache_oracle
+    hkv, d, page = spec["hkv"], spec["d"], spec["page"]
+    rng = np.random.default_rng(seed)
+    sample = 4096
+    key = rng.standard_normal((sample, hkv, d), dtype=np.float32)
+    value = rng.standard_normal((sample, hkv, d), dtype=np.float32)
+    slots = rng.permutation(sample).astype(np.int64)
+    kc = np.zeros((sample // page, page, hkv, d), dtype=np.float32)
+    vc = np.zeros_like(kc)
+    scale = np.linspace(0.5, 1.5, hkv).astype(np.float32)
+    done, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < budget_s:
+        kv_cache_oracle.write_kv_cache(key, value, kc, vc, slots, scale, scale, fp8=spec["fp8"])
+        done += sample
+    t = time.perf_counter() - t0
+    work = kv_cache_oracle.algorithmic_bytes(done, hkv, d, spec["fp8"])
+    return dict(value=work / t / 1e9, unit="GB/s", cores=1, kind="port",
+                sample=f"oracle scatter of {done} of the step's {spec['tokens']} tokens, {t:.1f} s"), t
+
+
+def run_kv_write(args, spec, rank, world, local):
+    """KV-cache write workload: same JSON contract, the kernel timed by CUDA events around each call."""
+    import torch
+    import torch.distributed as dist
+    from atrex.src.nvidia.flash_attn.sm100 import kv_cache, runtime
+    from oracle import kv_cache_oracle
+
+    kind = KIND["kv_write"]
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    runtime.prewarm(device)
+    key, value, kc, vc, slots, scales = kv_write_inputs(spec, 1729 + 1000 * rank, device, torch)
+    ks, vs = scales if scales else (None, None)
+    work = kv_cache_oracle.algorithmic_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"])
+    warmup = max(3, args.warmup)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        kv_cache.write_kv_cache(key, value, kc, vc, slots, ks, vs)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = start.elapsed_time(stop)
+    # the kernel alone: one event pair per call, calls queued back to back (one kernel per call)
+    n_timed = min(args.steps, 50)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
+    for a, b in pairs:
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    kernel_ms = sum(a.elapsed_time(b) for a, b in pairs) / n_timed
+    # end to end: the step's rows and slot ids come from pinned host memory; the cache is resident device state
+    host = dict(key=key.cpu().pin_memory(), value=value.cpu().pin_memory(), slots=slots.cpu().pin_memory())
+    done = torch.zeros(1, dtype=torch.int64).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+
+    def e2e_step():
+        key.copy_(host["key"], non_blocking=True)
+        value.copy_(host["value"], non_blocking=True)
+        slots.copy_(host["slots"], non_blocking=True)
+        step()
+        done.copy_(slots[-1:], non_blocking=True)   # the write returns nothing: read back one word as the completion
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    stats = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = stats.tolist()
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = work / (kernel_ms * 1e-3) / 1e9
+        line = dict(
+            metric=kind["metric"], value=work * world * args.steps / (elapsed_ms * 1e-3) / 1e9, unit="GB/s",
+            n_gpus=world, steps=args.steps, warmup=warmup, ms_per_step=elapsed_ms / args.steps,
+            higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16->e4m3" if spec["fp8"] else "bf16",
+            data="synthetic",
+            config=dict(workload=args.workload, new_tokens=spec["tokens"], num_kv_heads=spec["hkv"],
+                        head_dim=spec["d"], page_size=spec["page"], cache="interleaved K|V pool, random page order",
+                        sharding="one step per rank, no collective",
+                        l2="rows read + written per step (0.8 - 1.07 GB) >> 126 MB L2",
+                        algorithmic_work_per_step_rank0=work),
+            roofline=dict(bound="hbm", achieved=achieved, peak=peaks["hbm"], unit="GB/s", frac=achieved / peaks["hbm"],
+                          traffic=NCU_TRAFFIC_RATIO.get(args.workload, 1.0) * work, peak_source=peaks["source"],
+                          kernel="atrex_sm100_kv_write_kernel", kernel_ms=kernel_ms,
+                          frac_of_nominal_8tbs=achieved / 8000.0),
+            e2e=dict(value=work * world / (e2e_ms * 1e-3) / 1e9, unit="GB/s", h2d_bytes_per_step=h2d,
+                     d2h_bytes_per_step=8, steps=e2e_steps,
+                     note="the step's K/V rows and slot ids copied from pinned host memory each step (PCIe-bound); "
+                          "the caches are resident device state"),
+            gpu_launches=args.steps, clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"],
+                                                 reasons=clocks["reasons"]),
+            device_status=runtime.check_device_status(device),
+        )
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = kv_write_cpu(spec, 1729, 10.0)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -334,6 +506,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
+        return
+    if spec["kind"] == "kv_write":
+        run_kv_write(args, spec, rank, world, local)
         return
 
     import torch

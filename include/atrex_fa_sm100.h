@@ -191,6 +191,47 @@ ATREX_FA_API int atrex_fa_sm100_prewarm(void);
 ATREX_FA_API uint64_t atrex_fa_sm100_static_scratch_bytes(void);
 ATREX_FA_API int atrex_fa_sm100_forward_static_scratch(const atrex_fa_sm100_params* p, void* stream);
 
+/*
+ * KV-cache write path: the step before attention in the caller.  Scatters the new key / value rows
+ * of a step, `key`, `value` [num_tokens, num_kv_heads, head_dim] BF16, into the paged pools that
+ * atrex_fa_sm100_forward reads (`k`, `v` of atrex_fa_sm100_params with the same page / row / head
+ * strides): token t goes to page slot_mapping[t] / page_size, row slot_mapping[t] % page_size; a
+ * negative slot skips the token.  cache_dtype ATREX_FA_BF16 copies; ATREX_FA_E4M3 stores
+ * e4m3(x / scale[head]) rounded to nearest even and saturated to +-448, where k_scale / v_scale are
+ * device FP32 arrays indexed head * scale_head_stride (stride 0: one scale for the tensor; NULL: 1.0)
+ * and are the descales the attention call is then given for that head.
+ *
+ * The reference has no writer: its tests fill caches by indexing
+ * (op_test/utils/flash_attn_contract.py:40-51; op_test/nvidia/flash_attn/test_flash_attn_sm120.py:236-244)
+ * and its stride rules (src/nvidia/flash_attn/sm120/launch.py:231-251) define the layouts a writer has
+ * to produce; all of them are expressible with the strides below.
+ *
+ * All strides are in ELEMENTS of their tensor.  head_dim is a multiple of 8 (16 for an E4M3 cache);
+ * every base pointer and every stride times its element size is 16-byte aligned for BF16 tensors and
+ * 8-byte aligned for an E4M3 cache.  Nothing is allocated; one kernel is enqueued on `stream`.
+ */
+typedef struct atrex_fa_sm100_kv_write_params {
+  uint32_t struct_bytes; /* sizeof(atrex_fa_sm100_kv_write_params) */
+  uint32_t abi_version;  /* ATREX_FA_SM100_ABI_VERSION */
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping; /* [num_tokens] */
+  const float* k_scale;
+  const float* v_scale;
+  int64_t key_token_stride, key_head_stride, value_token_stride, value_head_stride;
+  int64_t key_cache_page_stride, key_cache_row_stride, key_cache_head_stride;
+  int64_t value_cache_page_stride, value_cache_row_stride, value_cache_head_stride;
+  int64_t k_scale_head_stride, v_scale_head_stride;
+  int32_t num_tokens, num_kv_heads, head_dim, page_size;
+  int32_t cache_dtype; /* ATREX_FA_BF16 or ATREX_FA_E4M3 */
+  int32_t reserved;
+} atrex_fa_sm100_kv_write_params;
+
+ATREX_FA_API size_t atrex_fa_sm100_kv_write_params_bytes(void);
+ATREX_FA_API int atrex_fa_sm100_kv_cache_write(const atrex_fa_sm100_kv_write_params* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
