@@ -16,6 +16,7 @@
 #include <cuda_fp8.h>
 
 #include "fa_kernels.cuh"
+#include "softmax_math.cuh"
 
 namespace atrex_sm100 {
 
@@ -24,20 +25,31 @@ namespace {
 constexpr int kWriteThreads = 256;
 constexpr int kInFlight = 4;
 
-__device__ __forceinline__ uint2 quantise8(uint4 raw, float scale) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  uint32_t out[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float2 a = __bfloat1622float2(h[2 * i]), b = __bfloat1622float2(h[2 * i + 1]);
-    // IEEE division, not a reciprocal multiply: results must match x / scale rounded once
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a.x, scale), __fdiv_rn(a.y, scale)),
-                                                 __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(b.x, scale), __fdiv_rn(b.y, scale)),
-                                                 __NV_SATFINITE, __NV_E4M3);
-    out[i] = lo | (hi << 16);
-  }
-  return make_uint2(out[0], out[1]);
+// x / s correctly rounded, from the correctly rounded reciprocal r = RN(1/s) (Markstein's sequence: q0 = x r,
+// remainder by one exact FMA, one corrective FMA), two elements per instruction (f32x2): three FMA-pipe
+// instructions per PAIR instead of a full IEEE division per element, with one reciprocal per vector.  The
+// cases the sequence does not cover -- quotients that overflow or are denormal -- are above E4M3's
+// saturation point or below its smallest step either way; an overflowed first estimate is kept as it is
+// (+-inf saturates; the correction would be inf - inf).
+__device__ __forceinline__ uint32_t quotients_e4m3x2(uint32_t bf16_pair, f32x2 s2, f32x2 neg_s2, f32x2 r2) {
+  const f32x2 x2 = pack2(__uint_as_float(bf16_pair << 16), __uint_as_float(bf16_pair & 0xffff0000u));
+  const f32x2 q0 = mul2(x2, r2);
+  const f32x2 rem = fma2(q0, neg_s2, x2);
+  const f32x2 q = fma2(rem, r2, q0);
+  float a0, a1, b0, b1;
+  unpack2(q0, a0, a1);
+  unpack2(q, b0, b1);
+  b0 = fabsf(a0) <= 3.0e38f ? b0 : a0;
+  b1 = fabsf(a1) <= 3.0e38f ? b1 : a1;
+  return __nv_cvt_float2_to_fp8x2(make_float2(b0, b1), __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ uint2 quantise8(uint4 raw, float s) {
+  const float r = __frcp_rn(s);
+  const f32x2 s2 = pack2(s, s), neg_s2 = pack2(-s, -s), r2 = pack2(r, r);
+  const uint32_t lo0 = quotients_e4m3x2(raw.x, s2, neg_s2, r2), hi0 = quotients_e4m3x2(raw.y, s2, neg_s2, r2);
+  const uint32_t lo1 = quotients_e4m3x2(raw.z, s2, neg_s2, r2), hi1 = quotients_e4m3x2(raw.w, s2, neg_s2, r2);
+  return make_uint2(lo0 | (hi0 << 16), lo1 | (hi1 << 16));
 }
 
 // One warp per (tensor, token): the slot lookup and the page arithmetic happen once per token, the
@@ -47,6 +59,7 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
   const int lane = threadIdx.x & 31;
   const int vec_per_row = p.head_dim >> 3;                 // 16-byte vectors per (token, head) row
   const int vec_per_tok = p.num_kv_heads * vec_per_row;
+  const int row_shift = (vec_per_row & (vec_per_row - 1)) == 0 ? __ffs(vec_per_row) - 1 : -1;   // power of two: shift
   const long long units = 2ll * p.num_tokens;              // K tokens, then V tokens
   const long long warps = (long long)gridDim.x * (kWriteThreads / 32);
   for (long long unit = (long long)blockIdx.x * (kWriteThreads / 32) + (threadIdx.x >> 5); unit < units; unit += warps) {
@@ -69,7 +82,7 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
 #pragma unroll
       for (int u = 0; u < kInFlight; ++u) {
         const int v = v0 + u * 32;
-        head[u] = v / vec_per_row;
+        head[u] = row_shift >= 0 ? v >> row_shift : v / vec_per_row;
         vec[u] = v - head[u] * vec_per_row;
         if (v < vec_per_tok) raw[u] = __ldg(reinterpret_cast<const uint4*>(src + head[u] * src_head + vec[u] * 8));
       }

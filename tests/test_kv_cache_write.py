@@ -179,6 +179,36 @@ def test_write_shapes(page, heads, dim):
 
 
 @pytest.mark.gpu
+def test_fp8_quotients_are_correctly_rounded():
+    """Every BF16 bit pattern divided by awkward scales (significand all ones, just above a power of two, tiny,
+    huge): the stored E4M3 byte equals the oracle's for all of them."""
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    x = bits.view(torch.bfloat16)
+    x = x[torch.isfinite(x.float())]
+    n = x.numel() // 16 * 16
+    x = x[:n]
+    scales = torch.tensor([float(np.nextafter(np.float32(1.0), np.float32(0.0))), float(np.nextafter(np.float32(2.0), np.float32(3.0))),
+                           3.0, 0.3333333432674408, 1e-3, 977.0, float(np.nextafter(np.float32(0.5), np.float32(0.0))), 1.7],
+                          dtype=torch.float32)
+    heads = scales.numel()
+    key = x.view(-1, 1, 16).expand(-1, heads, 16).contiguous()      # [tokens, heads, 16]: every head sees every value
+    tokens = key.shape[0]
+    page = 16
+    pages = math.ceil(tokens / page)
+    kc = torch.zeros(pages, page, heads, 16, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    vc = torch.zeros_like(kc)
+    slots = torch.arange(tokens, dtype=torch.int64)
+    kv_cache.write_kv_cache(key.cuda(), key.cuda(), kc, vc, slots.cuda(), scales.cuda(), scales.flip(0).contiguous().cuda())
+    torch.cuda.synchronize()
+    want_k = np.zeros((pages, page, heads, 16), dtype=np.float32)
+    want_v = np.zeros_like(want_k)
+    kv_cache_oracle.write_kv_cache(key.float().numpy(), key.float().numpy(), want_k, want_v, slots.numpy(),
+                                   scales.numpy(), scales.flip(0).numpy(), fp8=True)
+    assert np.array_equal(kc.float().cpu().numpy(), want_k)
+    assert np.array_equal(vc.float().cpu().numpy(), want_v)
+
+
+@pytest.mark.gpu
 def test_write_empty_and_all_padding():
     kc = torch.full((2, 16, 2, 64), 1.0, dtype=torch.bfloat16, device="cuda")
     vc = kc.clone()
