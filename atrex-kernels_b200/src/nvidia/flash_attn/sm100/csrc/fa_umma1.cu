@@ -231,9 +231,6 @@ __device__ __forceinline__ float half_exp(uint32_t s_tmem, const uint32_t (&s)[C
   return sum_of(sum2);
 }
 
-__device__ __forceinline__ void group_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 // Barrier that also ORs a predicate over the group: a bounded wait that expired in one thread takes the
 // whole group out of its loop together (a plain bar.sync would strand the others).
 __device__ __forceinline__ bool group_barrier_or(int id, int threads, bool pred) {
