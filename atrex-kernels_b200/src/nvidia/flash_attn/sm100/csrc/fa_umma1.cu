@@ -10,12 +10,15 @@
 // the M operand instead; here the packed rows are M and the spare rows are idle, which an HBM-bound
 // call can afford):
 //
-//   * TMEM = S0 | S1 | O (tile_n + tile_n + head_dim columns); warp 4 issues QK^T for tile j+1 into
-//     the other S buffer while the softmax warpgroup works on tile j, then P V for tile j as soon as
-//     its P is in TMEM, so the matrix work of one tile hides behind the softmax of the next;
-//   * warps 5 and 6 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles; every CTA
-//     loads its own copy; Q comes by TMA when the GQA group divides 128, otherwise the softmax warpgroup
-//     copies its own rows into the swizzled tile;
+//   * TMEM = S0 | S1 | O (tile_n + tile_n + head_dim columns); warp 8 issues QK^T for tile j+1 into
+//     the other S buffer while the softmax warps work on tile j, then P V for tile j as soon as its P
+//     is in TMEM, so the matrix work of one tile hides behind the softmax of the next;
+//   * warps 0-7 are the softmax: TWO threads per row, each with half of the tile's key columns and half
+//     of the O columns, exchanging their partial row maximum through shared memory (two warps per
+//     scheduler keep the MUFU pipe busy where one cannot);
+//   * warps 9 and 10 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles; every CTA
+//     loads its own copy; Q comes by TMA when the GQA group divides 128, otherwise the two threads of a
+//     row copy half of it each into the swizzled tile;
 //   * FP8: q_descale * k_descale ride in the softmax scale, P is written as E4M3 shifted up by 2^4
 //     with a lazy-rescale threshold of 2^4 (P <= 256 < 448, prefill_cutedsl.py:2577-2593), V stays
 //     MN-major E4M3 in shared memory, v_descale is applied in the epilogue;
