@@ -6,18 +6,19 @@
 //
 //   * one CTA walks a static stripe of work items; an item is 256 packed GQA rows
 //     (two 128-row Q subtiles) of one (request, KV head), heaviest requests first;
-//   * warp 9 is the TMA producer: Q subtiles once per item, then K and V tiles of
+//   * warps 9 and 10 are the TMA producers, K (and the Q subtiles, once per item) and V: tiles of
 //     128 tokens gathered page by page through the block table into a 4-slot ring of
-//     128-byte-swizzled tiles (each CTA loads its own copy);
-//   * warp 8 issues tcgen05.mma: S = Q K^T (both operands K-major in shared memory)
-//     into TMEM, then O_tile = P V with P read straight from TMEM and V MN-major in
-//     shared memory, alternating between the two subtiles so that one subtile's
-//     softmax overlaps the other's matrix work;
-//   * warpgroups 0 and 1 (one thread per row) do the online softmax in the log2
-//     domain and write P as BF16 back into the S columns of TMEM; O accumulates in
-//     TMEM across KV tiles and is rescaled in place only when a row maximum grows by
-//     more than 2^8 (the lazy rescale of prefill_cutedsl.py:2589-2593), which after
-//     the first tiles is rare;
+//     128-byte-swizzled tiles (each CTA loads its own copy); the next tile's page ids are read
+//     before the wait for the current slot, so the table lookup is off the issue path;
+//   * warp 8 issues tcgen05.mma (the whole warp runs the issue code, lane 0's instruction is
+//     predicated): S = Q K^T (both operands K-major in shared memory) into TMEM, then
+//     O_tile = P V with P read straight from TMEM and V MN-major in shared memory, alternating
+//     between the two subtiles so that one subtile's softmax overlaps the other's matrix work;
+//   * warpgroups 0 and 1 (one thread per row) do the online softmax in the log2 domain and write
+//     P as BF16 back into the S columns of TMEM, handing it to the issuer in two parts (after 96
+//     and 128 keys) so that P V starts under the last exponentials; O accumulates in TMEM across
+//     KV tiles and is rescaled in place only when a row maximum grows by more than 2^8 (the lazy
+//     rescale of prefill_cutedsl.py:2589-2593), which after the first tiles is rare;
 //   * TMEM: S0 | S1 | O0 | O1, 128 columns each (all 512).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a code, drains its
