@@ -62,5 +62,8 @@ struct KvWriteParams {
   int num_tokens, num_kv_heads, head_dim, page_size;
 };
 cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cudaStream_t stream);
+// Per-head E4M3 scales (max |x| / 448) of the rows a write would store; `amax` is 2 * num_kv_heads words of scratch.
+cudaError_t kv_scales_launch(const KvWriteParams& p, unsigned* amax, float* k_scale, float* v_scale, int sm_count,
+                             cudaStream_t stream);
 
 }  // namespace atrex_sm100

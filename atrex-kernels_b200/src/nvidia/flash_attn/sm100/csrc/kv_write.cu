@@ -101,6 +101,73 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
   }
 }
 
+// Per-KV-head scales for an E4M3 cache: scale[head] = max |x| over the step's rows of that head / 448, so that
+// x / scale fills the format's range.  Pass 1 reduces |x| (BF16 magnitudes compare like their bit patterns, so
+// the maximum is an integer max of 15-bit fields) per warp, then per CTA in shared memory, then with one
+// atomicMax per head and CTA; pass 2 turns the maxima into FP32 scales.  `amax` must be zero on entry.
+__global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_amax_kernel(const KvWriteParams p, unsigned* amax) {
+  extern __shared__ unsigned s_amax[];                     // [2][num_kv_heads]
+  for (int i = threadIdx.x; i < 2 * p.num_kv_heads; i += kWriteThreads) s_amax[i] = 0u;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int vec_per_row = p.head_dim >> 3;
+  const int vec_per_tok = p.num_kv_heads * vec_per_row;
+  const int row_shift = (vec_per_row & (vec_per_row - 1)) == 0 ? __ffs(vec_per_row) - 1 : -1;
+  const long long units = 2ll * p.num_tokens;
+  const long long warps = (long long)gridDim.x * (kWriteThreads / 32);
+  // A lane keeps the same (head, vector) slots for every token: kInFlight loads per token, their maxima kept per slot.
+  for (int v0 = lane; v0 < vec_per_tok; v0 += 32 * kInFlight) {
+    int head[kInFlight], vec[kInFlight];
+    unsigned best[2][kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int v = v0 + u * 32;
+      head[u] = row_shift >= 0 ? v >> row_shift : v / vec_per_row;
+      vec[u] = v - head[u] * vec_per_row;
+      best[0][u] = best[1][u] = 0u;
+    }
+    for (long long unit = (long long)blockIdx.x * (kWriteThreads / 32) + (threadIdx.x >> 5); unit < units; unit += warps) {
+      const int which = unit >= p.num_tokens;
+      const long long tok = unit - (which ? p.num_tokens : 0);
+      if (__ldg(p.slot_mapping + tok) < 0) continue;       // padding tokens are not stored, so they do not count
+      const __nv_bfloat16* src = (which ? p.value : p.key) + tok * (which ? p.v_token_stride : p.k_token_stride);
+      const long long src_head = which ? p.v_head_stride : p.k_head_stride;
+      uint4 raw[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u)
+        raw[u] = v0 + u * 32 < vec_per_tok ? __ldg(reinterpret_cast<const uint4*>(src + head[u] * src_head + vec[u] * 8))
+                                           : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const unsigned w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        unsigned m = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m = max(m, max(w[i] & 0x7fffu, (w[i] >> 16) & 0x7fffu));
+        if (which) best[1][u] = max(best[1][u], m);
+        else best[0][u] = max(best[0][u], m);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      if (v0 + u * 32 >= vec_per_tok) continue;
+      if (best[0][u]) atomicMax(&s_amax[head[u]], best[0][u]);
+      if (best[1][u]) atomicMax(&s_amax[p.num_kv_heads + head[u]], best[1][u]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * p.num_kv_heads; i += kWriteThreads)
+    if (s_amax[i]) atomicMax(&amax[i], s_amax[i]);
+}
+
+// amax (BF16 magnitude bits) -> scale = amax / 448 (IEEE division); a head without a finite non-zero value gets 1.
+__global__ void atrex_sm100_kv_scale_kernel(const unsigned* amax, float* k_scale, float* v_scale, int num_kv_heads) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * num_kv_heads) return;
+  const float a = __uint_as_float(amax[i] << 16);
+  const float scale = (a > 0.f && a < __int_as_float(0x7f800000)) ? __fdiv_rn(a, 448.f) : 1.f;
+  (i < num_kv_heads ? k_scale : v_scale)[i % num_kv_heads] = scale;
+}
+
 }  // namespace
 
 cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cudaStream_t stream) {
@@ -112,6 +179,25 @@ cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cuda
   if (ctas > cap) ctas = cap;
   if (fp8) return launch_kernel(atrex_sm100_kv_write_kernel<true>, dim3((unsigned)ctas), dim3(kWriteThreads), 0, stream, p);
   return launch_kernel(atrex_sm100_kv_write_kernel<false>, dim3((unsigned)ctas), dim3(kWriteThreads), 0, stream, p);
+}
+
+cudaError_t kv_scales_launch(const KvWriteParams& p, unsigned* amax, float* k_scale, float* v_scale, int sm_count,
+                             cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(unsigned) * 2 * p.num_kv_heads, stream);
+  if (e != cudaSuccess) return e;
+  const long long units = 2ll * p.num_tokens;
+  if (units > 0) {
+    const int warps_per_cta = kWriteThreads / 32;
+    long long ctas = (units + warps_per_cta - 1) / warps_per_cta;
+    const long long cap = (long long)sm_count * 8;
+    if (ctas > cap) ctas = cap;
+    e = launch_kernel(atrex_sm100_kv_amax_kernel, dim3((unsigned)ctas), dim3(kWriteThreads),
+                      sizeof(unsigned) * 2 * p.num_kv_heads, stream, p, amax);
+    if (e != cudaSuccess) return e;
+  }
+  const int n = 2 * p.num_kv_heads;
+  return launch_kernel(atrex_sm100_kv_scale_kernel, dim3((n + 127) / 128), dim3(128), 0, stream,
+                       (const unsigned*)amax, k_scale, v_scale, p.num_kv_heads);
 }
 
 }  // namespace atrex_sm100

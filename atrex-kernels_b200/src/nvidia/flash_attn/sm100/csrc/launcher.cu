@@ -507,52 +507,88 @@ int atrex_fa_sm100_forward_static_scratch(const atrex_fa_sm100_params* p, void* 
 
 size_t atrex_fa_sm100_kv_write_params_bytes(void) { return sizeof(atrex_fa_sm100_kv_write_params); }
 
-int atrex_fa_sm100_kv_cache_write(const atrex_fa_sm100_kv_write_params* p, void* stream) {
+static int kv_fill(const atrex_fa_sm100_kv_write_params* p, bool need_cache, atrex_sm100::KvWriteParams* k, bool* fp8_out,
+                   int* sm_count) {
   using namespace atrex_sm100;
   if (p == nullptr) return fail(ATREX_FA_INVALID_VALUE, "null parameter block");
   if (p->struct_bytes != sizeof(atrex_fa_sm100_kv_write_params) || p->abi_version != ATREX_FA_SM100_ABI_VERSION)
     return fail(ATREX_FA_ABI_MISMATCH, "kv-write parameter block does not match this library");
   if (p->num_tokens < 0 || p->num_kv_heads <= 0 || p->head_dim <= 0 || p->page_size <= 0)
     return fail(ATREX_FA_INVALID_VALUE, "negative or zero size");
-  if (p->cache_dtype != ATREX_FA_BF16 && p->cache_dtype != ATREX_FA_E4M3)
-    return fail(ATREX_FA_UNSUPPORTED, "cache dtype must be BF16 or E4M3");
-  const bool fp8 = p->cache_dtype == ATREX_FA_E4M3;
+  bool fp8 = false;
+  if (need_cache) {
+    if (p->cache_dtype != ATREX_FA_BF16 && p->cache_dtype != ATREX_FA_E4M3)
+      return fail(ATREX_FA_UNSUPPORTED, "cache dtype must be BF16 or E4M3");
+    fp8 = p->cache_dtype == ATREX_FA_E4M3;
+  }
   if (p->head_dim % (fp8 ? 16 : 8)) return fail(ATREX_FA_UNSUPPORTED, "head_dim must be a multiple of 8 (16 for E4M3)");
-  if (p->num_tokens == 0) return ATREX_FA_OK;
-  if (!p->key || !p->value || !p->key_cache || !p->value_cache || !p->slot_mapping)
-    return fail(ATREX_FA_INVALID_VALUE, "null tensor pointer");
-  // 16-byte source vectors; 16-byte (BF16) or 8-byte (E4M3) destination vectors
-  const int64_t src_strides[] = {p->key_token_stride, p->key_head_stride, p->value_token_stride, p->value_head_stride};
-  for (int64_t st : src_strides)
-    if ((st * 2) % 16) return fail(ATREX_FA_UNSUPPORTED, "key / value strides must be multiples of 16 bytes");
-  const int64_t dst_strides[] = {p->key_cache_page_stride,   p->key_cache_row_stride,   p->key_cache_head_stride,
-                                 p->value_cache_page_stride, p->value_cache_row_stride, p->value_cache_head_stride};
-  const int dst_align = fp8 ? 8 : 16, dst_es = fp8 ? 1 : 2;
-  for (int64_t st : dst_strides)
-    if ((st * dst_es) % dst_align) return fail(ATREX_FA_UNSUPPORTED, "cache strides are not vector aligned");
-  if (((uintptr_t)p->key | (uintptr_t)p->value) % 16 || ((uintptr_t)p->key_cache | (uintptr_t)p->value_cache) % dst_align)
-    return fail(ATREX_FA_UNSUPPORTED, "base pointers are not vector aligned");
+  if (p->num_tokens > 0) {
+    if (!p->key || !p->value || !p->slot_mapping) return fail(ATREX_FA_INVALID_VALUE, "null tensor pointer");
+    if (need_cache && (!p->key_cache || !p->value_cache)) return fail(ATREX_FA_INVALID_VALUE, "null cache pointer");
+    // 16-byte source vectors; 16-byte (BF16) or 8-byte (E4M3) destination vectors
+    const int64_t src_strides[] = {p->key_token_stride, p->key_head_stride, p->value_token_stride, p->value_head_stride};
+    for (int64_t st : src_strides)
+      if ((st * 2) % 16) return fail(ATREX_FA_UNSUPPORTED, "key / value strides must be multiples of 16 bytes");
+    if (((uintptr_t)p->key | (uintptr_t)p->value) % 16) return fail(ATREX_FA_UNSUPPORTED, "key / value are not 16-byte aligned");
+    if (need_cache) {
+      const int64_t dst_strides[] = {p->key_cache_page_stride,   p->key_cache_row_stride,   p->key_cache_head_stride,
+                                     p->value_cache_page_stride, p->value_cache_row_stride, p->value_cache_head_stride};
+      const int dst_align = fp8 ? 8 : 16, dst_es = fp8 ? 1 : 2;
+      for (int64_t st : dst_strides)
+        if ((st * dst_es) % dst_align) return fail(ATREX_FA_UNSUPPORTED, "cache strides are not vector aligned");
+      if (((uintptr_t)p->key_cache | (uintptr_t)p->value_cache) % dst_align)
+        return fail(ATREX_FA_UNSUPPORTED, "cache pointers are not vector aligned");
+    }
+  }
   DeviceInfo* dev = nullptr;
   int st = current_device(&dev);
   if (st != ATREX_FA_OK) return st;
+  *sm_count = dev->sm_count;
+  *fp8_out = fp8;
+  k->key = static_cast<const __nv_bfloat16*>(p->key);
+  k->value = static_cast<const __nv_bfloat16*>(p->value);
+  k->key_cache = p->key_cache;
+  k->value_cache = p->value_cache;
+  k->slot_mapping = reinterpret_cast<const long long*>(p->slot_mapping);
+  k->k_scale = p->k_scale;
+  k->v_scale = p->v_scale;
+  k->k_token_stride = p->key_token_stride, k->k_head_stride = p->key_head_stride;
+  k->v_token_stride = p->value_token_stride, k->v_head_stride = p->value_head_stride;
+  k->kc_page_stride = p->key_cache_page_stride, k->kc_row_stride = p->key_cache_row_stride;
+  k->kc_head_stride = p->key_cache_head_stride;
+  k->vc_page_stride = p->value_cache_page_stride, k->vc_row_stride = p->value_cache_row_stride;
+  k->vc_head_stride = p->value_cache_head_stride;
+  k->k_scale_head_stride = p->k_scale_head_stride, k->v_scale_head_stride = p->v_scale_head_stride;
+  k->num_tokens = p->num_tokens, k->num_kv_heads = p->num_kv_heads, k->head_dim = p->head_dim, k->page_size = p->page_size;
+  return ATREX_FA_OK;
+}
+
+int atrex_fa_sm100_kv_cache_write(const atrex_fa_sm100_kv_write_params* p, void* stream) {
+  using namespace atrex_sm100;
   KvWriteParams k;
-  k.key = static_cast<const __nv_bfloat16*>(p->key);
-  k.value = static_cast<const __nv_bfloat16*>(p->value);
-  k.key_cache = p->key_cache;
-  k.value_cache = p->value_cache;
-  k.slot_mapping = reinterpret_cast<const long long*>(p->slot_mapping);
-  k.k_scale = p->k_scale;
-  k.v_scale = p->v_scale;
-  k.k_token_stride = p->key_token_stride, k.k_head_stride = p->key_head_stride;
-  k.v_token_stride = p->value_token_stride, k.v_head_stride = p->value_head_stride;
-  k.kc_page_stride = p->key_cache_page_stride, k.kc_row_stride = p->key_cache_row_stride;
-  k.kc_head_stride = p->key_cache_head_stride;
-  k.vc_page_stride = p->value_cache_page_stride, k.vc_row_stride = p->value_cache_row_stride;
-  k.vc_head_stride = p->value_cache_head_stride;
-  k.k_scale_head_stride = p->k_scale_head_stride, k.v_scale_head_stride = p->v_scale_head_stride;
-  k.num_tokens = p->num_tokens, k.num_kv_heads = p->num_kv_heads, k.head_dim = p->head_dim, k.page_size = p->page_size;
-  cudaError_t e = kv_write_launch(k, fp8, dev->sm_count, static_cast<cudaStream_t>(stream));
+  bool fp8 = false;
+  int sms = 0;
+  int st = kv_fill(p, true, &k, &fp8, &sms);
+  if (st != ATREX_FA_OK) return st;
+  if (p->num_tokens == 0) return ATREX_FA_OK;
+  cudaError_t e = kv_write_launch(k, fp8, sms, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "kv-cache write kernel launch", e);
+  return ATREX_FA_OK;
+}
+
+int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* p, float* k_scale_out, float* v_scale_out,
+                             void* scratch, void* stream) {
+  using namespace atrex_sm100;
+  if (k_scale_out == nullptr || v_scale_out == nullptr || scratch == nullptr || ((uintptr_t)scratch % 4))
+    return fail(ATREX_FA_INVALID_VALUE, "null or misaligned output / scratch pointer");
+  KvWriteParams k;
+  bool fp8 = false;
+  int sms = 0;
+  int st = kv_fill(p, false, &k, &fp8, &sms);
+  if (st != ATREX_FA_OK) return st;
+  cudaError_t e = kv_scales_launch(k, static_cast<unsigned*>(scratch), k_scale_out, v_scale_out, sms,
+                                   static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "kv-scales kernel launch", e);
   return ATREX_FA_OK;
 }
 

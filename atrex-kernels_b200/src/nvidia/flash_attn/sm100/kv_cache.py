@@ -46,6 +46,9 @@ def _bind(lib):
     lib.atrex_fa_sm100_kv_write_params_bytes.restype = ctypes.c_size_t
     lib.atrex_fa_sm100_kv_cache_write.restype = ctypes.c_int
     lib.atrex_fa_sm100_kv_cache_write.argtypes = [ctypes.POINTER(KvWriteParams), ctypes.c_void_p]
+    lib.atrex_fa_sm100_kv_scales.restype = ctypes.c_int
+    lib.atrex_fa_sm100_kv_scales.argtypes = [ctypes.POINTER(KvWriteParams), ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_void_p]
     if lib.atrex_fa_sm100_kv_write_params_bytes() != ctypes.sizeof(KvWriteParams):
         raise RuntimeError("libatrex_fa_sm100.so does not match this Python binding (kv-write struct size)")
     lib._atrex_kv_write_bound = True
@@ -113,3 +116,38 @@ def write_kv_cache(key, value, key_cache, value_cache, slot_mapping, k_scale=Non
     with torch.cuda.device(key.device):
         stream = torch.cuda.current_stream(key.device).cuda_stream
         runtime.raise_for_status(lib.atrex_fa_sm100_kv_cache_write(ctypes.byref(p), stream))
+
+
+def compute_kv_scales(key, value, slot_mapping):
+    """Per-KV-head scales for an FP8 E4M3 cache from the rows about to be written: ``(k_scale, v_scale)``, FP32
+    ``[num_kv_heads]`` on the device, ``max |x| / 448`` over the non-padding tokens of each head (1.0 for a head
+    with no finite non-zero value).  Pass them to ``write_kv_cache`` and, expanded over the batch, to the
+    attention call as ``k_descale`` / ``v_descale``."""
+    if key.ndim != 3 or value.shape != key.shape:
+        raise ValueError("key and value must be [num_tokens, num_kv_heads, head_dim] of one shape")
+    if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
+        raise NotImplementedError("key and value must be bfloat16")
+    tokens, heads, dim = key.shape
+    if slot_mapping.shape != (tokens,) or slot_mapping.dtype != torch.int64 or slot_mapping.stride(0) != 1:
+        raise ValueError("slot_mapping must be a contiguous int64 [num_tokens]")
+    if not (key.device == value.device == slot_mapping.device):
+        raise ValueError("all tensors must be on one device")
+    if key.device.type != "cuda":
+        raise NotImplementedError("Atrex sm100 KV-cache scales run on CUDA devices only")
+    if dim % 8 or key.stride(2) != 1 or value.stride(2) != 1:
+        raise NotImplementedError("head_dim must be a contiguous multiple of 8")
+    lib = runtime.load_library()
+    _bind(lib)
+    p = KvWriteParams()
+    p.struct_bytes, p.abi_version = ctypes.sizeof(KvWriteParams), runtime.ABI_VERSION
+    p.key, p.value, p.slot_mapping = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
+    p.key_token_stride, p.key_head_stride = key.stride(0), key.stride(1)
+    p.value_token_stride, p.value_head_stride = value.stride(0), value.stride(1)
+    p.num_tokens, p.num_kv_heads, p.head_dim, p.page_size = tokens, heads, dim, 1
+    scales = torch.empty(2, heads, dtype=torch.float32, device=key.device)
+    scratch = torch.empty(2 * heads, dtype=torch.int32, device=key.device)
+    with torch.cuda.device(key.device):
+        stream = torch.cuda.current_stream(key.device).cuda_stream
+        runtime.raise_for_status(lib.atrex_fa_sm100_kv_scales(ctypes.byref(p), scales[0].data_ptr(),
+                                                              scales[1].data_ptr(), scratch.data_ptr(), stream))
+    return scales[0], scales[1]

@@ -68,6 +68,9 @@ WORKLOADS = {
     # pools, BF16 cache and FP8 E4M3 cache (per-head scales); 0.5 GB of K/V rows per step (4x L2)
     "kv_write": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=False, scaling="weak"),
     "kv_write_fp8": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=True, scaling="weak"),
+    # the same with the per-head scales computed from the step's rows first (max |x| / 448): two passes over K/V
+    "kv_write_fp8_scaled": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=True, scales="computed",
+                                scaling="weak"),
     "kv_write_small": dict(kind="kv_write", tokens=65536, hkv=8, d=128, page=64, fp8=False, scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
@@ -398,6 +401,9 @@ def run_kv_write(args, spec, rank, world, local):
     key, value, kc, vc, slots, scales = kv_write_inputs(spec, 1729 + 1000 * rank, device, torch)
     ks, vs = scales if scales else (None, None)
     work = kv_cache_oracle.algorithmic_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"])
+    computed = spec.get("scales") == "computed"
+    if computed:
+        work += spec["tokens"] * spec["hkv"] * spec["d"] * 2 * 2      # the scale pass reads every K and V row once more
     warmup = max(3, args.warmup)
 
     def barrier():
@@ -406,7 +412,11 @@ def run_kv_write(args, spec, rank, world, local):
         torch.cuda.synchronize()
 
     def step():
-        kv_cache.write_kv_cache(key, value, kc, vc, slots, ks, vs)
+        if computed:
+            k_s, v_s = kv_cache.compute_kv_scales(key, value, slots)
+            kv_cache.write_kv_cache(key, value, kc, vc, slots, k_s, v_s)
+        else:
+            kv_cache.write_kv_cache(key, value, kc, vc, slots, ks, vs)
 
     for _ in range(warmup):
         step()
@@ -471,13 +481,14 @@ def run_kv_write(args, spec, rank, world, local):
                         algorithmic_work_per_step_rank0=work),
             roofline=dict(bound="hbm", achieved=achieved, peak=peaks["hbm"], unit="GB/s", frac=achieved / peaks["hbm"],
                           traffic=NCU_TRAFFIC_RATIO.get(args.workload, 1.0) * work, peak_source=peaks["source"],
-                          kernel="atrex_sm100_kv_write_kernel", kernel_ms=kernel_ms,
+                          kernel="atrex_sm100_kv_amax_kernel + atrex_sm100_kv_write_kernel" if computed
+                          else "atrex_sm100_kv_write_kernel", kernel_ms=kernel_ms,
                           frac_of_nominal_8tbs=achieved / 8000.0),
             e2e=dict(value=work * world / (e2e_ms * 1e-3) / 1e9, unit="GB/s", h2d_bytes_per_step=h2d,
                      d2h_bytes_per_step=8, steps=e2e_steps,
                      note="the step's K/V rows and slot ids copied from pinned host memory each step (PCIe-bound); "
                           "the caches are resident device state"),
-            gpu_launches=args.steps, clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"],
+            gpu_launches=args.steps * (3 if computed else 1), clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"],
                                                  reasons=clocks["reasons"]),
             device_status=runtime.check_device_status(device),
         )

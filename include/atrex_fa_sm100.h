@@ -232,6 +232,18 @@ typedef struct atrex_fa_sm100_kv_write_params {
 ATREX_FA_API size_t atrex_fa_sm100_kv_write_params_bytes(void);
 ATREX_FA_API int atrex_fa_sm100_kv_cache_write(const atrex_fa_sm100_kv_write_params* p, void* stream);
 
+/*
+ * Scales for an E4M3 cache, computed from the rows the write is about to store: k_scale_out[h] and
+ * v_scale_out[h] (device FP32 [num_kv_heads]) = max |x| over the non-padding tokens of head h / 448, 1.0 for
+ * a head without a finite non-zero value.  Only key, value, slot_mapping, their strides and the sizes of
+ * `p` are read (the cache fields and cache_dtype are ignored).  `scratch` is 8 * num_kv_heads bytes of
+ * device memory, 4-byte aligned, contents irrelevant.  Enqueues a memset and two kernels on `stream`;
+ * allocates nothing.  The results feed atrex_fa_sm100_kv_cache_write (k_scale / v_scale, head stride 1)
+ * and then the attention call's k_descale / v_descale.
+ */
+ATREX_FA_API int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* p, float* k_scale_out,
+                                          float* v_scale_out, void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

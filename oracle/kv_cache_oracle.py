@@ -36,11 +36,31 @@ def write_kv_cache(key, value, key_cache, value_cache, slot_mapping, k_scale=Non
             continue
         p, r = divmod(slot, page)
         if fp8:
-            key_cache[p, r] = fa_oracle.e4m3_round((key[t] / ks[:, None]).astype(np.float32))
-            value_cache[p, r] = fa_oracle.e4m3_round((value[t] / vs[:, None]).astype(np.float32))
+            with np.errstate(over="ignore"):   # a quotient beyond FP32 saturates like any other large value
+                key_cache[p, r] = fa_oracle.e4m3_round((key[t] / ks[:, None]).astype(np.float32))
+                value_cache[p, r] = fa_oracle.e4m3_round((value[t] / vs[:, None]).astype(np.float32))
         else:
             key_cache[p, r] = key[t]
             value_cache[p, r] = value[t]
+
+
+def kv_scales(key, value, slot_mapping):
+    """Per-head E4M3 scales: max |x| over the non-padding tokens / 448 in float32; 1.0 where that maximum is zero
+    or not finite."""
+    keep = np.asarray(slot_mapping) >= 0
+
+    def one(x):
+        x = np.asarray(x, dtype=np.float32)[keep]
+        heads = x.shape[1]
+        out = np.ones(heads, dtype=np.float32)
+        if x.shape[0] == 0:
+            return out
+        amax = np.abs(x).max(axis=(0, 2))
+        ok = np.isfinite(amax) & (amax > 0)
+        out[ok] = (amax[ok] / np.float32(448.0)).astype(np.float32)
+        return out
+
+    return one(key), one(value)
 
 
 def algorithmic_bytes(tokens_written, num_kv_heads, head_dim, fp8):

@@ -208,6 +208,44 @@ def test_fp8_quotients_are_correctly_rounded():
     assert np.array_equal(vc.float().cpu().numpy(), want_v)
 
 
+def test_oracle_scales():
+    key = np.zeros((5, 3, 8), dtype=np.float32)
+    value = np.zeros_like(key)
+    key[1, 0, 3] = -896.0
+    key[2, 1, 0] = 7.0
+    key[4, 1, 1] = 100.0            # padding token: ignored
+    value[0, 2, 7] = np.inf
+    ks, vs = kv_cache_oracle.kv_scales(key, value, np.array([0, 1, 2, 3, -1]))
+    assert ks.tolist() == [2.0, np.float32(7.0) / np.float32(448.0), 1.0] and vs.tolist() == [1.0, 1.0, 1.0]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,dim,tokens", [(2, 128, 777), (8, 128, 4096), (3, 64, 50), (1, 256, 1)])
+def test_scales_match_oracle_and_fill_the_range(heads, dim, tokens):
+    g = torch.Generator().manual_seed(tokens)
+    parent = (torch.randn(tokens, heads + 1, dim, generator=g) * 5).bfloat16()
+    key = parent[:, :heads]
+    value = (torch.randn(tokens, heads, dim, generator=g) * 0.01).bfloat16()
+    if tokens > 10:
+        value[:, 0] = 0                       # a head of zeros gets scale 1
+    slots = torch.arange(tokens, dtype=torch.int64)
+    if tokens > 10:
+        slots[::3] = -1                       # padding tokens do not count
+        key[0] = 1e30                         # ... even when they are huge (token 0 is padding)
+    ks, vs = kv_cache.compute_kv_scales(key.cuda(), value.cuda(), slots.cuda())
+    torch.cuda.synchronize()
+    want_k, want_v = kv_cache_oracle.kv_scales(key.float().numpy(), value.float().numpy(), slots.numpy())
+    assert np.array_equal(ks.cpu().numpy(), want_k) and np.array_equal(vs.cpu().numpy(), want_v)
+    # writing with these scales uses the whole E4M3 range and never saturates
+    page = 16
+    pages = math.ceil(tokens / page)
+    kc = torch.zeros(pages, page, heads, dim, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    vc = torch.zeros_like(kc)
+    kv_cache.write_kv_cache(key.cuda().contiguous(), value.cuda(), kc, vc, slots.cuda(), ks, vs)
+    torch.cuda.synchronize()
+    assert float(kc.float().abs().max()) == 448.0
+
+
 @pytest.mark.gpu
 def test_write_empty_and_all_padding():
     kc = torch.full((2, 16, 2, 64), 1.0, dtype=torch.bfloat16, device="cuda")
