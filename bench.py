@@ -23,6 +23,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import sys
@@ -113,18 +114,56 @@ def draw_lengths(spec, seed):
     return list(kv), list(kv)
 
 
+# ---- work accounting (the benchmark's own; tests/test_bench_accounting.py checks it against the oracle's) ----
+def causal_visible_pairs(q_len, kv_len, left=-1):
+    """(query, key) pairs a causal call does not mask: query i sees keys [max(0, i + off - left), i + off],
+    off = kv_len - q_len (bottom-right aligned); left < 0 = no sliding window."""
+    off = kv_len - q_len
+    total = 0
+    for i in range(q_len):
+        hi = min(kv_len - 1, i + off)
+        lo = 0 if left < 0 else max(0, i + off - left)
+        total += max(0, hi - lo + 1)
+    return total
+
+
+def algorithmic_flops(q_lens, kv_lens, num_q_heads, head_dim, left=-1):
+    """4 * D * Hq * visible pairs: 2 FLOP per multiply-add in Q K^T and in P V."""
+    pairs = 0
+    for nq, nk in zip(q_lens, kv_lens):
+        if left < 0 and nk >= nq:
+            pairs += nq * (nk - nq) + nq * (nq + 1) // 2          # closed form of the sum above
+        else:
+            pairs += causal_visible_pairs(nq, nk, left)
+    return 4 * head_dim * num_q_heads * pairs
+
+
+def algorithmic_decode_bytes(q_lens, kv_lens, num_q_heads, num_kv_heads, head_dim, elem_bytes, page_size, left=-1):
+    """K + V bytes of the keys any query row of a request can see, its page-table entries, Q read and O written."""
+    total = 0
+    for nq, nk in zip(q_lens, kv_lens):
+        span = nk if left < 0 else min(nk, left + nq)
+        total += span * num_kv_heads * head_dim * 2 * elem_bytes
+        total += 4 * math.ceil(span / page_size)
+        total += nq * num_q_heads * head_dim * (elem_bytes + 2)
+    return total
+
+
+def kv_write_bytes(tokens, num_kv_heads, head_dim, fp8):
+    """K and V rows read as BF16 and written once in the cache's element size, plus the 8-byte slot ids."""
+    row = num_kv_heads * head_dim
+    return tokens * (2 * row * 2 + 2 * row * (1 if fp8 else 2) + 8)
+
+
 def work_units(spec, q_lens, kv_lens):
     """Algorithmic bytes (decode) or FLOPs (prefill) of one pass over the batch."""
-    from oracle import fa_oracle
-
-    window = spec["window"] or (-1, -1)
+    left = spec["window"][0] if spec["window"] else -1
     if spec["kind"] == "decode":
-        total = fa_oracle.algorithmic_decode_bytes(q_lens, kv_lens, spec["hq"], spec["hkv"], spec["d"], 2,
-                                                   spec["page"], window=window)
+        total = algorithmic_decode_bytes(q_lens, kv_lens, spec["hq"], spec["hkv"], spec["d"], 2, spec["page"], left)
         if spec["lse"]:
             total += 4 * sum(q_lens) * spec["hq"]
         return total
-    return fa_oracle.algorithmic_flops(q_lens, kv_lens, spec["hq"], spec["d"], True, window)
+    return algorithmic_flops(q_lens, kv_lens, spec["hq"], spec["d"], left)
 
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read only)."""
@@ -380,7 +419,7 @@ def kv_write_cpu(spec, seed, budget_s):
         kv_cache_oracle.write_kv_cache(key, value, kc, vc, slots, scale, scale, fp8=spec["fp8"])
         done += sample
     t = time.perf_counter() - t0
-    work = kv_cache_oracle.algorithmic_bytes(done, hkv, d, spec["fp8"])
+    work = kv_write_bytes(done, hkv, d, spec["fp8"])
     return dict(value=work / t / 1e9, unit="GB/s", cores=1, kind="port",
                 sample=f"oracle scatter of {done} of the step's {spec['tokens']} tokens, {t:.1f} s"), t
 
@@ -390,7 +429,6 @@ def run_kv_write(args, spec, rank, world, local):
     import torch
     import torch.distributed as dist
     from atrex.src.nvidia.flash_attn.sm100 import kv_cache, runtime
-    from oracle import kv_cache_oracle
 
     kind = KIND["kv_write"]
     torch.cuda.set_device(local)
@@ -400,7 +438,7 @@ def run_kv_write(args, spec, rank, world, local):
     runtime.prewarm(device)
     key, value, kc, vc, slots, scales = kv_write_inputs(spec, 1729 + 1000 * rank, device, torch)
     ks, vs = scales if scales else (None, None)
-    work = kv_cache_oracle.algorithmic_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"])
+    work = kv_write_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"])
     computed = spec.get("scales") == "computed"
     if computed:
         work += spec["tokens"] * spec["hkv"] * spec["d"] * 2 * 2      # the scale pass reads every K and V row once more

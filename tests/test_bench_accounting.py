@@ -1,0 +1,50 @@
+"""bench.py's own work accounting (algorithmic bytes / FLOPs) agrees with the oracle's definitions."""
+
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+
+import numpy as np
+
+from oracle import fa_oracle, kv_cache_oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("atrex_bench", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        spec.loader.exec_module(mod)
+    finally:
+        sys.argv = argv
+    return mod
+
+
+def test_flops_and_bytes_match_the_oracle():
+    b = _bench()
+    rng = np.random.default_rng(5)
+    for left in (-1, 0, 7, 4095):
+        q = rng.integers(1, 40, 12).tolist()
+        kv = [a + int(x) for a, x in zip(q, rng.integers(0, 60, 12))]
+        assert b.algorithmic_flops(q, kv, 8, 128, left) == fa_oracle.algorithmic_flops(q, kv, 8, 128, True, (left, 0))
+        assert b.algorithmic_decode_bytes(q, kv, 32, 8, 128, 2, 64, left) == \
+            fa_oracle.algorithmic_decode_bytes(q, kv, 32, 8, 128, 2, 64, window=(left, 0))
+        for nq, nk in zip(q, kv):
+            assert b.causal_visible_pairs(nq, nk, left) == fa_oracle.visible_pairs(nq, nk, True, (left, 0))
+    for fp8 in (False, True):
+        assert b.kv_write_bytes(1000, 8, 128, fp8) == kv_cache_oracle.algorithmic_bytes(1000, 8, 128, fp8)
+
+
+def test_every_workload_has_work_units():
+    b = _bench()
+    for name, spec in b.WORKLOADS.items():
+        if spec["kind"] == "kv_write":
+            assert b.kv_write_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"]) > 0
+            continue
+        small = dict(spec, batch=2)
+        q, kv = b.draw_lengths(small, 1)
+        assert b.work_units(small, q, kv) > 0, name
