@@ -44,8 +44,7 @@ __device__ __forceinline__ uint32_t quotients_e4m3x2(uint32_t bf16_pair, f32x2 s
   return __nv_cvt_float2_to_fp8x2(make_float2(b0, b1), __NV_SATFINITE, __NV_E4M3);
 }
 
-__device__ __forceinline__ uint2 quantise8(uint4 raw, float s) {
-  const float r = __frcp_rn(s);
+__device__ __forceinline__ uint2 quantise8(uint4 raw, float s, float r) {
   const f32x2 s2 = pack2(s, s), neg_s2 = pack2(-s, -s), r2 = pack2(r, r);
   const uint32_t lo0 = quotients_e4m3x2(raw.x, s2, neg_s2, r2), hi0 = quotients_e4m3x2(raw.y, s2, neg_s2, r2);
   const uint32_t lo1 = quotients_e4m3x2(raw.z, s2, neg_s2, r2), hi1 = quotients_e4m3x2(raw.w, s2, neg_s2, r2);
@@ -56,6 +55,17 @@ __device__ __forceinline__ uint2 quantise8(uint4 raw, float s) {
 // lanes then move the token's num_kv_heads * head_dim / 8 vectors, kInFlight loads ahead of the stores.
 template <bool kFp8>
 __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(const KvWriteParams p) {
+  extern __shared__ float s_scale[];                       // E4M3 only: [tensor][head] scale, then reciprocal
+  if (kFp8) {
+    for (int i = threadIdx.x; i < 2 * p.num_kv_heads; i += kWriteThreads) {
+      const int which = i >= p.num_kv_heads, head = i - which * p.num_kv_heads;
+      const float* scales = which ? p.v_scale : p.k_scale;
+      const float sc = scales ? __ldg(scales + head * (which ? p.v_scale_head_stride : p.k_scale_head_stride)) : 1.f;
+      s_scale[i] = sc;
+      s_scale[2 * p.num_kv_heads + i] = __frcp_rn(sc);     // correctly rounded, once per CTA and head
+    }
+    __syncthreads();
+  }
   const int lane = threadIdx.x & 31;
   const int vec_per_row = p.head_dim >> 3;                 // 16-byte vectors per (token, head) row
   const int vec_per_tok = p.num_kv_heads * vec_per_row;
@@ -74,8 +84,7 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
     const long long dst_tok = which ? page * p.vc_page_stride + in_page * p.vc_row_stride
                                     : page * p.kc_page_stride + in_page * p.kc_row_stride;
     uint8_t* cache = reinterpret_cast<uint8_t*>(which ? p.value_cache : p.key_cache);
-    const float* scales = which ? p.v_scale : p.k_scale;
-    const long long scale_stride = which ? p.v_scale_head_stride : p.k_scale_head_stride;
+    const float* head_scale = s_scale + which * p.num_kv_heads;
     for (int v0 = lane; v0 < vec_per_tok; v0 += 32 * kInFlight) {
       uint4 raw[kInFlight];
       int head[kInFlight], vec[kInFlight];
@@ -91,8 +100,8 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
         if (v0 + u * 32 >= vec_per_tok) continue;
         const long long off = dst_tok + head[u] * dst_head + vec[u] * 8;     // in cache elements
         if (kFp8) {
-          const float scale = scales ? __ldg(scales + head[u] * scale_stride) : 1.f;
-          *reinterpret_cast<uint2*>(cache + off) = quantise8(raw[u], scale);
+          *reinterpret_cast<uint2*>(cache + off) =
+              quantise8(raw[u], head_scale[head[u]], head_scale[2 * p.num_kv_heads + head[u]]);
         } else {
           *reinterpret_cast<uint4*>(cache + off * 2) = raw[u];
         }
@@ -177,7 +186,9 @@ cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cuda
   long long ctas = (units + warps_per_cta - 1) / warps_per_cta;
   const long long cap = (long long)sm_count * 8;   // 8 resident CTAs of 256 threads per SM, then the warps stride on
   if (ctas > cap) ctas = cap;
-  if (fp8) return launch_kernel(atrex_sm100_kv_write_kernel<true>, dim3((unsigned)ctas), dim3(kWriteThreads), 0, stream, p);
+  if (fp8)
+    return launch_kernel(atrex_sm100_kv_write_kernel<true>, dim3((unsigned)ctas), dim3(kWriteThreads),
+                         sizeof(float) * 4 * p.num_kv_heads, stream, p);
   return launch_kernel(atrex_sm100_kv_write_kernel<false>, dim3((unsigned)ctas), dim3(kWriteThreads), 0, stream, p);
 }
 

@@ -515,6 +515,7 @@ static int kv_fill(const atrex_fa_sm100_kv_write_params* p, bool need_cache, atr
     return fail(ATREX_FA_ABI_MISMATCH, "kv-write parameter block does not match this library");
   if (p->num_tokens < 0 || p->num_kv_heads <= 0 || p->head_dim <= 0 || p->page_size <= 0)
     return fail(ATREX_FA_INVALID_VALUE, "negative or zero size");
+  if (p->num_kv_heads > 1024) return fail(ATREX_FA_UNSUPPORTED, "more than 1024 KV heads");   // per-head shared-memory tables
   bool fp8 = false;
   if (need_cache) {
     if (p->cache_dtype != ATREX_FA_BF16 && p->cache_dtype != ATREX_FA_E4M3)
