@@ -7,7 +7,8 @@ call.  This module allocates what the caller did not pass (``out``, ``lse``), as
 the native launcher how much call-local scratch the call needs, takes it from the
 torch allocator (so a CUDA-graph pool owns it during capture and nothing is
 retained between calls, as the reference requires:
-src/nvidia/flash_attn/sm103/decode_runtime.py:829-847) and issues the custom op.
+src/nvidia/flash_attn/sm103/decode_runtime.py:829-847) and enqueues the call: directly through
+the C ABI in eager mode, through the custom op ``atrex_sm100::fa_fwd`` when a tracer is compiling.
 The route and the split count are resolved inside the native launcher from
 graph-static sizes only.
 """
@@ -38,9 +39,14 @@ def forward(*, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, max_seqlen_q, max
     args = (q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, page_table, q_descale, k_descale,
             v_descale, learnable_sink, status, int(max_seqlen_q), int(max_seqlen_k), float(softmax_scale),
             float(softcap), bool(causal), window_left, window_right, int(num_splits), int(route))
-    info = runtime.plan(runtime.build_params(*args))
+    params = runtime.build_params(*args)
+    info = runtime.plan(params)
     workspace = None
     if info.workspace_bytes:
         workspace = torch.empty(info.workspace_bytes, dtype=torch.uint8, device=q.device)
-    runtime.fa_fwd(q, k, v, out, lse, workspace, *args[5:])
+    if torch.compiler.is_compiling():
+        # under a tracer the call must be an operator the tracer can see
+        runtime.fa_fwd(q, k, v, out, lse, workspace, *args[5:])
+    else:
+        runtime.launch_params(params, workspace, q.device)
     return out, lse

@@ -202,6 +202,15 @@ def _fa_fwd_cuda(q, k, v, out, lse, workspace, cu_seqlens_q, cu_seqlens_k, sequs
     raise_for_status(load_library().atrex_fa_sm100_forward(ctypes.byref(params), ws_ptr, ws_bytes, stream))
 
 
+def launch_params(params: Params, workspace, device) -> None:
+    """Enqueue a call whose parameter block is already built (eager path: no dispatcher round trip, the block
+    that was planned is the block that runs)."""
+    ws_ptr = None if workspace is None else workspace.data_ptr()
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    raise_for_status(load_library().atrex_fa_sm100_forward(ctypes.byref(params), ws_ptr, ws_bytes, stream))
+
+
 def _fa_fwd_meta(*args):
     return None
 

@@ -476,6 +476,27 @@ def test_scratch_is_call_local():
     assert torch.cuda.memory_allocated() <= baseline + 256 * 1024
 
 
+def test_custom_op_path_matches_the_eager_path():
+    """Eager calls go straight to the C ABI; under a tracer the same call is the operator atrex_sm100::fa_fwd.
+    Both enqueue the same kernels: identical output for a decode and a prefill case."""
+    from atrex import flash_attn_varlen_func
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    for case in (T.make_case(64, [1] * 4, [3000, 17, 640, 2049], hq=32, hkv=8),
+                 T.make_case(64, [300, 100], [300, 400], hq=8, hkv=2)):
+        out, lse = flash_attn_varlen_func(**case, return_softmax_lse=True)
+        out2, lse2 = torch.empty_like(out), torch.empty_like(lse)
+        args = (case["q"], case["k"], case["v"], out2, lse2, case["cu_seqlens_q"], None, case["seqused_k"],
+                case["block_table"], None, None, None, None, runtime.device_status(out.device),
+                case["max_seqlen_q"], case["max_seqlen_k"], case["softmax_scale"], 0.0, True, -1, -1, 0,
+                runtime.ROUTE_AUTO)
+        info = runtime.plan(runtime.build_params(*args))
+        ws = torch.empty(max(1, info.workspace_bytes), dtype=torch.uint8, device=out.device)
+        torch.ops.atrex_sm100.fa_fwd(*args[:5], ws, *args[5:])
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2) and torch.equal(lse, lse2)
+
+
 def test_only_atrex_kernels_run():
     """Every compute kernel the public call launches carries the atrex_ prefix (reference:
     op_test/utils/flash_attn_contract.py:178-212)."""
