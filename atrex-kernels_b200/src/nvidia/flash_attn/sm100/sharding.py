@@ -75,3 +75,39 @@ def gather_heads(local_out, world_size: int, group=None):
     staged = torch.empty((world_size * total_q, heads, dim), dtype=local_out.dtype, device=local_out.device)
     dist.all_gather_into_tensor(staged, local_out.contiguous(), group=group)
     return staged.view(world_size, total_q, heads, dim).permute(1, 0, 2, 3).reshape(total_q, world_size * heads, dim)
+
+
+def merge_partial_attention(partial_out, partial_lse):
+    """Merge attention computed over disjoint key sets: ``partial_out [W, total_q, Hq, D]``, ``partial_lse
+    [W, Hq, total_q]`` (natural log, ``-inf`` where a part saw no key) -> ``(out [total_q, Hq, D], lse [Hq, total_q])``.
+
+    ``out = sum_w exp(lse_w - lse) * out_w`` with ``lse = logsumexp_w lse_w``: the same algebra as the split-KV
+    combine kernel (and the reference's, src/nvidia/flash_attn/sm103/decode_reduce_cutedsl.py:71-152), here across
+    ranks instead of across splits.  Parts without keys get weight 0 and their (arbitrary) output is not read.
+    """
+    import torch
+
+    lse = torch.logsumexp(partial_lse.float(), dim=0)                               # [Hq, total_q]
+    weight = torch.exp(partial_lse.float() - torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse)))
+    weight = torch.where(torch.isfinite(partial_lse), weight, torch.zeros_like(weight))      # [W, Hq, total_q]
+    contrib = torch.where(weight.permute(0, 2, 1).unsqueeze(-1) > 0, partial_out.float(), torch.zeros((), device=partial_out.device))
+    out = (contrib * weight.permute(0, 2, 1).unsqueeze(-1)).sum(dim=0)
+    return out.to(partial_out.dtype), lse
+
+
+def gather_context_parallel(local_out, local_lse, world_size: int, group=None):
+    """Decode context parallelism: every rank holds a disjoint shard of each request's KV cache, attends its own
+    shard (``return_softmax_lse=True``; for a query length of 1 every local key is visible) and this function
+    all-gathers the ``(O, LSE)`` pairs over NCCL and merges them.  Returns the full ``(out, lse)`` on every rank.
+    Two ``all_gather_into_tensor`` calls on this GPU's own tensors; with ``world_size == 1`` it is the identity."""
+    import torch
+    import torch.distributed as dist
+
+    if world_size == 1:
+        return local_out, local_lse
+    outs = torch.empty((world_size,) + tuple(local_out.shape), dtype=local_out.dtype, device=local_out.device)
+    lses = torch.empty((world_size,) + tuple(local_lse.shape), dtype=local_lse.dtype, device=local_lse.device)
+    dist.all_gather_into_tensor(outs.view(-1, *local_out.shape[1:]), local_out.contiguous(), group=group)
+    dist.all_gather_into_tensor(lses.view(-1, *local_lse.shape[1:]), local_lse.contiguous(), group=group)
+    return merge_partial_attention(outs, lses)
+

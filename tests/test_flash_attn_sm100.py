@@ -11,6 +11,8 @@ pins their numerics; for them the oracle in oracle/fa_oracle.py is the definitio
 import os
 import re
 
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -495,6 +497,44 @@ def test_custom_op_path_matches_the_eager_path():
         torch.ops.atrex_sm100.fa_fwd(*args[:5], ws, *args[5:])
         torch.cuda.synchronize()
         assert torch.equal(out, out2) and torch.equal(lse, lse2)
+
+
+def test_decode_context_parallel_merge_of_two_shards():
+    """Decode context parallelism emulated on one GPU: every request's pages are dealt alternately to two shards,
+    each shard is attended on its own (with LSE) and the two (O, LSE) pairs are merged the way
+    sharding.gather_context_parallel merges ranks; equals attention over the whole cache."""
+    from atrex import flash_attn_varlen_func
+    from atrex.src.nvidia.flash_attn.sm100 import sharding
+
+    page = 64
+    kv_lens = [1000, 64, 333, 5000, 1]
+    case = T.make_case(page, [1] * len(kv_lens), kv_lens, hq=32, hkv=8)
+    full_o, full_l = flash_attn_varlen_func(**case, return_softmax_lse=True)
+    table = case["block_table"].cpu()
+    outs, lses = [], []
+    for shard in range(2):
+        width = (table.shape[1] + 1) // 2
+        sub = torch.full((len(kv_lens), max(width, 1)), -1, dtype=torch.int32)
+        used = []
+        for b, n in enumerate(kv_lens):
+            pages = math.ceil(n / page)
+            mine = list(range(shard, pages, 2))
+            tokens = sum(min(page, n - j * page) for j in mine)
+            # a shard's pages are all full except possibly the request's last page, which must come last
+            order = sorted(mine, key=lambda j: (j == pages - 1))
+            for slot, j in enumerate(order):
+                sub[b, slot] = table[b, j]
+            used.append(tokens)
+        part = dict(case, block_table=sub.cuda(), seqused_k=torch.tensor(used, dtype=torch.int32).cuda(),
+                    max_seqlen_k=sub.shape[1] * page)
+        o, l = flash_attn_varlen_func(**part, return_softmax_lse=True)
+        outs.append(o)
+        lses.append(l)
+    got_o, got_l = sharding.merge_partial_attention(torch.stack(outs), torch.stack(lses))
+    torch.cuda.synchronize()
+    assert (got_o.float() - full_o.float()).abs().max().item() <= T.BF16_O_ATOL
+    assert torch.allclose(got_l, full_l, rtol=T.LSE_RTOL, atol=T.LSE_RTOL)
+    assert float(lses[1][0, 4]) == float("-inf")          # the one-key request has nothing on shard 1
 
 
 def test_only_atrex_kernels_run():

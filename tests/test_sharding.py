@@ -87,6 +87,30 @@ def _worker(rank, world, port, result_dir):
         gathered = sharding.gather_heads(local_out, world)
         expect = np.concatenate([full[b] for b in range(len(q_lens))])
         np.testing.assert_allclose(gathered.numpy(), expect, rtol=0, atol=0)
+        # (3) decode context parallelism: query length 1, each rank holds every world-th key of every request
+        #     (one request's local shard is empty on rank 1), partial (O, LSE) all-gathered and merged
+        dq = rng.standard_normal((len(kv_lens), hq, d)).astype(np.float32)
+        dkv = [1 if b == 2 else n for b, n in enumerate(kv_lens)]          # request 2 has a single key
+        cu1 = np.arange(len(kv_lens) + 1, dtype=np.int32)
+        want_o = np.zeros_like(dq)
+        want_l = np.zeros((hq, len(kv_lens)), np.float32)
+        loc_o = np.zeros_like(dq)
+        loc_l = np.full((hq, len(kv_lens)), -np.inf, np.float32)
+        for b, n in enumerate(dkv):
+            o, l = fa_oracle.attention(dq[b:b + 1], k[b][:n], v[b][:n], np.array([0, 1], np.int32),
+                                       cu_seqlens_k=np.array([0, n], np.int32), causal=True)
+            want_o[b], want_l[:, b] = o[0], l[:, 0]
+            mine_k, mine_v = k[b][:n][rank::world], v[b][:n][rank::world]
+            if len(mine_k):
+                o, l = fa_oracle.attention(dq[b:b + 1], mine_k, mine_v, np.array([0, 1], np.int32),
+                                           cu_seqlens_k=np.array([0, len(mine_k)], np.int32), causal=True)
+                loc_o[b], loc_l[:, b] = o[0], l[:, 0]
+            else:
+                loc_o[b] = np.nan                                           # must never be read
+        assert cu1[-1] == len(dkv)
+        got_o, got_l = sharding.gather_context_parallel(torch.from_numpy(loc_o), torch.from_numpy(loc_l), world)
+        np.testing.assert_allclose(got_o.numpy(), want_o, rtol=0, atol=2e-6)
+        np.testing.assert_allclose(got_l.numpy(), want_l, rtol=0, atol=2e-6)
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -96,3 +120,13 @@ def test_two_rank_request_sharding_and_head_gather(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_merge_partial_attention_handles_empty_parts():
+    out = torch.tensor([[[[1.0, 2.0]]], [[[float("nan"), float("nan")]]], [[[3.0, 6.0]]]])      # [W=3, T=1, H=1, D=2]
+    lse = torch.tensor([[[0.0]], [[float("-inf")]], [[0.0]]])                                      # [W, H, T]
+    merged, total = sharding.merge_partial_attention(out, lse)
+    assert torch.allclose(merged, torch.tensor([[[2.0, 4.0]]])) and torch.allclose(total, torch.log(torch.tensor([[2.0]])))
+    merged, total = sharding.merge_partial_attention(out[1:2], lse[1:2])                            # no key anywhere
+    assert torch.equal(merged, torch.zeros(1, 1, 2)) and total.item() == float("-inf")
+
