@@ -143,6 +143,47 @@ atrex_sm100_plan_kernel(const __grid_constant__ FwdParams p, int m_rows, int32_t
   if (tid == 0) tile_prefix[B] = carry;
 }
 
+// Merge of attention computed over disjoint key sets by different ranks (context parallelism): parts
+// [W, total_q, Hq, D] BF16 with natural-log LSE [W, Hq, total_q] -> out [total_q, Hq, D] BF16, lse [Hq, total_q].
+// One warp per (query row, head); same algebra as the split combine above, natural-log domain, BF16 partials.
+// A part with LSE = -inf has weight 0 and its output row (possibly NaN) is not read.
+__global__ void __launch_bounds__(kCombineWarps * 32)
+atrex_sm100_merge_parts_kernel(const __nv_bfloat16* __restrict__ parts, const float* __restrict__ part_lse,
+                               __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int world, int64_t total_q,
+                               int num_q_heads, int head_dim) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);   // (query, head), head fastest
+  if (row >= total_q * num_q_heads) return;
+  const int64_t q = row / num_q_heads;
+  const int h = (int)(row - q * num_q_heads);
+  const int64_t lse_stride = (int64_t)num_q_heads * total_q, lse_off = (int64_t)h * total_q + q;
+  float mx = -INFINITY;
+  for (int w = 0; w < world; ++w) mx = fmaxf(mx, part_lse[w * lse_stride + lse_off]);
+  float denom = 0.f;
+  float acc[8];                                            // head_dim <= 256: 8 elements per lane
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const int per_lane = head_dim / 32;
+  if (mx != -INFINITY) {
+    for (int w = 0; w < world; ++w) {
+      const float l = part_lse[w * lse_stride + lse_off];
+      if (l == -INFINITY) continue;
+      const float wgt = __expf(l - mx);
+      denom += wgt;
+      const __nv_bfloat16* src = parts + ((int64_t)w * total_q * num_q_heads + row) * head_dim + lane * per_lane;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < per_lane) acc[i] += wgt * __bfloat162float(src[i]);
+    }
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  __nv_bfloat16* dst = out + row * head_dim + lane * per_lane;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (i < per_lane) dst[i] = __float2bfloat16(acc[i] * inv);
+  if (lane == 0) lse[lse_off] = denom > 0.f ? mx + __logf(denom) : -INFINITY;
+}
+
 }  // namespace
 
 cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream) {
@@ -158,6 +199,16 @@ cudaError_t plan_launch(const FwdParams& p, int m_rows, int32_t* order, int32_t*
                         cudaStream_t stream) {
   return launch_kernel(atrex_sm100_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, p, m_rows, order,
                        tile_prefix);
+}
+
+cudaError_t merge_parts_launch(const void* parts, const float* part_lse, void* out, float* lse, int world,
+                               int64_t total_q, int num_q_heads, int head_dim, cudaStream_t stream) {
+  const int64_t rows = total_q * num_q_heads;
+  if (rows == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((rows + kCombineWarps - 1) / kCombineWarps);
+  return launch_kernel(atrex_sm100_merge_parts_kernel, dim3(grid), dim3(kCombineWarps * 32), 0, stream,
+                       static_cast<const __nv_bfloat16*>(parts), part_lse, static_cast<__nv_bfloat16*>(out), lse, world,
+                       total_q, num_q_heads, head_dim);
 }
 
 }  // namespace atrex_sm100

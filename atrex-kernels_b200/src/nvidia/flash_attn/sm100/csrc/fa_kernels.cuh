@@ -42,6 +42,9 @@ cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_coun
 
 // ---- fa_combine.cu: merge split partials; tile plan ----
 cudaError_t combine_launch(const FwdParams& p, int head_dim, cudaStream_t stream);
+// merge of per-rank (O, natural-log LSE) pairs computed over disjoint key sets (context parallelism)
+cudaError_t merge_parts_launch(const void* parts, const float* part_lse, void* out, float* lse, int world,
+                               int64_t total_q, int num_q_heads, int head_dim, cudaStream_t stream);
 // order[batch], tile_prefix[batch + 1] for row tiles of m_rows packed rows
 cudaError_t plan_launch(const FwdParams& p, int m_rows, int32_t* order, int32_t* tile_prefix,
                         cudaStream_t stream);

@@ -593,4 +593,20 @@ int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* p, float* k_s
   return ATREX_FA_OK;
 }
 
+int atrex_fa_sm100_merge_parts(const void* parts, const float* part_lse, void* out, float* lse, int32_t world,
+                               int64_t total_q, int32_t num_q_heads, int32_t head_dim, void* stream) {
+  using namespace atrex_sm100;
+  if (world <= 0 || total_q < 0 || num_q_heads <= 0) return fail(ATREX_FA_INVALID_VALUE, "negative or zero size");
+  if (head_dim <= 0 || head_dim % 32 || head_dim > 256) return fail(ATREX_FA_UNSUPPORTED, "head_dim must be a multiple of 32 up to 256");
+  if (total_q == 0) return ATREX_FA_OK;
+  if (!parts || !part_lse || !out || !lse) return fail(ATREX_FA_INVALID_VALUE, "null tensor pointer");
+  DeviceInfo* dev = nullptr;
+  int st = current_device(&dev);
+  if (st != ATREX_FA_OK) return st;
+  cudaError_t e = merge_parts_launch(parts, part_lse, out, lse, world, total_q, num_q_heads, head_dim,
+                                     static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(ATREX_FA_CUDA_ERROR, "merge kernel launch", e);
+  return ATREX_FA_OK;
+}
+
 }  // extern "C"

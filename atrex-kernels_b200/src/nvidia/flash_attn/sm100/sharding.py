@@ -109,5 +109,31 @@ def gather_context_parallel(local_out, local_lse, world_size: int, group=None):
     lses = torch.empty((world_size,) + tuple(local_lse.shape), dtype=local_lse.dtype, device=local_lse.device)
     dist.all_gather_into_tensor(outs.view(-1, *local_out.shape[1:]), local_out.contiguous(), group=group)
     dist.all_gather_into_tensor(lses.view(-1, *local_lse.shape[1:]), local_lse.contiguous(), group=group)
+    if local_out.is_cuda and local_out.dtype == torch.bfloat16 and local_lse.dtype == torch.float32:
+        return _merge_parts_native(outs, lses)              # one kernel instead of a chain of element-wise ones
     return merge_partial_attention(outs, lses)
+
+
+def _merge_parts_native(outs, lses):
+    """``merge_partial_attention`` as one launch of the library's merge kernel (BF16 parts, FP32 LSE, CUDA)."""
+    import ctypes
+
+    import torch
+
+    from . import runtime
+
+    lib = runtime.load_library()
+    fn = lib.atrex_fa_sm100_merge_parts
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
+                   ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    world, total_q, heads, dim = outs.shape
+    outs, lses = outs.contiguous(), lses.contiguous()
+    out = torch.empty((total_q, heads, dim), dtype=torch.bfloat16, device=outs.device)
+    lse = torch.empty((heads, total_q), dtype=torch.float32, device=outs.device)
+    with torch.cuda.device(outs.device):
+        stream = torch.cuda.current_stream(outs.device).cuda_stream
+        runtime.raise_for_status(fn(outs.data_ptr(), lses.data_ptr(), out.data_ptr(), lse.data_ptr(), world, total_q,
+                                    heads, dim, stream))
+    return out, lse
 

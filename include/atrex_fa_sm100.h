@@ -244,6 +244,20 @@ ATREX_FA_API int atrex_fa_sm100_kv_cache_write(const atrex_fa_sm100_kv_write_par
 ATREX_FA_API int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* p, float* k_scale_out,
                                           float* v_scale_out, void* scratch, void* stream);
 
+/*
+ * Context parallelism, the merge step: `parts` [world, total_q, num_q_heads, head_dim] BF16 and `part_lse`
+ * [world, num_q_heads, total_q] FP32 natural log are the outputs of atrex_fa_sm100_forward (with return_lse) of
+ * `world` ranks that each attended a disjoint shard of every request's keys, gathered into this GPU's memory
+ * (e.g. by an NCCL all-gather).  Writes out [total_q, num_q_heads, head_dim] BF16 and lse [num_q_heads, total_q]:
+ * out = sum_w exp(lse_w - lse) out_w, lse = logsumexp_w lse_w; a part with lse = -inf is not read.  All tensors
+ * dense; head_dim a multiple of 32 up to 256.  Same algebra as the split-KV combine
+ * (src/nvidia/flash_attn/sm103/decode_reduce_cutedsl.py:71-152), across ranks instead of across splits.  The
+ * reference rejects context parallelism (python/atrex/api/flash_attn.py:128-135); this has no counterpart there.
+ */
+ATREX_FA_API int atrex_fa_sm100_merge_parts(const void* parts, const float* part_lse, void* out, float* lse,
+                                            int32_t world, int64_t total_q, int32_t num_q_heads, int32_t head_dim,
+                                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -535,6 +535,16 @@ def test_decode_context_parallel_merge_of_two_shards():
     assert (got_o.float() - full_o.float()).abs().max().item() <= T.BF16_O_ATOL
     assert torch.allclose(got_l, full_l, rtol=T.LSE_RTOL, atol=T.LSE_RTOL)
     assert float(lses[1][0, 4]) == float("-inf")          # the one-key request has nothing on shard 1
+    # the library's merge kernel (what gather_context_parallel uses on CUDA) against the torch formulation
+    nat_o, nat_l = sharding._merge_parts_native(torch.stack(outs), torch.stack(lses))
+    torch.cuda.synchronize()
+    assert (nat_o.float() - got_o.float()).abs().max().item() <= 2e-2 * max(1.0, got_o.float().abs().max().item()) / 4
+    assert torch.allclose(nat_l, got_l, rtol=1e-5, atol=1e-5)
+    assert (nat_o.float() - full_o.float()).abs().max().item() <= T.BF16_O_ATOL
+    poisoned = torch.stack(outs).clone()
+    poisoned[1, 4] = float("nan")                          # the empty shard's row must not be read
+    nat_o2, _ = sharding._merge_parts_native(poisoned, torch.stack(lses))
+    assert torch.equal(nat_o2, nat_o)
 
 
 def test_only_atrex_kernels_run():
