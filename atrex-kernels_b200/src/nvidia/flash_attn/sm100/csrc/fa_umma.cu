@@ -161,7 +161,7 @@ constexpr float kRescaleThreshold = 8.f;
 
 // Pairs of every 8 whose exponential is a polynomial on the FMA pipe (the rest use the MUFU pipe).
 #ifndef ATREX_UMMA2_POLY_OF8
-#define ATREX_UMMA2_POLY_OF8 2
+#define ATREX_UMMA2_POLY_OF8 0
 #endif
 constexpr int kPolyOf8 = ATREX_UMMA2_POLY_OF8;
 #ifndef ATREX_UMMA2_P_FIRST_CHUNKS

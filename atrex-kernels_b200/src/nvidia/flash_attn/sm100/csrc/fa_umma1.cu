@@ -37,7 +37,7 @@ namespace {
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
 #ifndef ATREX_UMMA1_POLY_OF8
-#define ATREX_UMMA1_POLY_OF8 3
+#define ATREX_UMMA1_POLY_OF8 1
 #endif
 constexpr int kPolyOf8_1 = ATREX_UMMA1_POLY_OF8;   // pairs of every 8 whose exponential runs on the FMA pipe
 constexpr int kSoftmaxWarps1 = 8;                 // two threads per row: 2 x 4 warps
