@@ -7,7 +7,17 @@ signature, argument meaning, return convention and exception types
 (:98-277) restated for the one target this build serves, ``("nvidia", "sm100")``,
 with the features the reference's NVIDIA targets refuse but this build runs:
 head_dim 128 and 256, sliding windows, ``s_aux`` sinks in prefill and decode,
-softcap, and ``num_splits`` up to 256.
+softcap, ``num_splits`` up to 256, and context parallelism over the keys
+(``cp_world_size``, ``cp_rank``, ``cp_tot_seqused_k``; the reference rejects all
+three, python/atrex/api/flash_attn.py:128-135).
+
+Context parallelism: rank ``r`` of ``W`` holds every ``W``-th key of each request
+(its local key ``j`` is the request's key ``j * W + r``, the layout serving engines
+use for decode context parallelism); ``seqused_k`` gives the LOCAL lengths and
+``cp_tot_seqused_k`` the totals.  Query row ``i`` of a request with ``q_len`` rows
+sits at position ``tot - q_len + i`` and sees local key ``j`` iff
+``j * W + r <= tot - q_len + i``.  Each rank's call returns its partial ``(out,
+lse)``; ``atrex.src.nvidia.flash_attn.sm100.sharding`` merges them across ranks.
 
 Conventions: a malformed call raises ``ValueError``; a well-formed call that this
 build does not run raises ``NotImplementedError``; the message names the offending
@@ -36,9 +46,6 @@ _UNSUPPORTED_ARGUMENTS = (
     ("max_seqlen_k_prefill", 0, "Atrex does not consume provider-specific prefill/decode counters (max_seqlen_k_prefill)"),
     ("dropout_p", 0, "Atrex attention supports inference without dropout (dropout_p)"),
     ("return_attn_probs", False, "Atrex attention does not return probabilities (return_attn_probs)"),
-    ("cp_world_size", 1, "Atrex attention does not yet support context parallelism (cp_world_size)"),
-    ("cp_rank", 0, "Atrex attention does not yet support context parallelism (cp_rank)"),
-    ("cp_tot_seqused_k", None, "Atrex attention does not yet support context parallelism (cp_tot_seqused_k)"),
     ("alibi_slopes", None, "Atrex attention does not support ALiBi (alibi_slopes)"),
     ("q_v", None, "Atrex standard attention does not support auxiliary Q/MLA (q_v)"),
     ("qv", None, "Atrex standard attention does not support auxiliary Q/MLA (qv)"),
@@ -91,6 +98,30 @@ def _validate_descales(call, torch, batch, num_kv_heads):
             raise ValueError("FP8 descales must be float32 [batch,num_kv_heads] on the Q device")
 
 
+def _validate_context_parallel(call, torch, batch, window):
+    """``cp_world_size`` ranks each hold every ``cp_world_size``-th key; see the module docstring."""
+    world, rank, total = call["cp_world_size"], call["cp_rank"], call["cp_tot_seqused_k"]
+    if not isinstance(world, int) or not isinstance(rank, int) or isinstance(world, bool) or isinstance(rank, bool):
+        raise ValueError("cp_world_size and cp_rank must be Python ints")
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("cp_rank must lie in [0, cp_world_size) and cp_world_size must be positive")
+    if world == 1:
+        if total is not None:
+            raise ValueError("cp_tot_seqused_k is only meaningful with cp_world_size > 1")
+        return
+    q = call["q"]
+    if total is None:
+        raise ValueError("context parallelism (cp_world_size > 1) requires cp_tot_seqused_k")
+    if total.shape != (batch,) or total.dtype != torch.int32 or total.device != q.device or total.stride(0) != 1:
+        raise ValueError("cp_tot_seqused_k must be a contiguous int32 [batch] on the Q device")
+    if call["seqused_k"] is None:
+        raise ValueError("context parallelism requires seqused_k (the local key counts)")
+    if not call["causal"]:
+        raise NotImplementedError("Atrex sm100 context parallelism serves causal attention only (causal)")
+    if window[0] >= 0 or window[1] > 0:
+        raise NotImplementedError("Atrex sm100 context parallelism does not support a sliding window (window_size)")
+
+
 def _validate_sm100_call(call, torch, batch, window, softcap):
     """Checks specific to the sm_100a kernels (the reference's per-target block is :51-88)."""
     q, k, v = call["q"], call["k"], call["v"]
@@ -128,6 +159,7 @@ def _validate_sm100_call(call, torch, batch, window, softcap):
         raise NotImplementedError("Atrex sm100 attention indexes rows and pages with 32 bits")
     if block_table is None and call["cu_seqlens_k"] is None:
         raise NotImplementedError("Atrex sm100 packed K/V requires cu_seqlens_k")
+    _validate_context_parallel(call, torch, batch, window)
     if q.dtype == torch.float8_e4m3fn:
         if not _FP8_ROUTE_BUILT:
             raise NotImplementedError("Atrex sm100 attention does not serve float8_e4m3fn yet (BF16 only)")
@@ -371,6 +403,9 @@ def flash_attn_varlen_func(
             k_descale=k_descale,
             v_descale=v_descale,
             num_splits=num_splits,
+            cp_world_size=cp_world_size,
+            cp_rank=cp_rank,
+            cp_tot_seqused_k=cp_tot_seqused_k,
         )
     return (output, lse) if return_softmax_lse else output
 

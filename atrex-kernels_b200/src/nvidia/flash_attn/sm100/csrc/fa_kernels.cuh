@@ -63,6 +63,7 @@ struct KvWriteParams {
   long long kc_page_stride, kc_row_stride, kc_head_stride, vc_page_stride, vc_row_stride, vc_head_stride;
   long long k_scale_head_stride, v_scale_head_stride;
   int num_tokens, num_kv_heads, head_dim, page_size;
+  long long slot_limit;   // num_pages * page_size when the caller gave the pool size, else the largest value
 };
 cudaError_t kv_write_launch(const KvWriteParams& p, bool fp8, int sm_count, cudaStream_t stream);
 // Per-head E4M3 scales (max |x| / 448) of the rows a write would store; `amax` is 2 * num_kv_heads words of scratch.

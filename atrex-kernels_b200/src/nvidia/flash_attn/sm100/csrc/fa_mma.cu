@@ -104,11 +104,11 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
   request_kv(p, b, kv_len, k_start);
 
   // ---- key range this row tile can see, then this split's share of its tiles ----
-  const int off = kv_len - q_len;
+  const int off = request_off(p, b, kv_len, q_len);
   const int qi_lo = row0 / p.group;
   const int qi_hi = min(q_len - 1, (row0 + M - 1) / p.group);
   int kv_end = kv_len, kv_begin = 0;
-  if (p.window_right >= 0) kv_end = min(kv_len, qi_hi + off + p.window_right + 1);
+  if (p.window_right >= 0) kv_end = min(kv_len, right_bound(p, qi_hi + off));
   if (p.window_left >= 0) kv_begin = max(0, qi_lo + off - p.window_left);
   int tile_lo = 0, tile_hi = 0;
   if (kv_end > kv_begin) {
@@ -223,12 +223,12 @@ atrex_sm100_fwd_mma_kernel(const __grid_constant__ FwdParams p) {
     for (int h = 0; h < 2; ++h) {
       const int row = row0 + wm * 16 + g + h * 8;
       const int qi = min(row / p.group, q_len - 1);
-      vis_hi[h] = p.window_right >= 0 ? min(kv_len, qi + off + p.window_right + 1) : kv_len;
+      vis_hi[h] = p.window_right >= 0 ? min(kv_len, right_bound(p, qi + off)) : kv_len;
       vis_lo[h] = p.window_left >= 0 ? max(0, qi + off - p.window_left) : 0;
     }
     // tiles fully inside [full_lo, full_hi) need no mask
     const int full_lo = p.window_left >= 0 ? max(0, qi_hi + off - p.window_left) : 0;
-    const int full_hi = p.window_right >= 0 ? min(kv_len, qi_lo + off + p.window_right + 1) : kv_len;
+    const int full_hi = p.window_right >= 0 ? min(kv_len, right_bound(p, qi_lo + off)) : kv_len;
 
     float dq = 1.f, dk = 1.f;
     if (p.q_descale) dq = p.q_descale[b * p.q_descale_bs + kvh * p.q_descale_hs];

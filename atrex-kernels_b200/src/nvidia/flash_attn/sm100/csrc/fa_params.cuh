@@ -32,6 +32,7 @@ struct alignas(64) FwdParams {
   const float* k_descale;
   const float* v_descale;
   const __nv_bfloat16* sink;
+  const int32_t* cp_tot_seqused_k;   // total keys per request over all context-parallel ranks (cp_world_size > 1)
   int32_t* status;
 
   // split-KV scratch: normalised partial O [splits, total_q, Hq, D] f32 and
@@ -63,6 +64,9 @@ struct alignas(64) FwdParams {
   int32_t num_splits;
   int32_t num_row_tiles;  // upper bound of row tiles (grid sizing); batch when order == null
   int32_t q_via_tma;      // single-tile tcgen05 kernel: Q tile arrives by TMA (GQA group divides 128)
+  int32_t kv_cap;         // paged: block_table width x page_size, the most keys a request's table row can name
+  int32_t cp_world_size;  // context-parallel ranks (1 = off): local key j is the request's key j * world + rank
+  int32_t cp_rank;
   float softmax_scale;
   float softcap;
   // position (1..3, minus 1) of the head / row / page coordinate in each tensor map
@@ -70,16 +74,39 @@ struct alignas(64) FwdParams {
   int8_t v_perm[3];
 };
 
-// KV length and the first K row (packed K/V) of request b.
+// KV length and the first K row (packed K/V) of request b.  Lengths are clamped to what the caller's buffers can
+// hold, so a stale or corrupt length (a graph replayed after its metadata was overwritten) never becomes an
+// out-of-range page-table or row index: paged, at most the table row's width in keys; packed, at most the rows
+// left in the K/V tensor.
 __device__ __forceinline__ void request_kv(const FwdParams& p, int b, int& kv_len, int& k_start) {
   k_start = 0;
   if (p.cu_seqlens_k != nullptr) {
     k_start = p.cu_seqlens_k[b];
     kv_len = p.cu_seqlens_k[b + 1] - k_start;
+    if (p.seqused_k != nullptr) kv_len = min(kv_len, p.seqused_k[b]);
+    if (k_start < 0 || k_start > p.total_k) kv_len = 0;
+    else kv_len = min(kv_len, p.total_k - k_start);
   } else {
-    kv_len = p.seqused_k[b];
+    kv_len = min(p.seqused_k[b], p.kv_cap);
   }
   if (kv_len < 0) kv_len = 0;
+}
+
+// Distance from a query index to the last key it may see: row i of a request sees keys up to i + off.  Without
+// context parallelism off = kv_len - q_len (bottom-right alignment); with it, positions are the request's global
+// ones and off = total keys - q_len.
+__device__ __forceinline__ int request_off(const FwdParams& p, int b, int kv_len, int q_len) {
+  return (p.cp_world_size > 1 ? p.cp_tot_seqused_k[b] : kv_len) - q_len;
+}
+
+// Exclusive upper bound of the LOCAL key indices row `qi` may see when the call has a right bound
+// (window_right >= 0, which causal implies); the caller clamps it to [.., kv_len].  `pos` = qi + request_off().
+__device__ __forceinline__ int right_bound(const FwdParams& p, int pos) {
+  if (p.cp_world_size > 1) {
+    const int t = pos - p.cp_rank;               // local key j is global key j * world + rank
+    return t < 0 ? 0 : t / p.cp_world_size + 1;
+  }
+  return pos + p.window_right + 1;
 }
 
 }  // namespace atrex_sm100

@@ -83,11 +83,11 @@ __device__ __forceinline__ bool decode_item(const FwdParams& p, int item, Item& 
   it.q_len = p.cu_seqlens_q[it.b + 1] - it.q_start;
   it.rows_total = it.q_len * p.group;
   request_kv(p, it.b, it.kv_len, it.k_start);
-  it.off = it.kv_len - it.q_len;
+  it.off = request_off(p, it.b, it.kv_len, it.q_len);
   const int qi_lo = it.row0 / p.group;
   const int qi_hi = min(it.q_len - 1, (it.row0 + kRowsPerItem - 1) / p.group);
   int kv_end = it.kv_len, kv_begin = 0;
-  if (p.window_right >= 0) kv_end = min(it.kv_len, qi_hi + it.off + p.window_right + 1);
+  if (p.window_right >= 0) kv_end = min(it.kv_len, right_bound(p, qi_hi + it.off));
   if (p.window_left >= 0) kv_begin = max(0, qi_lo + it.off - p.window_left);
   it.tile_lo = 0;
   it.n_tiles = 0;
@@ -467,12 +467,12 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       const int row = sub_row0 + r;
       const int qi = min(row / p.group, max(it.q_len - 1, 0));
       const int hd = it.kvh * p.group + row % p.group;
-      const int vis_hi = p.window_right >= 0 ? min(it.kv_len, qi + it.off + p.window_right + 1) : it.kv_len;
+      const int vis_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, qi + it.off)) : it.kv_len;
       const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
       const int sqi_lo = sub_row0 / p.group;
       const int sqi_hi = min(it.q_len - 1, (sub_row0 + kBM - 1) / p.group);
       const int full_lo = p.window_left >= 0 ? max(0, sqi_hi + it.off - p.window_left) : 0;
-      const int full_hi = p.window_right >= 0 ? min(it.kv_len, sqi_lo + it.off + p.window_right + 1) : it.kv_len;
+      const int full_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, sqi_lo + it.off)) : it.kv_len;
       float dq = 1.f, dk = 1.f, dv = 1.f;
       if (p.q_descale) dq = p.q_descale[it.b * p.q_descale_bs + it.kvh * p.q_descale_hs];
       if (p.k_descale) dk = p.k_descale[it.b * p.k_descale_bs + it.kvh * p.k_descale_hs];

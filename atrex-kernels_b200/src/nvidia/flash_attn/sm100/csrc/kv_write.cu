@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_write_kernel(con
     const int which = unit >= p.num_tokens;
     const long long tok = unit - (which ? p.num_tokens : 0);
     const long long slot = __ldg(p.slot_mapping + tok);
-    if (slot < 0) continue;                                // padding token (warp-uniform)
+    if (slot < 0 || slot >= p.slot_limit) continue;        // padding token, or a slot past the pools (warp-uniform)
     const long long page = slot / p.page_size, in_page = slot - page * p.page_size;
     const __nv_bfloat16* src = (which ? p.value : p.key) + tok * (which ? p.v_token_stride : p.k_token_stride);
     const long long src_head = which ? p.v_head_stride : p.k_head_stride;
@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(kWriteThreads) atrex_sm100_kv_amax_kernel(cons
     for (long long unit = (long long)blockIdx.x * (kWriteThreads / 32) + (threadIdx.x >> 5); unit < units; unit += warps) {
       const int which = unit >= p.num_tokens;
       const long long tok = unit - (which ? p.num_tokens : 0);
-      if (__ldg(p.slot_mapping + tok) < 0) continue;       // padding tokens are not stored, so they do not count
+      const long long slot = __ldg(p.slot_mapping + tok);
+      if (slot < 0 || slot >= p.slot_limit) continue;      // tokens that are not stored do not count
       const __nv_bfloat16* src = (which ? p.value : p.key) + tok * (which ? p.v_token_stride : p.k_token_stride);
       const long long src_head = which ? p.v_head_stride : p.k_head_stride;
       uint4 raw[kInFlight];

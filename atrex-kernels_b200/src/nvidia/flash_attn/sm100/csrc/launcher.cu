@@ -96,40 +96,52 @@ struct Resolved {
 };
 
 int check_params(const atrex_fa_sm100_params* p) {
-  if (p == nullptr) return ATREX_FA_INVALID_VALUE;
+  if (p == nullptr) return fail(ATREX_FA_INVALID_VALUE, "parameter block is NULL");
   if (p->struct_bytes != sizeof(atrex_fa_sm100_params) || p->abi_version != ATREX_FA_SM100_ABI_VERSION)
-    return ATREX_FA_ABI_MISMATCH;
+    return fail(ATREX_FA_ABI_MISMATCH, "struct_bytes / abi_version do not match this library");
   if (p->batch < 0 || p->total_q < 0 || p->total_k < 0 || p->num_pages < 0 || p->page_size < 0 ||
-      p->max_seqlen_q < 0 || p->max_seqlen_k < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 ||
-      p->num_q_heads % p->num_kv_heads != 0 || p->num_splits < 0)
-    return ATREX_FA_INVALID_VALUE;
-  if (p->cu_seqlens_q == nullptr || p->out == nullptr) return ATREX_FA_INVALID_VALUE;
-  if (p->total_q > 0 && p->q == nullptr) return ATREX_FA_INVALID_VALUE;
+      p->max_seqlen_q < 0 || p->max_seqlen_k < 0 || p->max_pages_per_seq < 0)
+    return fail(ATREX_FA_INVALID_VALUE, "negative size (batch, total_q, total_k, num_pages, page_size, max_seqlen_*, max_pages_per_seq)");
+  if (p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
+    return fail(ATREX_FA_INVALID_VALUE, "num_q_heads must be a positive multiple of num_kv_heads");
+  if (p->num_splits < 0) return fail(ATREX_FA_INVALID_VALUE, "num_splits is negative");
+  if (p->cu_seqlens_q == nullptr || p->out == nullptr) return fail(ATREX_FA_INVALID_VALUE, "cu_seqlens_q or out is NULL");
+  if (p->total_q > 0 && p->q == nullptr) return fail(ATREX_FA_INVALID_VALUE, "q is NULL");
   if (p->page_size > 0) {
-    if (p->block_table == nullptr || p->seqused_k == nullptr) return ATREX_FA_INVALID_VALUE;
+    if (p->block_table == nullptr || p->seqused_k == nullptr)
+      return fail(ATREX_FA_INVALID_VALUE, "paged K/V needs block_table and seqused_k");
   } else if (p->cu_seqlens_k == nullptr) {
-    return ATREX_FA_INVALID_VALUE;
+    return fail(ATREX_FA_INVALID_VALUE, "packed K/V needs cu_seqlens_k");
   }
-  if (p->return_lse && p->lse == nullptr) return ATREX_FA_INVALID_VALUE;
-  if (p->softcap < 0.f) return ATREX_FA_INVALID_VALUE;
-  if (p->head_dim != 128 && p->head_dim != 256) return ATREX_FA_UNSUPPORTED;
-  if (p->dtype != ATREX_FA_BF16 && p->dtype != ATREX_FA_E4M3) return ATREX_FA_UNSUPPORTED;
-  if (p->num_splits > kMaxSplits) return ATREX_FA_UNSUPPORTED;
+  if (p->return_lse && p->lse == nullptr) return fail(ATREX_FA_INVALID_VALUE, "return_lse without an lse buffer");
+  if (p->softcap < 0.f) return fail(ATREX_FA_INVALID_VALUE, "softcap is negative");
+  if (p->cp_world_size < 0 || (p->cp_world_size > 1 && (p->cp_rank < 0 || p->cp_rank >= p->cp_world_size)))
+    return fail(ATREX_FA_INVALID_VALUE, "cp_rank outside [0, cp_world_size)");
+  if (p->cp_world_size > 1) {
+    if (p->cp_tot_seqused_k == nullptr) return fail(ATREX_FA_INVALID_VALUE, "cp_world_size > 1 needs cp_tot_seqused_k");
+    if (!p->causal || p->window_left >= 0 || p->window_right > 0)
+      return fail(ATREX_FA_UNSUPPORTED, "context parallelism serves causal calls without a sliding window");
+  }
+  if (p->head_dim != 128 && p->head_dim != 256) return fail(ATREX_FA_UNSUPPORTED, "head_dim must be 128 or 256");
+  if (p->dtype != ATREX_FA_BF16 && p->dtype != ATREX_FA_E4M3) return fail(ATREX_FA_UNSUPPORTED, "dtype must be BF16 or E4M3");
+  if (p->num_splits > kMaxSplits) return fail(ATREX_FA_UNSUPPORTED, "num_splits above 256");
   if (p->page_size > 0 && p->page_size % 64 != 0 && p->page_size != 16 && p->page_size != 32)
-    return ATREX_FA_UNSUPPORTED;
+    return fail(ATREX_FA_UNSUPPORTED, "page_size must be 16, 32 or a multiple of 64");
   if (p->route != ATREX_FA_ROUTE_AUTO && p->route != ATREX_FA_ROUTE_MMA && p->route != ATREX_FA_ROUTE_UMMA)
-    return ATREX_FA_INVALID_VALUE;
+    return fail(ATREX_FA_INVALID_VALUE, "unknown route");
   // 16-byte alignment of everything the kernels touch with vectors or TMA
   const uint64_t es = p->dtype == ATREX_FA_E4M3 ? 1 : 2;
   auto misaligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0; };
-  if (misaligned(p->q) || misaligned(p->k) || misaligned(p->v) || misaligned(p->out)) return ATREX_FA_UNSUPPORTED;
+  if (misaligned(p->q) || misaligned(p->k) || misaligned(p->v) || misaligned(p->out))
+    return fail(ATREX_FA_UNSUPPORTED, "q, k, v and out must be 16-byte aligned");
   const int64_t strides[] = {p->q_row_stride, p->q_head_stride, p->k_row_stride, p->k_head_stride,
                              p->v_row_stride, p->v_head_stride, p->out_row_stride, p->out_head_stride,
                              p->page_size ? p->k_page_stride : 0, p->page_size ? p->v_page_stride : 0};
   for (int64_t s : strides)
-    if (s < 0 || (static_cast<uint64_t>(s) * es) % 16 != 0) return ATREX_FA_UNSUPPORTED;
+    if (s < 0 || (static_cast<uint64_t>(s) * es) % 16 != 0)
+      return fail(ATREX_FA_UNSUPPORTED, "a q / k / v / out stride is negative or not a multiple of 16 bytes");
   if ((static_cast<uint64_t>(p->out_row_stride) * 2) % 16 != 0 || (static_cast<uint64_t>(p->out_head_stride) * 2) % 16 != 0)
-    return ATREX_FA_UNSUPPORTED;
+    return fail(ATREX_FA_UNSUPPORTED, "an out stride is not a multiple of 16 bytes");
   return ATREX_FA_OK;
 }
 
@@ -147,8 +159,11 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   const bool fp8 = p->dtype == ATREX_FA_E4M3;
   const bool tensor_ok = p->softcap == 0.f && p->softmax_scale > 0.f && umma1_supports(p->head_dim);
   const bool umma2_ok = tensor_ok && umma_supports(p->head_dim, group, !fp8) && p->q_head_stride <= p->q_row_stride;
-  if ((p->route == ATREX_FA_ROUTE_UMMA || fp8) && !tensor_ok) return ATREX_FA_UNSUPPORTED;
-  if (fp8 && p->route == ATREX_FA_ROUTE_MMA) return ATREX_FA_UNSUPPORTED;   // the mma.sync kernel is BF16 only
+  if ((p->route == ATREX_FA_ROUTE_UMMA || fp8) && !tensor_ok)
+    return fail(ATREX_FA_UNSUPPORTED, fp8 ? "E4M3 calls run on the tcgen05 kernels only: no softcap, softmax_scale > 0"
+                                          : "the tcgen05 route takes no softcap and needs softmax_scale > 0");
+  if (fp8 && p->route == ATREX_FA_ROUTE_MMA)   // the mma.sync kernel is BF16 only
+    return fail(ATREX_FA_UNSUPPORTED, "E4M3 calls cannot take the mma.sync route");
   int kernel;
   if (p->route == ATREX_FA_ROUTE_MMA) kernel = kKernelMma;
   else if (fp8) kernel = kKernelUmma1;
@@ -173,7 +188,8 @@ int resolve(const atrex_fa_sm100_params* p, int sm_count, Resolved* r) {
   r->tiled = kernel == kKernelUmma2 || packed_max > r->m_rows;
   const int64_t tiles_bound =
       r->tiled ? ((int64_t)p->total_q * group) / r->m_rows + p->batch : (int64_t)p->batch;
-  if (tiles_bound * p->num_kv_heads * kMaxSplits > 0x7FFFFFFFll) return ATREX_FA_UNSUPPORTED;
+  if (tiles_bound * p->num_kv_heads * kMaxSplits > 0x7FFFFFFFll)
+    return fail(ATREX_FA_UNSUPPORTED, "row tiles x KV heads x splits exceeds the 32-bit work-item range");
   r->num_row_tiles = (int)tiles_bound;
 
   // keys one row tile can see, at the upper bound (a two-sided window limits it)
@@ -298,8 +314,9 @@ const char* atrex_fa_sm100_status_string(int status) {
 
 int atrex_fa_sm100_plan(const atrex_fa_sm100_params* p, atrex_fa_sm100_plan_info* plan) {
   if (plan == nullptr) return fail(ATREX_FA_INVALID_VALUE, "plan is NULL");
+  g_last_error[0] = 0;
   int st = check_params(p);
-  if (st != ATREX_FA_OK) return fail(st, "parameter check failed");
+  if (st != ATREX_FA_OK) return st;
   int sm_count = p->sm_count;
   if (sm_count <= 0) {
     DeviceInfo* info = nullptr;
@@ -319,16 +336,120 @@ int atrex_fa_sm100_plan(const atrex_fa_sm100_params* p, atrex_fa_sm100_plan_info
 }
 
 int atrex_fa_sm100_prewarm(void) {
+  g_last_error[0] = 0;
   DeviceInfo* info = nullptr;
   const int st = current_device(&info);
   if (st != ATREX_FA_OK) return st;
   return prepare_device(*info);
 }
 
+// The TMA descriptors of a call and what was decided with them.
+struct EncodedMaps {
+  CUtensorMap k_map, v_map, q_map;
+  int8_t k_perm[3], v_perm[3];
+  int32_t box_rows, q_via_tma, num_pages;
+};
+
+static int encode_maps(const atrex_fa_sm100_params* p, const Resolved& r, EncodedMaps& m) {
+  int st = ATREX_FA_OK;
+  const bool paged = p->page_size > 0;
+  const int64_t rows = paged ? p->page_size : p->total_k;
+  const int64_t pages = paged ? p->num_pages : 1;
+  const int es = p->dtype == ATREX_FA_E4M3 ? 1 : 2;
+  // Rows one TMA box covers: a whole KV tile of the chosen kernel, or less where pages are smaller.  A box never
+  // crosses a page: with pages of 192, 320, ... rows a 128-key tile straddles pages at 64-row granularity, so
+  // the box is the largest power of two dividing both (page sizes are 16, 32 or multiples of 64).
+  int box_rows = r.tile_n;
+  if (paged) while (p->page_size % box_rows != 0) box_rows >>= 1;
+  const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
+  int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
+  if (empty_kv) {
+    // No key exists: the kernels will not issue a copy, but the descriptors must still be valid.
+    st = encode_kv_map(&m.k_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, kperm, es);
+    if (st == ATREX_FA_OK)
+      st = encode_kv_map(&m.v_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, vperm, es);
+  } else {
+    st = encode_kv_map(&m.k_map, p->k, p->k_head_stride, p->k_row_stride,
+                       paged ? p->k_page_stride : p->k_row_stride * rows, p->num_kv_heads, rows, pages,
+                       p->head_dim, box_rows, kperm, es);
+    if (st == ATREX_FA_OK)
+      st = encode_kv_map(&m.v_map, p->v, p->v_head_stride, p->v_row_stride,
+                         paged ? p->v_page_stride : p->v_row_stride * rows, p->num_kv_heads, rows, pages,
+                         p->head_dim, box_rows, vperm, es);
+  }
+  if (st != ATREX_FA_OK) return st;
+  for (int i = 0; i < 3; ++i) { m.k_perm[i] = kperm[i]; m.v_perm[i] = vperm[i]; }
+  m.q_via_tma = r.kernel == kKernelUmma2 || (r.kernel == kKernelUmma1 && umma1_q_via_tma(p->num_q_heads / p->num_kv_heads) &&
+                                             p->q_head_stride <= p->q_row_stride);
+  if (m.q_via_tma) {
+    st = encode_q_map(&m.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
+                      p->num_q_heads / p->num_kv_heads, es);
+    if (st != ATREX_FA_OK) return st;
+  }
+  m.box_rows = box_rows;
+  m.num_pages = empty_kv ? 0 : (int)pages;
+  return ATREX_FA_OK;
+}
+
+// A serving loop repeats the same call shape over the same Q buffer and KV pools step after step, and
+// encoding two or three TMA descriptors through the driver is the largest single cost on the host side
+// of a launch.  Each host thread keeps the descriptors of its last few distinct (Q, K, V layout, kernel)
+// combinations.  The key holds every input of the encoding, so a hit returns descriptors that are
+// bit-identical to a fresh encoding; nothing that lives in device memory (lengths, page tables,
+// descales) is cached, and every other kernel argument is rebuilt from the caller's block on each call.
+namespace {
+struct MapKey {
+  const void *q, *k, *v;
+  int64_t q_row_stride, q_head_stride, k_page_stride, k_row_stride, k_head_stride, v_page_stride, v_row_stride,
+      v_head_stride;
+  int32_t total_q, total_k, num_pages, page_size, num_q_heads, num_kv_heads, head_dim, dtype, kernel, tile_n, device,
+      pad;
+};
+constexpr int kMapCacheSlots = 16;
+struct CachedMaps {
+  bool valid = false;
+  uint64_t stamp = 0;
+  MapKey key;
+  EncodedMaps maps;
+};
+thread_local CachedMaps g_maps[kMapCacheSlots];
+thread_local uint64_t g_map_stamp = 0;
+}  // namespace
+
+static int maps_for(const atrex_fa_sm100_params* p, const Resolved& r, int device, const EncodedMaps** out) {
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.q = p->q; key.k = p->k; key.v = p->v;
+  key.q_row_stride = p->q_row_stride; key.q_head_stride = p->q_head_stride;
+  key.k_page_stride = p->k_page_stride; key.k_row_stride = p->k_row_stride; key.k_head_stride = p->k_head_stride;
+  key.v_page_stride = p->v_page_stride; key.v_row_stride = p->v_row_stride; key.v_head_stride = p->v_head_stride;
+  key.total_q = p->total_q; key.total_k = p->total_k; key.num_pages = p->num_pages; key.page_size = p->page_size;
+  key.num_q_heads = p->num_q_heads; key.num_kv_heads = p->num_kv_heads; key.head_dim = p->head_dim;
+  key.dtype = p->dtype; key.kernel = r.kernel; key.tile_n = r.tile_n; key.device = device;
+  CachedMaps* victim = &g_maps[0];
+  for (CachedMaps& c : g_maps) {
+    if (c.valid && std::memcmp(&c.key, &key, sizeof(key)) == 0) {
+      c.stamp = ++g_map_stamp;
+      *out = &c.maps;
+      return ATREX_FA_OK;
+    }
+    if (victim->valid && (!c.valid || c.stamp < victim->stamp)) victim = &c;
+  }
+  victim->valid = false;
+  const int st = encode_maps(p, r, victim->maps);
+  if (st != ATREX_FA_OK) return st;
+  victim->key = key;
+  victim->stamp = ++g_map_stamp;
+  victim->valid = true;
+  *out = &victim->maps;
+  return ATREX_FA_OK;
+}
+
 int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint64_t workspace_bytes,
                            void* stream_ptr) {
+  g_last_error[0] = 0;
   int st = check_params(p);
-  if (st != ATREX_FA_OK) return fail(st, "parameter check failed");
+  if (st != ATREX_FA_OK) return st;
   DeviceInfo* info = nullptr;
   st = current_device(&info);
   if (st != ATREX_FA_OK) return st;
@@ -341,51 +462,26 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   if (p->batch == 0 || p->total_q == 0) return ATREX_FA_OK;
   st = prepare_device(*info);
   if (st != ATREX_FA_OK) return st;
+  const EncodedMaps* maps = nullptr;
+  st = maps_for(p, r, (int)(info - g_devices), &maps);
+  if (st != ATREX_FA_OK) return st;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const bool paged = p->page_size > 0;
+  const bool fp8 = p->dtype == ATREX_FA_E4M3;
   FwdParams f;
   std::memset(&f, 0, sizeof(f));
-  const bool paged = p->page_size > 0;
-  const int64_t rows = paged ? p->page_size : p->total_k;
-  const int64_t pages = paged ? p->num_pages : 1;
-  // rows one TMA box covers: a whole KV tile of the chosen kernel, or a page if pages are smaller
-  const bool fp8 = p->dtype == ATREX_FA_E4M3;
-  const int es = fp8 ? 1 : 2;
-  const int kTileN = r.tile_n;
-  const int box_rows = paged ? (p->page_size >= kTileN ? kTileN : p->page_size) : kTileN;
-  const bool empty_kv = rows == 0 || pages == 0 || p->k == nullptr || p->v == nullptr;
-  int8_t kperm[3] = {0, 1, 2}, vperm[3] = {0, 1, 2};
-  if (empty_kv) {
-    // No key exists: the kernels will not issue a copy, but the descriptors must still be valid.
-    st = encode_kv_map(&f.k_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, kperm, es);
-    if (st == ATREX_FA_OK)
-      st = encode_kv_map(&f.v_map, p->q, p->head_dim, p->head_dim, p->head_dim, 1, 1, 1, p->head_dim, box_rows, vperm, es);
-  } else {
-    st = encode_kv_map(&f.k_map, p->k, p->k_head_stride, p->k_row_stride,
-                       paged ? p->k_page_stride : p->k_row_stride * rows, p->num_kv_heads, rows, pages,
-                       p->head_dim, box_rows, kperm, es);
-    if (st == ATREX_FA_OK)
-      st = encode_kv_map(&f.v_map, p->v, p->v_head_stride, p->v_row_stride,
-                         paged ? p->v_page_stride : p->v_row_stride * rows, p->num_kv_heads, rows, pages,
-                         p->head_dim, box_rows, vperm, es);
-  }
-  if (st != ATREX_FA_OK) return st;
-  for (int i = 0; i < 3; ++i) { f.k_perm[i] = kperm[i]; f.v_perm[i] = vperm[i]; }
-  f.q_via_tma = r.kernel == kKernelUmma2 || (r.kernel == kKernelUmma1 && umma1_q_via_tma(p->num_q_heads / p->num_kv_heads) &&
-                                             p->q_head_stride <= p->q_row_stride);
-  if (f.q_via_tma) {
-    st = encode_q_map(&f.q_map, p->q, p->q_head_stride, p->q_row_stride, p->num_q_heads, p->total_q, p->head_dim,
-                      p->num_q_heads / p->num_kv_heads, es);
-    if (st != ATREX_FA_OK) return st;
-  }
-
+  f.k_map = maps->k_map; f.v_map = maps->v_map; f.q_map = maps->q_map;
+  for (int i = 0; i < 3; ++i) { f.k_perm[i] = maps->k_perm[i]; f.v_perm[i] = maps->v_perm[i]; }
+  f.q_via_tma = maps->q_via_tma;
   f.q = p->q; f.out = p->out; f.lse = p->return_lse ? p->lse : nullptr;
   f.cu_seqlens_q = p->cu_seqlens_q;
   f.cu_seqlens_k = paged ? nullptr : p->cu_seqlens_k;
   f.seqused_k = p->seqused_k;
   f.block_table = p->block_table;
   f.q_descale = p->q_descale; f.k_descale = p->k_descale; f.v_descale = p->v_descale;
-  f.sink = static_cast<const __nv_bfloat16*>(p->sink);
+  // with context parallelism the sink logit joins the softmax once, on rank 0; the merge across ranks carries it
+  f.sink = (p->cp_world_size > 1 && p->cp_rank != 0) ? nullptr : static_cast<const __nv_bfloat16*>(p->sink);
   f.status = p->device_status;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   if (r.tiled) {
@@ -403,8 +499,8 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   f.k_descale_bs = p->k_descale_batch_stride; f.k_descale_hs = p->k_descale_head_stride;
   f.v_descale_bs = p->v_descale_batch_stride; f.v_descale_hs = p->v_descale_head_stride;
   f.batch = p->batch; f.total_q = p->total_q; f.total_k = p->total_k;
-  f.num_pages = empty_kv ? 0 : (int)pages;
-  f.page_size = p->page_size; f.box_rows = box_rows;
+  f.num_pages = maps->num_pages;
+  f.page_size = p->page_size; f.box_rows = maps->box_rows;
   f.num_q_heads = p->num_q_heads; f.num_kv_heads = p->num_kv_heads;
   f.group = p->num_q_heads / p->num_kv_heads;
   f.causal = p->causal ? 1 : 0;
@@ -412,6 +508,13 @@ int atrex_fa_sm100_forward(const atrex_fa_sm100_params* p, void* workspace, uint
   f.window_right = p->causal ? 0 : (p->window_right < 0 ? -1 : p->window_right);
   f.num_splits = r.splits;
   f.num_row_tiles = r.num_row_tiles;
+  {
+    const int64_t cap = paged ? (int64_t)p->max_pages_per_seq * p->page_size : 0;
+    f.kv_cap = (int32_t)(cap > 0x7FFFFFFFll ? 0x7FFFFFFFll : cap);
+  }
+  f.cp_world_size = p->cp_world_size > 1 ? p->cp_world_size : 1;
+  f.cp_rank = p->cp_world_size > 1 ? p->cp_rank : 0;
+  f.cp_tot_seqused_k = p->cp_world_size > 1 ? p->cp_tot_seqused_k : nullptr;
   f.softmax_scale = p->softmax_scale;
   f.softcap = p->softcap;
 
@@ -510,10 +613,11 @@ size_t atrex_fa_sm100_kv_write_params_bytes(void) { return sizeof(atrex_fa_sm100
 static int kv_fill(const atrex_fa_sm100_kv_write_params* p, bool need_cache, atrex_sm100::KvWriteParams* k, bool* fp8_out,
                    int* sm_count) {
   using namespace atrex_sm100;
+  g_last_error[0] = 0;
   if (p == nullptr) return fail(ATREX_FA_INVALID_VALUE, "null parameter block");
   if (p->struct_bytes != sizeof(atrex_fa_sm100_kv_write_params) || p->abi_version != ATREX_FA_SM100_ABI_VERSION)
     return fail(ATREX_FA_ABI_MISMATCH, "kv-write parameter block does not match this library");
-  if (p->num_tokens < 0 || p->num_kv_heads <= 0 || p->head_dim <= 0 || p->page_size <= 0)
+  if (p->num_tokens < 0 || p->num_kv_heads <= 0 || p->head_dim <= 0 || p->page_size <= 0 || p->num_pages < 0)
     return fail(ATREX_FA_INVALID_VALUE, "negative or zero size");
   if (p->num_kv_heads > 1024) return fail(ATREX_FA_UNSUPPORTED, "more than 1024 KV heads");   // per-head shared-memory tables
   bool fp8 = false;
@@ -561,6 +665,7 @@ static int kv_fill(const atrex_fa_sm100_kv_write_params* p, bool need_cache, atr
   k->vc_head_stride = p->value_cache_head_stride;
   k->k_scale_head_stride = p->k_scale_head_stride, k->v_scale_head_stride = p->v_scale_head_stride;
   k->num_tokens = p->num_tokens, k->num_kv_heads = p->num_kv_heads, k->head_dim = p->head_dim, k->page_size = p->page_size;
+  k->slot_limit = p->num_pages > 0 ? (long long)p->num_pages * p->page_size : 0x7FFFFFFFFFFFFFFFll;
   return ATREX_FA_OK;
 }
 
@@ -596,6 +701,7 @@ int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* p, float* k_s
 int atrex_fa_sm100_merge_parts(const void* parts, const float* part_lse, void* out, float* lse, int32_t world,
                                int64_t total_q, int32_t num_q_heads, int32_t head_dim, void* stream) {
   using namespace atrex_sm100;
+  g_last_error[0] = 0;
   if (world <= 0 || total_q < 0 || num_q_heads <= 0) return fail(ATREX_FA_INVALID_VALUE, "negative or zero size");
   if (head_dim <= 0 || head_dim % 32 || head_dim > 256) return fail(ATREX_FA_UNSUPPORTED, "head_dim must be a multiple of 32 up to 256");
   if (total_q == 0) return ATREX_FA_OK;

@@ -60,19 +60,20 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 // The spinning part is kept out of line and rolled: a wait has a dozen call sites per kernel, and an
 // inlined, unrolled spin loop at each of them pushes the hot loops of the MMA-issuing and TMA-issuing
 // warps out of the instruction cache.
-#ifdef ATREX_MBAR_SPIN_INLINE   // for kernels that use setmaxnreg: no calls with their own register ABI
-__device__ __forceinline__
-#else
-static __device__ __noinline__   // one copy per translation unit
-#endif
-bool mbar_wait_slow(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, uint32_t limit) {
 #pragma unroll 1
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 4096) __nanosleep(64);
   }
   return false;
 }
+#ifdef ATREX_MBAR_SPIN_INLINE   // for kernels that use setmaxnreg: no calls with their own register ABI
+__device__ __forceinline__
+#else
+static __device__ __noinline__   // one copy per translation unit
+#endif
+bool mbar_wait_slow(uint64_t* bar, uint32_t parity) { return mbar_spin(bar, parity, kSpinLimit); }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity);

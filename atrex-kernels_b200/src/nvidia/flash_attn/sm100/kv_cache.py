@@ -36,7 +36,7 @@ class KvWriteParams(ctypes.Structure):
         ("k_scale_head_stride", ctypes.c_int64), ("v_scale_head_stride", ctypes.c_int64),
         ("num_tokens", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32),
         ("head_dim", ctypes.c_int32), ("page_size", ctypes.c_int32),
-        ("cache_dtype", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("cache_dtype", ctypes.c_int32), ("num_pages", ctypes.c_int32),
     ]
 
 
@@ -113,6 +113,7 @@ def write_kv_cache(key, value, key_cache, value_cache, slot_mapping, k_scale=Non
     p.value_cache_page_stride, p.value_cache_row_stride, p.value_cache_head_stride = value_cache.stride()[:3]
     p.num_tokens, p.num_kv_heads, p.head_dim, p.page_size = tokens, heads, dim, key_cache.shape[1]
     p.cache_dtype = 1 if key_cache.dtype == torch.float8_e4m3fn else 0
+    p.num_pages = key_cache.shape[0]     # slots past the pools are skipped like padding, never written
     with torch.cuda.device(key.device):
         stream = torch.cuda.current_stream(key.device).cuda_stream
         runtime.raise_for_status(lib.atrex_fa_sm100_kv_cache_write(ctypes.byref(p), stream))

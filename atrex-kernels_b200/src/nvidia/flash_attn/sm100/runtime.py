@@ -20,7 +20,7 @@ from pathlib import Path
 
 import torch
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 ROUTE_AUTO, ROUTE_MMA, ROUTE_UMMA = 0, 1, 2
 _STATUS_EXCEPTIONS = {1: ValueError, 2: NotImplementedError}
 
@@ -34,7 +34,7 @@ class Params(ctypes.Structure):
         [("struct_bytes", _u32), ("abi_version", _u32)]
         + [(n, _ptr) for n in ("q", "k", "v", "out", "lse", "cu_seqlens_q", "cu_seqlens_k", "seqused_k",
                                "block_table", "q_descale", "k_descale", "v_descale", "sink", "device_status",
-                               "profile_event_begin", "profile_event_end")]
+                               "profile_event_begin", "profile_event_end", "cp_tot_seqused_k")]
         + [(n, _i64) for n in ("q_row_stride", "q_head_stride",
                                "k_page_stride", "k_row_stride", "k_head_stride",
                                "v_page_stride", "v_row_stride", "v_head_stride",
@@ -45,7 +45,7 @@ class Params(ctypes.Structure):
         + [(n, _i32) for n in ("batch", "total_q", "total_k", "num_pages", "page_size", "max_pages_per_seq",
                                "max_seqlen_q", "max_seqlen_k", "num_q_heads", "num_kv_heads", "head_dim",
                                "dtype", "causal", "window_left", "window_right", "return_lse", "num_splits",
-                               "route", "sm_count")]
+                               "route", "sm_count", "cp_world_size", "cp_rank")]
         + [("softmax_scale", _f32), ("softcap", _f32)]
     )
 
@@ -128,9 +128,35 @@ def check_device_status(device) -> int:
     return value
 
 
+def set_pointers(p: Params, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, q_descale,
+                 k_descale, v_descale, sink, status, cp_tot_seqused_k=None) -> None:
+    """The part of a parameter block that changes from call to call for one layout: the addresses."""
+    p.q, p.k, p.v, p.out, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _ptr_of(lse)
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_seqlens_q.data_ptr(), _ptr_of(cu_seqlens_k)
+    p.seqused_k, p.block_table = _ptr_of(seqused_k), _ptr_of(block_table)
+    p.q_descale, p.k_descale, p.v_descale = _ptr_of(q_descale), _ptr_of(k_descale), _ptr_of(v_descale)
+    p.sink, p.device_status = _ptr_of(sink), _ptr_of(status)
+    p.cp_tot_seqused_k = _ptr_of(cp_tot_seqused_k)
+
+
+def layout_key(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, q_descale, k_descale,
+               v_descale, sink, status, max_seqlen_q, max_seqlen_k, softmax_scale, softcap, causal,
+               window_left, window_right, num_splits, route, cp_world_size=1, cp_rank=0, cp_tot_seqused_k=None):
+    """Everything ``build_params`` reads except the addresses: two calls with equal keys differ only in pointers.
+    No tensor contents, identities or version counters enter it."""
+    return (q.shape, q.stride(), q.dtype, k.shape, k.stride(), v.stride(), out.stride(), lse is not None,
+            cu_seqlens_q.shape[0], cu_seqlens_k is None, seqused_k is None,
+            None if block_table is None else (block_table.shape[1], block_table.stride(0)),
+            None if q_descale is None else q_descale.stride(), None if k_descale is None else k_descale.stride(),
+            None if v_descale is None else v_descale.stride(), sink is None, status is None,
+            max_seqlen_q, max_seqlen_k, softmax_scale, softcap, causal, window_left, window_right, num_splits, route,
+            cp_world_size, cp_rank)
+
+
 def build_params(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, q_descale, k_descale,
                  v_descale, sink, status, max_seqlen_q, max_seqlen_k, softmax_scale, softcap, causal,
-                 window_left, window_right, num_splits, route) -> Params:
+                 window_left, window_right, num_splits, route, cp_world_size=1, cp_rank=0,
+                 cp_tot_seqused_k=None) -> Params:
     p = Params()
     p.struct_bytes, p.abi_version = ctypes.sizeof(Params), ABI_VERSION
     p.q, p.k, p.v, p.out, p.lse = _ptr_of(q), _ptr_of(k), _ptr_of(v), _ptr_of(out), _ptr_of(lse)
@@ -138,6 +164,8 @@ def build_params(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, block
     p.seqused_k, p.block_table = _ptr_of(seqused_k), _ptr_of(block_table)
     p.q_descale, p.k_descale, p.v_descale = _ptr_of(q_descale), _ptr_of(k_descale), _ptr_of(v_descale)
     p.sink, p.device_status = _ptr_of(sink), _ptr_of(status)
+    p.cp_tot_seqused_k = _ptr_of(cp_tot_seqused_k)
+    p.cp_world_size, p.cp_rank = cp_world_size, cp_rank
     p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
     paged = block_table is not None
     if paged:
@@ -184,7 +212,8 @@ _SCHEMA = (
     "Tensor cu_seqlens_q, Tensor? cu_seqlens_k, Tensor? seqused_k, Tensor? block_table, "
     "Tensor? q_descale, Tensor? k_descale, Tensor? v_descale, Tensor? sink, Tensor(d!)? status, "
     "int max_seqlen_q, int max_seqlen_k, float softmax_scale, float softcap, bool causal, "
-    "int window_left, int window_right, int num_splits, int route) -> ()"
+    "int window_left, int window_right, int num_splits, int route, int cp_world_size=1, int cp_rank=0, "
+    "Tensor? cp_tot_seqused_k=None) -> ()"
 )
 _op_library = torch.library.Library("atrex_sm100", "DEF")
 _op_library.define(_SCHEMA)
@@ -192,10 +221,11 @@ _op_library.define(_SCHEMA)
 
 def _fa_fwd_cuda(q, k, v, out, lse, workspace, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, q_descale,
                  k_descale, v_descale, sink, status, max_seqlen_q, max_seqlen_k, softmax_scale, softcap, causal,
-                 window_left, window_right, num_splits, route):
+                 window_left, window_right, num_splits, route, cp_world_size=1, cp_rank=0, cp_tot_seqused_k=None):
     params = build_params(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, q_descale,
                           k_descale, v_descale, sink, status, max_seqlen_q, max_seqlen_k, softmax_scale, softcap,
-                          causal, window_left, window_right, num_splits, route)
+                          causal, window_left, window_right, num_splits, route, cp_world_size, cp_rank,
+                          cp_tot_seqused_k)
     ws_ptr = None if workspace is None else workspace.data_ptr()
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     stream = torch.cuda.current_stream(q.device).cuda_stream
@@ -208,10 +238,12 @@ def launch_params(params: Params, workspace, device) -> None:
     ws_ptr = None if workspace is None else workspace.data_ptr()
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     stream = torch.cuda.current_stream(device).cuda_stream
-    raise_for_status(load_library().atrex_fa_sm100_forward(ctypes.byref(params), ws_ptr, ws_bytes, stream))
+    status = (_lib or load_library()).atrex_fa_sm100_forward(ctypes.byref(params), ws_ptr, ws_bytes, stream)
+    if status:
+        raise_for_status(status)
 
 
-def _fa_fwd_meta(*args):
+def _fa_fwd_meta(*args, **kwargs):
     return None
 
 

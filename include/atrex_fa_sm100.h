@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define ATREX_FA_SM100_ABI_VERSION 4
+#define ATREX_FA_SM100_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define ATREX_FA_API __attribute__((visibility("default")))
@@ -75,15 +75,19 @@ typedef struct atrex_fa_sm100_params {
   float* lse;              /* [Hq, total_q] natural log, or NULL                             */
   const int32_t* cu_seqlens_q;  /* [batch+1]                                                 */
   const int32_t* cu_seqlens_k;  /* [batch+1] packed K/V only, else NULL                      */
-  const int32_t* seqused_k;     /* [batch] or NULL (packed K/V may give either)              */
+  const int32_t* seqused_k;     /* [batch]; required when paged.  Packed K/V: optional, and when  */
+                                /* given the used length is min(cu_seqlens_k[b+1]-cu_seqlens_k[b], seqused_k[b]) */
   const int32_t* block_table;   /* [batch, max_pages_per_seq] or NULL for packed K/V         */
   const float* q_descale;       /* [batch, Hkv] FP8 only, or NULL                            */
   const float* k_descale;
   const float* v_descale;
   const void* sink;             /* BF16 [Hq] sink logits (s_aux) or NULL                     */
   int32_t* device_status;       /* optional: kernels store a nonzero code here if a bounded wait expires */
-  void* profile_event_begin;    /* optional cudaEvent_t pair recorded on the stream right before and right   */
-  void* profile_event_end;      /* after the dominant kernel of the call (not the plan or combine kernels)   */
+  void* profile_event_begin;    /* benchmark hook: optional cudaEvent_t pair recorded on the stream right    */
+  void* profile_event_end;      /* before and after the dominant kernel of the call (not the plan or combine */
+                                /* kernels).  Production callers pass NULL for both.                         */
+  const int32_t* cp_tot_seqused_k;  /* [batch] total keys of each request over all context-parallel ranks;   */
+                                    /* read only when cp_world_size > 1, else NULL                            */
 
   int64_t q_row_stride, q_head_stride;
   int64_t k_page_stride, k_row_stride, k_head_stride;   /* page stride ignored for packed K/V */
@@ -99,7 +103,7 @@ typedef struct atrex_fa_sm100_params {
   int32_t total_k;             /* rows of packed K/V; 0 when paged */
   int32_t num_pages;           /* pool size when paged             */
   int32_t page_size;           /* 0 = packed K/V                   */
-  int32_t max_pages_per_seq;   /* block_table width                */
+  int32_t max_pages_per_seq;   /* block_table width; a seqused_k above max_pages_per_seq * page_size is clamped to it */
   int32_t max_seqlen_q;        /* upper bounds only: real lengths are read on the device */
   int32_t max_seqlen_k;
   int32_t num_q_heads, num_kv_heads, head_dim;
@@ -110,6 +114,13 @@ typedef struct atrex_fa_sm100_params {
   int32_t num_splits;          /* 0 = launcher chooses, else 1..256 */
   int32_t route;               /* enum atrex_fa_route               */
   int32_t sm_count;            /* 0 = query the current device      */
+  /* Context parallelism over the keys (no counterpart in the reference, which rejects these arguments:
+   * python/atrex/api/flash_attn.py:128-135).  Rank r of W holds every W-th key of each request: its local key j
+   * is the request's key j * W + r, seqused_k holds the LOCAL lengths and cp_tot_seqused_k the totals.  A query
+   * row i of a request of q_len rows sits at position tot - q_len + i and sees local key j iff
+   * j * W + r <= tot - q_len + i.  The caller merges the ranks' (out, lse) with atrex_fa_sm100_merge_parts.
+   * cp_world_size 0 or 1 = off.  Causal calls without a sliding window only. */
+  int32_t cp_world_size, cp_rank;
   float softmax_scale;
   float softcap;               /* 0 = off                           */
 } atrex_fa_sm100_params;
@@ -182,7 +193,9 @@ ATREX_FA_API int atrex_fa_sm100_prewarm(void);
  *
  * The first call on a device looks up the array's device address; make that first
  * call (or any call of this function on that device) before starting a stream
- * capture.  All calls on one device share the one array and it keeps the previous
+ * capture.  The address is remembered per device for the life of the process: after
+ * a cudaDeviceReset the remembered address is stale, so a process that resets a
+ * device must not call this entry point on it again.  All calls on one device share the one array and it keeps the previous
  * call's contents: nothing in it needs clearing between calls, but two calls whose
  * kernels can overlap on the GPU (different streams without an ordering between
  * them) race on it and must be serialised by the caller.
@@ -226,7 +239,7 @@ typedef struct atrex_fa_sm100_kv_write_params {
   int64_t k_scale_head_stride, v_scale_head_stride;
   int32_t num_tokens, num_kv_heads, head_dim, page_size;
   int32_t cache_dtype; /* ATREX_FA_BF16 or ATREX_FA_E4M3 */
-  int32_t reserved;
+  int32_t num_pages;   /* pages in the pools: a slot >= num_pages * page_size is skipped like a negative one; 0 = unchecked */
 } atrex_fa_sm100_kv_write_params;
 
 ATREX_FA_API size_t atrex_fa_sm100_kv_write_params_bytes(void);
@@ -257,6 +270,18 @@ ATREX_FA_API int atrex_fa_sm100_kv_scales(const atrex_fa_sm100_kv_write_params* 
 ATREX_FA_API int atrex_fa_sm100_merge_parts(const void* parts, const float* part_lse, void* out, float* lse,
                                             int32_t world, int64_t total_q, int32_t num_q_heads, int32_t head_dim,
                                             void* stream);
+
+/*
+ * Self-test of the bounded device-side wait (no counterpart in the reference; its precedent for a wait
+ * with a limit is _tma_mbarrier_try_wait_parity(..., time_limit), src/nvidia/flash_attn/sm120/attention_cutedsl.py:2434).
+ * Every wait inside the kernels gives up after an iteration limit, stores a code in
+ * atrex_fa_sm100_params.device_status and lets its kernel return.  This entry point exercises exactly that
+ * path: one thread waits at most `spin_limit` (1..65536) polls on a barrier that nobody arrives at, then
+ * stores 104 (wait expired) in *device_status (may be NULL) and 0 in *result (1 would mean the barrier
+ * completed), and the kernel returns normally.  One tiny kernel on `stream`; allocates nothing.
+ */
+ATREX_FA_API int atrex_fa_sm100_selftest_bounded_wait(int32_t* device_status, int32_t* result, uint32_t spin_limit,
+                                                      void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,13 +28,18 @@ What it follows (paths are relative to the alibaba/atrex-kernels tree):
   (``src/nvidia/flash_attn/sm120/runtime.py:575-577`` delegates this to
   flash-attn-4's ``create_softcap_scoremod``, which is not vendored).
 
+* context parallelism over the keys (``cp_world_size``, ``cp_rank``, ``cp_tot_seqused_k``): the reference
+  rejects these arguments (``python/atrex/api/flash_attn.py:128-135``), so the definition is this file's: rank
+  ``r`` of ``W`` holds the keys ``r, r + W, r + 2W, ...`` of each request, a query row ``i`` of ``q_len`` rows sits
+  at position ``tot - q_len + i`` and sees local key ``j`` iff ``j * W + r <= tot - q_len + i`` (causal only).
+
 Parity status.  Causal / non-causal, paged / contiguous, varlen, GQA, descales
 and LSE are PINNED: ``tests/golden`` holds outputs of the reference's own
 ``reference()`` and ``_fp32_prefill_ref`` run on CPU, and ``tests/test_oracle.py``
 checks this module against them.  Sliding window, sinks and softcap are
 PARITY UNPINNED: no reference test exercises their numerics (the reference
 rejects windows on NVIDIA and never runs a sink or softcap case), so for those
-three this file is the definition.
+three this file is the definition; context parallelism likewise.
 """
 
 from __future__ import annotations
@@ -101,15 +106,18 @@ def resolve_window(causal, left, right):
     return left, right
 
 
-def _request_attention(q, k, v, scale, left, right, softcap, sink):
-    """q [nq,Hq,D], k/v [nk,Hq,D] (already head-expanded, FP32).  Returns O, LSE."""
+def _request_attention(q, k, v, scale, left, right, softcap, sink, key_pos=None, total=None):
+    """q [nq,Hq,D], k/v [nk,Hq,D] (already head-expanded, FP32).  Returns O, LSE.
+
+    ``key_pos`` / ``total``: positions of the local keys inside the whole request and its total key count
+    (context parallelism); default is keys 0..nk-1 of a request of nk keys."""
     nq, hq, _ = q.shape
     nk = k.shape[0]
     out = np.zeros_like(q)
     lse = np.full((hq, nq), -np.inf, dtype=np.float32)
-    off = nk - nq
+    off = (nk if total is None else total) - nq
     rows = np.arange(nq)[:, None] + off
-    cols = np.arange(nk)[None, :]
+    cols = (np.arange(nk) if key_pos is None else np.asarray(key_pos))[None, :]
     hidden = np.zeros((nq, nk), dtype=bool)
     if right is not None:
         hidden |= cols > rows + right
@@ -153,6 +161,9 @@ def attention(
     q_descale=None,
     k_descale=None,
     v_descale=None,
+    cp_world_size=1,
+    cp_rank=0,
+    cp_tot_seqused_k=None,
 ):
     """FP32 attention over packed varlen Q and paged or packed K/V.
 
@@ -201,8 +212,13 @@ def attention(
             vr = vr * np.asarray(v_descale, np.float32)[b].reshape(1, hkv, 1)
         kr = np.repeat(kr, group, axis=1)
         vr = np.repeat(vr, group, axis=1)
+        key_pos = total = None
+        if cp_world_size > 1:   # this rank's local key j is the request's key j * W + r; the sink joins on rank 0 only
+            key_pos = np.arange(kr.shape[0]) * cp_world_size + cp_rank
+            total = int(np.asarray(cp_tot_seqused_k)[b])
         o_b, lse_b = _request_attention(qr.astype(np.float32), kr.astype(np.float32), vr.astype(np.float32),
-                                        scale, left, right, softcap, sink)
+                                        scale, left, right, softcap,
+                                        sink if cp_world_size <= 1 or cp_rank == 0 else None, key_pos, total)
         out[cu_q[b] : cu_q[b + 1]] = o_b
         lse[:, cu_q[b] : cu_q[b + 1]] = lse_b
     return out, lse

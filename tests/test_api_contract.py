@@ -154,6 +154,11 @@ def test_good_calls_are_eligible(as_b200):
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, s_aux=torch.zeros(8, dtype=torch.bfloat16)))
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, softcap=30.0, num_splits=256, causal=False))
     assert atrex.can_use_flash_attn_varlen_func(**dict(good, logits_soft_cap=30.0))
+    # context parallelism over the keys: local lengths in seqused_k, totals in cp_tot_seqused_k
+    total = torch.tensor([400, 800], dtype=torch.int32)
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, cp_world_size=4, cp_rank=3, cp_tot_seqused_k=total))
+    assert atrex.can_use_flash_attn_varlen_func(**dict(good, cp_world_size=4, cp_rank=0, cp_tot_seqused_k=total,
+                                                       s_aux=torch.zeros(8, dtype=torch.bfloat16)))
     assert atrex.can_use_flash_attn_varlen_func(
         **dict(_call(fp8=True, d=256), k_descale=torch.ones(1, 1).expand(2, 2))) == fp8_ok
 
@@ -167,8 +172,16 @@ BAD = [
     (dict(max_seqlen_k_decode=1), NotImplementedError, "max_seqlen_k_decode"),
     (dict(dropout_p=0.1), NotImplementedError, "dropout"),
     (dict(return_attn_probs=True), NotImplementedError, "return_attn_probs"),
-    (dict(cp_world_size=2), NotImplementedError, "context parallelism"),
-    (dict(cp_tot_seqused_k=torch.zeros(1)), NotImplementedError, "context parallelism"),
+    (dict(cp_world_size=2), ValueError, "cp_tot_seqused_k"),
+    (dict(cp_tot_seqused_k=torch.zeros(2, dtype=torch.int32)), ValueError, "cp_tot_seqused_k"),
+    (dict(cp_world_size=2, cp_rank=2, cp_tot_seqused_k=torch.zeros(2, dtype=torch.int32)), ValueError, "cp_rank"),
+    (dict(cp_world_size=0), ValueError, "cp_world_size"),
+    (dict(cp_world_size=2, cp_tot_seqused_k=torch.zeros(2, dtype=torch.int64)), ValueError, "cp_tot_seqused_k"),
+    (dict(cp_world_size=2, cp_tot_seqused_k=torch.zeros(3, dtype=torch.int32)), ValueError, "cp_tot_seqused_k"),
+    (dict(cp_world_size=2, cp_tot_seqused_k=torch.zeros(2, dtype=torch.int32), causal=False), NotImplementedError,
+     "causal"),
+    (dict(cp_world_size=2, cp_tot_seqused_k=torch.zeros(2, dtype=torch.int32), window_size=(64, 0)),
+     NotImplementedError, "window_size"),
     (dict(alibi_slopes=torch.zeros(8)), NotImplementedError, "ALiBi"),
     (dict(q_v=torch.zeros(1)), NotImplementedError, "q_v"),
     (dict(qv=torch.zeros(1)), NotImplementedError, "qv"),
@@ -381,3 +394,99 @@ def test_launcher_rejects_bad_blocks_before_any_launch():
     with pytest.raises(NotImplementedError, match="status 2"):
         runtime.plan(p)
     assert lib.atrex_fa_sm100_plan(None, ctypes.byref(info)) == 1
+
+
+def test_launcher_errors_name_the_failed_check_and_never_repeat_an_older_one():
+    """Every non-zero status comes with its own text; a later failure without text would otherwise show the
+    previous call's message on that thread."""
+    call = _call()
+    runtime, p = _plan(call, k_row_stride=3)
+    with pytest.raises(NotImplementedError, match="stride"):
+        runtime.plan(p)
+    fp8 = _call(fp8=True, d=256)
+    with pytest.raises(NotImplementedError, match="mma.sync route"):
+        runtime.plan(_plan(fp8, max_seqlen_q=1, max_seqlen_k=4096, route=runtime.ROUTE_MMA)[1])
+    _, capped = _plan(call, max_seqlen_q=64, max_seqlen_k=256, route=runtime.ROUTE_UMMA)
+    capped.softcap = 10.0
+    with pytest.raises(NotImplementedError, match="softcap"):
+        runtime.plan(capped)
+    with pytest.raises(ValueError, match="num_q_heads"):
+        runtime.plan(_plan(call, num_kv_heads=3)[1])
+    # a good call clears the text
+    runtime.plan(_plan(call)[1])
+    assert runtime.load_library().atrex_fa_sm100_last_error() == b""
+    # context-parallel blocks: rank range, totals pointer, causal only
+    with pytest.raises(ValueError, match="cp_rank"):
+        runtime.plan(_plan(call, cp_world_size=2, cp_rank=2, cp_tot_seqused_k=64)[1])
+    with pytest.raises(ValueError, match="cp_tot_seqused_k"):
+        runtime.plan(_plan(call, cp_world_size=2, cp_rank=1)[1])
+    with pytest.raises(NotImplementedError, match="context parallelism"):
+        runtime.plan(_plan(call, cp_world_size=2, cp_rank=1, cp_tot_seqused_k=64, causal=0)[1])
+    runtime.plan(_plan(call, cp_world_size=2, cp_rank=1, cp_tot_seqused_k=64)[1])
+
+
+@pytest.mark.parametrize("page", [192, 320, 448, 4224])
+def test_pages_that_are_not_a_multiple_of_the_kv_tile_are_planned(page):
+    """Page sizes that are multiples of 64 but not of the 128-key tile are served (a tile then straddles pages
+    and is fetched in 64-row boxes); the plan is the same as for a 128-row page."""
+    call = _call(page=page)
+    runtime, p = _plan(call, max_seqlen_q=64, max_seqlen_k=4 * page)
+    info = runtime.plan(p)
+    assert info.route == runtime.ROUTE_UMMA and info.m_rows == 256
+
+
+def test_kv_write_block_is_checked_on_the_host():
+    from atrex.src.nvidia.flash_attn.sm100 import kv_cache, runtime
+
+    lib = runtime.load_library()
+    kv_cache._bind(lib)
+    p = kv_cache.KvWriteParams()
+    p.struct_bytes, p.abi_version = ctypes.sizeof(kv_cache.KvWriteParams), runtime.ABI_VERSION
+    p.num_tokens, p.num_kv_heads, p.head_dim, p.page_size, p.num_pages = 4, 2, 128, 64, -1
+    assert lib.atrex_fa_sm100_kv_cache_write(ctypes.byref(p), None) == 1
+    assert b"negative" in lib.atrex_fa_sm100_last_error()
+
+
+def test_device_status_word_is_reported_once_and_reset(monkeypatch):
+    """A kernel whose bounded wait expired leaves a code in the per-device status word; the host reads it,
+    reports it and clears it (CPU stand-in for the word, no kernel involved)."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    word = torch.tensor([103], dtype=torch.int32)
+    monkeypatch.setitem(runtime._status_tensors, 0, word)
+    assert runtime.check_device_status(torch.device("cuda", 0)) == 103
+    assert int(word) == 0
+    assert runtime.check_device_status(torch.device("cuda", 0)) == 0
+
+
+def test_repeated_layouts_reuse_the_filled_block_but_never_addresses(as_b200, monkeypatch):
+    """The eager path keeps one filled parameter block per layout and patches addresses into it: a second call with
+    other tensors of the same layout must reach the launcher with the NEW addresses and must not plan again."""
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime
+
+    seen, plans = [], []
+    monkeypatch.setattr(runtime, "device_status", lambda device: None)
+    monkeypatch.setattr(runtime, "launch_params", lambda params, ws, dev: seen.append(
+        (params.q, params.k, params.out, params.seqused_k, params.block_table)))
+    real_plan = runtime.plan
+    # (no GPU here: give the planner the SM count it would otherwise ask the device for)
+    monkeypatch.setattr(runtime, "plan", lambda params: (plans.append(1), setattr(params, "sm_count", 148),
+                                                         real_plan(params))[2])
+    monkeypatch.setattr(torch.cuda, "device", lambda d: __import__("contextlib").nullcontext())
+    monkeypatch.setattr(launch, "_local", __import__("threading").local())
+    empty = torch.empty
+    monkeypatch.setattr(torch, "empty", lambda *a, **k: empty(*a, **{**k, "device": "cpu"}))
+    a, b = _call(), _call()
+    b["seqused_k"] = torch.tensor([7, 9], dtype=torch.int32)
+    out_a, out_b = torch.zeros(6, 8, 128, dtype=torch.bfloat16), torch.zeros(6, 8, 128, dtype=torch.bfloat16)
+    atrex.flash_attn_varlen_func(**a, num_splits=1, out=out_a)
+    atrex.flash_attn_varlen_func(**b, num_splits=1, out=out_b)
+    assert len(plans) == 1 and len(seen) == 2
+    assert seen[0][0] == a["q"].data_ptr() and seen[1][0] == b["q"].data_ptr()
+    assert seen[1][3] == b["seqused_k"].data_ptr() and seen[1][4] == b["block_table"].data_ptr()
+    assert (seen[0][2], seen[1][2]) == (out_a.data_ptr(), out_b.data_ptr())
+    # another layout (a wider block table) is planned on its own
+    c = _call()
+    c["block_table"] = torch.zeros(2, 8, dtype=torch.int32)
+    atrex.flash_attn_varlen_func(**c, num_splits=1, out=out_a)
+    assert len(plans) == 2

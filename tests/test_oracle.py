@@ -78,6 +78,43 @@ def test_sink_only_changes_normalisation():
         np.testing.assert_allclose(out1[:, h], out0[:, h] * np.exp(lse0[h] - expect_lse)[:, None], rtol=1e-5, atol=1e-6)
 
 
+def test_context_parallel_shards_merge_to_the_unsharded_result():
+    """Every W-th key on each rank (local key j = global key j * W + r): the ranks' partial (O, LSE), merged with the
+    split-KV algebra, equal the oracle over all keys - for decode (q_len 1), ragged prefill rows, a request whose
+    early rows see no key on some ranks, and a sink that must be counted once."""
+    rng = np.random.default_rng(7)
+    hq, hkv, d, world = 4, 2, 128, 3
+    q_lens, kv_lens = [1, 5, 7, 2], [50, 9, 7, 1]
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    cu_k = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+    q = fa_oracle.bf16_round(rng.standard_normal((cu[-1], hq, d), dtype=np.float32))
+    k = fa_oracle.bf16_round(rng.standard_normal((cu_k[-1], hkv, d), dtype=np.float32))
+    v = fa_oracle.bf16_round(rng.standard_normal((cu_k[-1], hkv, d), dtype=np.float32))
+    sink = np.array([0.5, -0.25, 1.5, 0.0], dtype=np.float32)
+    for use_sink in (None, sink):
+        full_o, full_l = fa_oracle.attention(q, k, v, cu, cu_seqlens_k=cu_k, causal=True, sink=use_sink)
+        parts_o, parts_l = [], []
+        for r in range(world):
+            ks = np.concatenate([k[cu_k[b]:cu_k[b + 1]][r::world] for b in range(4)])
+            vs = np.concatenate([v[cu_k[b]:cu_k[b + 1]][r::world] for b in range(4)])
+            local = [len(range(r, n, world)) for n in kv_lens]
+            cu_l = np.concatenate([[0], np.cumsum(local)]).astype(np.int32)
+            o, l = fa_oracle.attention(q, ks, vs, cu, cu_seqlens_k=cu_l, causal=True, sink=use_sink,
+                                       cp_world_size=world, cp_rank=r,
+                                       cp_tot_seqused_k=np.array(kv_lens, np.int32))
+            parts_o.append(o)
+            parts_l.append(l)
+        parts_o, parts_l = np.stack(parts_o), np.stack(parts_l)            # [W, T, H, D], [W, H, T]
+        with np.errstate(invalid="ignore"):
+            lse = np.logaddexp.reduce(parts_l, axis=0)
+            w = np.where(np.isfinite(parts_l), np.exp(parts_l - np.where(np.isfinite(lse), lse, 0.0)), 0.0)
+        merged = (parts_o * w.transpose(0, 2, 1)[..., None]).sum(axis=0)
+        np.testing.assert_allclose(merged, full_o, rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(lse, full_l, rtol=1e-5, atol=1e-5)
+        # rank 2 holds key 2 of request 2 (7 keys, 7 rows): rows 0 and 1 sit before it and see nothing there
+        assert np.all(np.isneginf(parts_l[2][:, cu[2]:cu[2] + 2])) and np.all(parts_o[2][cu[2]:cu[2] + 2] == 0)
+
+
 def test_rows_without_keys():
     case = cases.build(dict(page=16, q_lens=[5, 2], kv_lens=[3, 0], hq=2, hkv=1, d=128, fp8=False, causal=True))
     out, lse = _oracle(case)
@@ -98,7 +135,7 @@ def test_rounding_helpers():
 
 
 def test_work_counters():
-    # BASELINE config 1: 4*128*16*246400 FLOP
+    # 4 requests of 128, 256, 384 and 512 tokens, 16 query heads, head_dim 128: 4*128*16*246400 FLOP
     assert fa_oracle.algorithmic_flops([128, 256, 384, 512], [128, 256, 384, 512], 16, 128, True) == 2018508800
     assert fa_oracle.visible_pairs(4, 100, True) == 4 * 96 + 10
     assert fa_oracle.visible_pairs(4, 100, True, (9, 0)) == 40
