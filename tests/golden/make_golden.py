@@ -7,7 +7,7 @@ Run in a checkout that has the alibaba/atrex-kernels tree available:
 It loads ``op_test/utils/flash_attn_contract.py`` by file path (so the
 reference's conftest, which wants an installed wheel, is not triggered), feeds
 its ``reference(case)`` the seeded CPU inputs from ``cases.py`` and stores the
-outputs.  For the contiguous BASELINE case it also runs ``_fp32_prefill_ref``
+outputs.  For the contiguous four-request case it also runs ``_fp32_prefill_ref``
 from ``op_test/nvidia/flash_attn/test_flash_attn_sm120.py:316-332`` (extracted
 by source text, since importing that test module needs a GPU wheel).
 The fixtures are outputs only; inputs are rebuilt from seeds.

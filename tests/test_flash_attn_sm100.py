@@ -138,7 +138,7 @@ def test_prefill_group_sizes(group, route):
 
 
 def test_prefill_packed_kv(route):
-    """Contiguous K/V packed by cu_seqlens_k (BASELINE config 1 shape: [128,256,384,512], 16/2 heads)."""
+    """Contiguous K/V packed by cu_seqlens_k: four requests of 128, 256, 384 and 512 tokens, 16 query / 2 KV heads."""
     from atrex import flash_attn_varlen_func
 
     lens = [128, 256, 384, 512]
@@ -299,7 +299,8 @@ def test_umma_prefill_long_causal():
 
 @pytest.mark.parametrize("page", [16, 64, 128])
 def test_fp8_prefill_hd256(page):
-    """E4M3 inputs with per-(request, KV head) descales, BF16 output (BASELINE config 3 shape, scaled down)."""
+    """E4M3 inputs with per-(request, KV head) descales, BF16 output (head_dim 256, 12 query heads on 1 KV
+    head, cached prefix)."""
     case = T.make_case(page, [300, 70, 1, 513], [300, 900, 64, 513], hq=12, hkv=1, d=256, fp8=True, std=0.8,
                        poison_tail=True)
     T.check(case, fp8=True)
@@ -363,7 +364,8 @@ def test_bf16_wide_short_q_on_tcgen05(hq, hkv, q_len, splits):
 
 
 def test_baseline_decode_config_subsample():
-    """BASELINE config 2 shape (B64, 32/8 heads, D128, page 64, KV in [1024,16384]); oracle on 6 requests."""
+    """Decode batch of 64 requests, 32 query / 8 KV heads, head_dim 128, page 64, KV lengths uniform in
+    [1024, 16384]; oracle on 6 requests."""
     rng = np.random.default_rng(1729)
     kv = rng.integers(1024, 16385, size=64).tolist()
     case = T.make_case(64, [1] * 64, kv, hq=32, hkv=8, spare_pages=16)
@@ -371,7 +373,8 @@ def test_baseline_decode_config_subsample():
 
 
 def test_baseline_spec_decode_config_subsample():
-    """BASELINE config 4 shape scaled in batch (Q4, 64/4 heads, page 128, KV 32768, window 4095, sinks, LSE)."""
+    """Speculative decode: 4 query tokens, 64 query / 4 KV heads, page 128, 32768 keys, window (4095, 0), sinks and
+    LSE, at a batch of 6; oracle on two requests."""
     case = T.make_case(128, [4] * 6, [32768] * 6, hq=64, hkv=4, spare_pages=4)
     sink = torch.randn(64, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
     T.check(case, requests=[0, 5], window_size=(4095, 0), s_aux=sink)
@@ -413,8 +416,8 @@ def test_prefill_last_row_equals_decode_at_full_length():
 
 
 def test_baseline_multi_gpu_prefill_shape_subsample():
-    """BASELINE config 5 shape (64/8 heads, head_dim 128, page 64, q = kv) on a few requests; oracle on the
-    shortest one (the others are covered by the cross-kernel property above)."""
+    """Full-length prefill (query length = KV length) with 64 query / 8 KV heads, head_dim 128, page 64 on a few
+    requests; oracle on the shortest one (the others are covered by the cross-kernel property above)."""
     lens = [1024, 6000, 2500]
     case = T.make_case(64, lens, lens, hq=64, hkv=8, std=0.7)
     T.check(case, requests=[0])
@@ -582,3 +585,229 @@ def test_poisoned_scratch_on_split_tcgen05_path():
     poison = torch.full((64 << 20,), 0xFF, dtype=torch.uint8, device="cuda")
     del poison
     T.check(case, num_splits=8)
+
+
+# ------------------------------------------------------------------ pages that straddle KV tiles, clamped lengths
+@pytest.mark.parametrize("page,d,fp8", [(192, 128, False), (320, 128, False), (192, 256, True), (448, 256, False)])
+def test_pages_that_are_not_a_multiple_of_the_kv_tile(page, d, fp8):
+    """A 128-key tile over pages of 192 / 320 / 448 rows starts in one page and ends in the next: it must be
+    fetched as two 64-row boxes (one 128-row box would read past the page and miss the next page's first rows).
+    Prefill on the tcgen05 kernels and decode on the mma.sync kernel, unused rows poisoned."""
+    case = T.make_case(page, [300, 129], [300, 1500], hq=8, hkv=1, d=d, fp8=fp8, std=0.6, poison_tail=True)
+    assert _planned_route(case) == 2
+    T.check(case, fp8=fp8)
+    decode = T.make_case(page, [1, 2, 1], [1500, 193, 5000], hq=8, hkv=2, d=d, fp8=fp8, poison_tail=True)
+    T.check(decode, fp8=fp8)
+
+
+def test_lengths_beyond_the_block_table_are_clamped():
+    """A stale seqused_k larger than the table row can address (a graph replayed over overwritten metadata) is
+    clamped to max_pages * page_size on the device: the request then reads exactly its table row, never past it."""
+    page, lens = 64, [256, 512]
+    case = T.make_case(page, [1, 3], lens, hq=8, hkv=2, spare_pages=0)
+    assert case["block_table"].shape[1] * page == 512
+    want_o, want_l = T.run(case)
+    stale = dict(case, seqused_k=torch.tensor([256, 1 << 30], dtype=torch.int32, device="cuda"))
+    got_o, got_l = T.run(stale)
+    torch.cuda.synchronize()
+    assert torch.equal(got_o, want_o) and torch.equal(got_l, want_l)
+    prefill = T.make_case(page, [200, 512], lens, hq=8, hkv=2, spare_pages=0, seed=3)
+    want_o, want_l = T.run(prefill)
+    got_o, got_l = T.run(dict(prefill, seqused_k=torch.tensor([256, 2 ** 31 - 1], dtype=torch.int32, device="cuda")))
+    torch.cuda.synchronize()
+    assert torch.equal(got_o, want_o) and torch.equal(got_l, want_l)
+
+
+def test_packed_kv_with_both_cu_seqlens_k_and_seqused_k_through_the_c_abi():
+    """The C ABI (unlike the Python API) accepts packed K/V with both arrays: the used length of a request is the
+    smaller of its cu_seqlens_k extent and seqused_k, as the oracle defines it."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+    from oracle import fa_oracle
+
+    lens, used = [128, 300, 77], [100, 300, 0]
+    g = torch.Generator().manual_seed(11)
+    total = sum(lens)
+    q = torch.randn(9, 8, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(total, 2, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(total, 2, 128, generator=g).bfloat16().cuda()
+    cu_q = torch.tensor([0, 3, 6, 9], dtype=torch.int32).cuda()
+    cu_k = torch.tensor([0, 128, 428, 505], dtype=torch.int32).cuda()
+    su = torch.tensor(used, dtype=torch.int32).cuda()
+    eo, el = fa_oracle.attention(T.to_numpy(q), T.to_numpy(k), T.to_numpy(v), T.to_numpy(cu_q),
+                                 cu_seqlens_k=T.to_numpy(cu_k), seqused_k=np.array(used), softmax_scale=128 ** -0.5,
+                                 causal=True)
+    for route in (runtime.ROUTE_MMA, runtime.ROUTE_UMMA):
+        out = torch.full_like(q, float("nan"))
+        lse = torch.full((8, 9), float("nan"), dtype=torch.float32, device="cuda")
+        params = runtime.build_params(q, k, v, out, lse, cu_q, cu_k, su, None, None, None, None, None,
+                                      runtime.device_status(q.device), 3, 300, 128 ** -0.5, 0.0, True, -1, -1, 1, route)
+        need = runtime.plan(params).workspace_bytes
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+        runtime.launch_params(params, ws, q.device)
+        torch.cuda.synchronize()
+        T.compare(out, lse, eo, el, [0, 3, 6, 9])
+
+
+# ------------------------------------------------------------------ the benchmark's own shapes
+def test_fp8_prefill_at_the_benchmark_heads_with_amax_descales():
+    """FP8 E4M3 causal paged prefill with a cached prefix at 24 query / 2 KV heads, head_dim 256, page 128, each
+    request quantised with its own scales (max |x| / 448 per request and KV head, the way a serving stack fills an
+    FP8 cache); oracle on two of the four requests."""
+    hq, hkv, d, page = 24, 2, 256, 128
+    q_lens, prefix = [512, 700, 2048, 1500], [300, 0, 4096, 2000]
+    kv_lens = [a + b for a, b in zip(q_lens, prefix)]
+    case = T.make_case(page, q_lens, kv_lens, hq=hq, hkv=hkv, d=d, seed=21)      # BF16 draw, quantised below
+    table = case["block_table"].long()
+    cu = case["cu_seqlens_q"].tolist()
+    kq, vq = torch.zeros_like(case["k"], dtype=torch.float8_e4m3fn), torch.zeros_like(case["v"], dtype=torch.float8_e4m3fn)
+    qq = torch.empty_like(case["q"], dtype=torch.float8_e4m3fn)
+    scales = {n: torch.empty(len(q_lens), hkv, dtype=torch.float32, device="cuda")
+              for n in ("q_descale", "k_descale", "v_descale")}
+    for r, n in enumerate(kv_lens):
+        ids = table[r, : math.ceil(n / page)]
+        for src, dst, name in ((case["k"], kq, "k_descale"), (case["v"], vq, "v_descale")):
+            block = src[ids].float()
+            scale = block.abs().amax(dim=(0, 1, 3)).clamp_min(1e-6) / 448.0
+            dst[ids] = (block / scale[None, None, :, None]).to(torch.float8_e4m3fn)
+            scales[name][r] = scale
+        rows = case["q"][cu[r]:cu[r + 1]].float().view(q_lens[r], hkv, hq // hkv, d)
+        scale = rows.abs().amax(dim=(0, 2, 3)).clamp_min(1e-6) / 448.0
+        qq[cu[r]:cu[r + 1]] = (rows / scale[None, :, None, None]).view(q_lens[r], hq, d).to(torch.float8_e4m3fn)
+        scales["q_descale"][r] = scale
+    fp8_case = dict(case, q=qq, k=kq, v=vq, **scales)
+    T.check(fp8_case, requests=[0, 1], fp8=True, return_lse=False)
+
+
+def test_prefill_of_131072_keys():
+    """One request at the longest length the multi-GPU prefill workload draws (131072 tokens, query = keys), 8 query
+    / 1 KV head, head_dim 128, page 64.  Size-independent property: the last prefill row equals a query-length-1
+    decode over the same cache (another kernel: mma.sync split-KV + combine); oracle on the first and the last 256
+    rows (the oracle takes a row slice as a request of its own: bottom-right alignment puts the last rows at the
+    end of the keys, and the first 256 rows see the first 256 keys only)."""
+    n, hq, page = 131072, 8, 64
+    case = T.make_case(page, [n], [n], hq=hq, hkv=1, std=0.7, spare_pages=2, seed=5)
+    out, lse = T.run(case)
+    decode = dict(case, q=case["q"][-1:].contiguous(), max_seqlen_q=1,
+                  cu_seqlens_q=torch.tensor([0, 1], dtype=torch.int32, device="cuda"))
+    out_d, lse_d = T.run(decode)
+    torch.cuda.synchronize()
+    assert (out[-1:].float() - out_d.float()).abs().max().item() <= T.BF16_O_ATOL
+    assert torch.allclose(lse[:, -1:], lse_d, rtol=T.LSE_RTOL, atol=T.LSE_RTOL)
+    cu256 = torch.tensor([0, 256], dtype=torch.int32, device="cuda")
+    tail = dict(case, q=case["q"][-256:], cu_seqlens_q=cu256)
+    eo, el = T.oracle_for(tail)
+    T.compare(out[-256:], lse[:, -256:], eo, el, [0, 256])
+    head = dict(case, q=case["q"][:256], cu_seqlens_q=cu256,
+                seqused_k=torch.tensor([256], dtype=torch.int32, device="cuda"))
+    eo, el = T.oracle_for(head)
+    T.compare(out[:256], lse[:, :256], eo, el, [0, 256])
+
+
+# ------------------------------------------------------------------ context parallelism over the keys
+def _cp_shards(case, kv_lens, world, page):
+    """Deal every request's keys round-robin to `world` caches (rank r gets keys r, r + W, ...), each with its own
+    pool and block table; returns one call dict per rank."""
+    table = case["block_table"].long().cpu()
+    hkv, d = case["k"].shape[2:]
+    dtype = case["k"].dtype
+    raw = torch.bfloat16 if dtype == torch.bfloat16 else torch.uint8     # move FP8 values as bytes
+    src_k, src_v = case["k"].view(raw), case["v"].view(raw)
+    shards = []
+    for r in range(world):
+        local = [len(range(r, n, world)) for n in kv_lens]
+        counts = [math.ceil(n / page) for n in local]
+        pool_k = torch.zeros(sum(counts) + 1, page, hkv, d, dtype=raw, device="cuda")
+        pool_v = torch.zeros_like(pool_k)
+        sub = torch.full((len(kv_lens), max(counts + [1])), -1, dtype=torch.int32)
+        nxt = 0
+        for b, n in enumerate(kv_lens):
+            ids = table[b, : math.ceil(n / page)].cuda()
+            keys = src_k[ids].reshape(-1, hkv, d)[:n][r::world]
+            vals = src_v[ids].reshape(-1, hkv, d)[:n][r::world]
+            for j in range(counts[b]):
+                rows = keys[j * page:(j + 1) * page]
+                pool_k[nxt, : rows.shape[0]] = rows
+                pool_v[nxt, : rows.shape[0]] = vals[j * page:(j + 1) * page]
+                sub[b, j] = nxt
+                nxt += 1
+        pool_k, pool_v = pool_k.view(dtype), pool_v.view(dtype)
+        shards.append(dict(case, k=pool_k, v=pool_v, block_table=sub.cuda(),
+                           seqused_k=torch.tensor(local, dtype=torch.int32, device="cuda"),
+                           max_seqlen_k=sub.shape[1] * page, cp_world_size=world, cp_rank=r,
+                           cp_tot_seqused_k=torch.tensor(kv_lens, dtype=torch.int32, device="cuda")))
+    return shards
+
+
+def _cp_oracle(shard, sink):
+    from oracle import fa_oracle
+
+    descales = {n: None if shard.get(n) is None else T.to_numpy(shard[n]) for n in ("q_descale", "k_descale", "v_descale")}
+    return fa_oracle.attention(T.to_numpy(shard["q"]), T.to_numpy(shard["k"]), T.to_numpy(shard["v"]),
+                               T.to_numpy(shard["cu_seqlens_q"]), seqused_k=T.to_numpy(shard["seqused_k"]),
+                               block_table=T.to_numpy(shard["block_table"]), softmax_scale=shard["softmax_scale"],
+                               causal=True, sink=T.to_numpy(sink), cp_world_size=shard["cp_world_size"],
+                               cp_rank=shard["cp_rank"], cp_tot_seqused_k=T.to_numpy(shard["cp_tot_seqused_k"]),
+                               **descales)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("shape", ["decode", "spec_decode", "prefill", "prefill_hd256_fp8"])
+def test_context_parallel_ranks_on_one_gpu(world, shape):
+    """Context parallelism emulated on one GPU: rank r's cache holds keys r, r + W, ... of every request; each
+    rank's call (cp_world_size, cp_rank, cp_tot_seqused_k) is checked against the oracle for that rank (the mask
+    uses the keys' positions in the whole request; the sink joins on rank 0 only), and the merged (O, LSE) against
+    the oracle over all keys."""
+    from atrex.src.nvidia.flash_attn.sm100 import sharding
+
+    page, fp8, d, hq, hkv = 64, False, 128, 32, 8
+    if shape == "decode":
+        q_lens, kv_lens = [1, 1, 1, 1], [1000, 3, 333, 1]
+    elif shape == "spec_decode":
+        q_lens, kv_lens, hq, hkv = [4, 4, 2], [900, 5, 64], 64, 4
+    elif shape == "prefill":
+        q_lens, kv_lens, hq, hkv = [300, 40, 129], [300, 700, 129], 8, 2
+    else:
+        q_lens, kv_lens, hq, hkv, d, fp8, page = [200, 30], [200, 500], 12, 1, 256, True, 128
+    case = T.make_case(page, q_lens, kv_lens, hq=hq, hkv=hkv, d=d, fp8=fp8, std=0.7, seed=13)
+    sink = torch.randn(hq, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
+    full_o, full_l = T.oracle_for(case, sink=sink)
+    cu = T.to_numpy(case["cu_seqlens_q"])
+    outs, lses = [], []
+    for shard in _cp_shards(case, kv_lens, world, page):
+        o, l = T.run(shard, s_aux=sink)
+        torch.cuda.synchronize()
+        eo, el = _cp_oracle(shard, sink)
+        T.compare(o, l, eo, el, cu, fp8=fp8)
+        outs.append(o)
+        lses.append(l)
+    got_o, got_l = sharding._merge_parts_native(torch.stack(outs), torch.stack(lses))
+    torch.cuda.synchronize()
+    T.compare(got_o, got_l, full_o, full_l, cu, fp8=fp8)
+
+
+# ------------------------------------------------------------------ the bounded wait, seen to expire
+def test_a_bounded_wait_that_expires_reports_and_returns():
+    """Every device-side wait gives up after a limit, stores a code in the status word and lets its kernel return.
+    The self-test kernel waits (256 polls) on a barrier nobody arrives at: it must return normally with result 0
+    and code 104 in the status word, which the host-side check reports once and clears.  Nothing traps; the
+    context stays usable (an attention call afterwards is still correct)."""
+    import ctypes
+
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    lib = runtime.load_library()
+    fn = lib.atrex_fa_sm100_selftest_bounded_wait
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
+    device = torch.device("cuda", torch.cuda.current_device())
+    assert runtime.check_device_status(device) == 0
+    word = runtime.device_status(device)
+    result = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert fn(word.data_ptr(), result.data_ptr(), 256, stream) == 0
+    torch.cuda.synchronize()
+    assert int(result) == 0
+    assert runtime.check_device_status(device) == 104
+    assert runtime.check_device_status(device) == 0
+    assert fn(word.data_ptr(), None, 256, stream) == 1          # a result pointer is required
+    T.check(T.make_case(64, [1, 2], [300, 70], hq=8, hkv=2))

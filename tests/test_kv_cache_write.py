@@ -260,6 +260,33 @@ def test_write_empty_and_all_padding():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fp8", [False, True])
+def test_slots_past_the_pools_are_skipped(fp8):
+    """A slot id at or beyond num_pages * page_size (a corrupt slot mapping) is skipped like a padding token: the
+    caches here are the first 3 pages of a 5-page buffer, slots aimed at pages 3 and 4 must leave those pages (and
+    everything else) untouched."""
+    pages, page, heads, dim = 5, 16, 2, 64
+    dtype = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    big_k = torch.full((pages, page, heads, dim), 1.0, device="cuda").to(dtype)
+    big_v = big_k.clone()
+    kc, vc = big_k[:3], big_v[:3]
+    g = torch.Generator().manual_seed(4)
+    rows = torch.randn(6, heads, dim, generator=g).bfloat16().cuda()
+    loud = rows.clone()
+    loud[3:] *= 100.0                                   # the out-of-range tokens carry the largest magnitudes
+    slots = torch.tensor([0, 17, 47, 48, 79, 1 << 40], dtype=torch.int64, device="cuda")
+    kv_cache.write_kv_cache(loud, loud, kc, vc, slots)
+    torch.cuda.synchronize()
+    assert bool((big_k[3:].float() == 1.0).all()) and bool((big_v[3:].float() == 1.0).all())
+    flat = kc.reshape(-1, heads, dim).float()
+    want = rows[:3].float().to(dtype).float() if fp8 else rows[:3].float()
+    assert torch.equal(flat[[0, 17, 47]], want)
+    untouched = torch.ones(3 * page, dtype=torch.bool, device="cuda")
+    untouched[[0, 17, 47]] = False
+    assert bool((flat[untouched] == 1.0).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True])
 def test_attention_over_written_cache(fp8):
     """Write dense K/V through the native path, then attend: equals the attention oracle over the same rows."""
     import atrex
@@ -324,7 +351,7 @@ def test_write_in_cuda_graph():
 
 @pytest.mark.gpu
 def test_write_full_size_round_trip():
-    """BASELINE-sized step (128K new tokens, 8 KV heads, head_dim 128): gather(write(x)) == x, nothing else touched."""
+    """Full-size step (128K new tokens, 8 KV heads, head_dim 128): gather(write(x)) == x, nothing else touched."""
     tokens, heads, dim, page = 131072, 8, 128, 64
     pages = tokens // page + 16
     g = torch.Generator(device="cuda").manual_seed(1)

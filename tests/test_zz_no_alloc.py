@@ -36,42 +36,73 @@ def _params(runtime, case, out, lse, num_splits):
                                 -1, -1, num_splits, 0)
 
 
+def _compare_entry_points(runtime, lib, static_forward, case, splits, limit, *, expect_launches):
+    """One call through atrex_fa_sm100_forward with caller scratch, the same call through the allocation-free
+    entry point; both against each other and against the oracle."""
+    stream = torch.cuda.current_stream().cuda_stream
+    shape_lse = (case["q"].shape[1], case["q"].shape[0])
+    out_ref = torch.empty_like(case["q"])
+    lse_ref = torch.empty(shape_lse, dtype=torch.float32, device="cuda")
+    p_ref = _params(runtime, case, out_ref, lse_ref, splits)
+    info = runtime.plan(p_ref)
+    need = info.workspace_bytes
+    assert 0 < need <= limit
+    assert info.kernel_launches == expect_launches
+    workspace = torch.empty(need, dtype=torch.uint8, device="cuda")
+    runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(p_ref), workspace.data_ptr(), need, stream))
+
+    out_new = torch.full_like(case["q"], float("nan"))
+    lse_new = torch.full(shape_lse, float("nan"), dtype=torch.float32, device="cuda")
+    p_new = _params(runtime, case, out_new, lse_new, splits)
+    before = torch.cuda.memory_allocated()
+    runtime.raise_for_status(static_forward(ctypes.byref(p_new), stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+
+    assert (out_new.float() - out_ref.float()).abs().max().item() <= T.BF16_O_ATOL
+    # rows that see no key carry LSE = -inf in both; compare the rest relatively
+    assert torch.equal(torch.isneginf(lse_new), torch.isneginf(lse_ref))
+    seen = torch.isfinite(lse_ref)
+    rel = (lse_new[seen] - lse_ref[seen]).abs() / lse_ref[seen].abs().clamp_min(1.0)
+    assert rel.max().item() <= T.LSE_RTOL
+    # and both agree with the oracle
+    eo, el = T.oracle_for(case)
+    T.compare(out_new, lse_new, eo, el, T.to_numpy(case["cu_seqlens_q"]))
+    return info
+
+
 def test_static_scratch_entry_point_matches_regular_entry_point():
     runtime, lib, static_forward = _entry_points()
     torch.cuda.set_device(0)
-    stream = torch.cuda.current_stream().cuda_stream
     limit = lib.atrex_fa_sm100_static_scratch_bytes()
     assert limit == 16 * 1024 * 1024
 
     # two different decode batches back to back: the second call finds the first call's partials in the array
     for seed, kv_lens, splits in ((11, [3000, 64, 517, 1], 6), (12, [40, 2100, 900, 1300], 4)):
         case = T.make_case(64, [1, 3, 4, 2], kv_lens, hq=16, hkv=2, seed=seed, poison_tail=True)
-        shape_lse = (case["q"].shape[1], case["q"].shape[0])
-        out_ref = torch.empty_like(case["q"])
-        lse_ref = torch.empty(shape_lse, dtype=torch.float32, device="cuda")
-        p_ref = _params(runtime, case, out_ref, lse_ref, splits)
-        need = runtime.plan(p_ref).workspace_bytes
-        assert 0 < need <= limit
-        workspace = torch.empty(need, dtype=torch.uint8, device="cuda")
-        runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(p_ref), workspace.data_ptr(), need, stream))
+        info = _compare_entry_points(runtime, lib, static_forward, case, splits, limit, expect_launches=2)
+        assert info.route == runtime.ROUTE_MMA
+    assert runtime.check_device_status("cuda") == 0
 
-        out_new = torch.full_like(case["q"], float("nan"))
-        lse_new = torch.full(shape_lse, float("nan"), dtype=torch.float32, device="cuda")
-        p_new = _params(runtime, case, out_new, lse_new, splits)
-        before = torch.cuda.memory_allocated()
-        runtime.raise_for_status(static_forward(ctypes.byref(p_new), stream))
-        torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
 
-        assert (out_new.float() - out_ref.float()).abs().max().item() <= T.BF16_O_ATOL
-        # rows that see no key carry LSE = -inf in both; compare the rest relatively
-        assert torch.equal(torch.isneginf(lse_new), torch.isneginf(lse_ref))
-        seen = torch.isfinite(lse_ref)
-        rel = (lse_new[seen] - lse_ref[seen]).abs() / lse_ref[seen].abs().clamp_min(1.0)
-        assert rel.max().item() <= T.LSE_RTOL
-        # and both agree with the oracle
-        eo, el = T.oracle_for(case)
-        T.compare(out_new, lse_new, eo, el, T.to_numpy(case["cu_seqlens_q"]))
+def test_static_scratch_entry_point_on_the_planned_and_the_tcgen05_split_routes():
+    """The array also holds the row-tile plan of calls with several row tiles per request (plan kernel +
+    attention kernel + combine), and the wide FP32 partials of the tcgen05 single-tile kernel's split-KV path;
+    two calls in a row on each, the second over the first one's leftovers."""
+    runtime, lib, static_forward = _entry_points()
+    torch.cuda.set_device(0)
+    limit = lib.atrex_fa_sm100_static_scratch_bytes()
+    # several row tiles per request (max_seqlen_q * group > rows per tile) with an explicit split: plan kernel,
+    # tcgen05 single-tile kernel, combine
+    for seed, q_lens, kv_lens in ((3, [200, 40], [700, 40]), (4, [64, 300], [900, 300])):
+        case = T.make_case(64, q_lens, kv_lens, hq=8, hkv=2, seed=seed, std=0.6, poison_tail=True)
+        info = _compare_entry_points(runtime, lib, static_forward, case, 2, limit, expect_launches=3)
+        assert info.route == runtime.ROUTE_UMMA and info.m_rows == 128
+    # speculative decode: 64 packed rows per KV head on the tcgen05 single-tile kernel, three KV splits
+    for seed, kv_lens in ((5, [5000, 300, 128]), (6, [64, 4000, 2500])):
+        case = T.make_case(128, [4, 4, 3], kv_lens, hq=64, hkv=4, seed=seed, poison_tail=True)
+        info = _compare_entry_points(runtime, lib, static_forward, case, 3, limit, expect_launches=2)
+        assert info.route == runtime.ROUTE_UMMA and info.num_splits == 3
     assert runtime.check_device_status("cuda") == 0
 
 
