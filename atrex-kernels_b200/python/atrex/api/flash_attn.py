@@ -25,7 +25,11 @@ argument.  ``can_use_flash_attn_varlen_func`` runs the same checks and nothing
 else: it never loads the native library, allocates or launches.
 """
 
+import contextlib
+
 from atrex.utils.device_target import detect_device_target
+
+_NO_DEVICE_SWITCH = contextlib.nullcontext()
 
 # One target only.  4 is the reference's number for its datacenter-Blackwell
 # generation (python/atrex/api/flash_attn.py:6-10 uses {4} for sm103).
@@ -276,6 +280,38 @@ def _validate_flash_attn_call(call):
     return target, window, softcap
 
 
+_TENSOR_ARGUMENTS = ("q", "k", "v", "cu_seqlens_q", "cu_seqlens_k", "seqused_k", "block_table", "out", "q_descale",
+                     "k_descale", "v_descale", "s_aux", "cp_tot_seqused_k")
+_ALIGNED_ARGUMENTS = ("q", "k", "v", "out")
+_VALIDATED_LIMIT = 512
+_validated = {}   # call signature -> (window, softcap) of a call that passed _validate_flash_attn_call
+
+
+def _call_signature(call):
+    """Everything the validator reads, as one hashable value, or None when the call is not of the usual form.
+
+    The checks of ``_validate_flash_attn_call`` look at argument VALUES for scalars and at shape, strides, dtype,
+    device (plus 16-byte alignment of Q, K, V and out, and ``requires_grad``) for tensors; they never read tensor
+    contents.  A serving loop repeats one signature step after step, so a call whose signature already passed
+    skips the 60-odd checks.  Tensor identity, version counters and device data never enter the signature.
+    """
+    try:
+        parts = []
+        for name, value in call.items():
+            if name in _TENSOR_ARGUMENTS and value is not None:
+                parts.append((value.shape, value.stride(), value.dtype, value.device, value.requires_grad,
+                              value.data_ptr() % 16 if name in _ALIGNED_ARGUMENTS else 0))
+            elif name == "window_size" and value is not None:
+                parts.append(tuple(value))
+            else:
+                parts.append(value)
+        signature = tuple(parts)
+        hash(signature)
+        return signature
+    except (AttributeError, TypeError, RuntimeError):
+        return None
+
+
 def can_use_flash_attn_varlen_func(
     q,
     k,
@@ -373,14 +409,29 @@ def flash_attn_varlen_func(
     ``lse`` is FP32 ``[num_q_heads, total_q]`` in natural log.  When ``out`` is
     supplied it is written in place and returned.
     """
+    call = locals()
     import torch
-
-    target, window, softcap = _validate_flash_attn_call(locals())
-    if (target.family, target.arch) != ("nvidia", "sm100"):  # exhaustive with _TARGET_FA_VERSIONS
-        raise AssertionError(f"unhandled validated target {target}")
     from atrex.src.nvidia.flash_attn.sm100.launch import forward
 
-    with torch.cuda.device(q.device):
+    signature = _call_signature(call)
+    known = _validated.get(signature) if signature is not None else None
+    if known is None:
+        target, window, softcap = _validate_flash_attn_call(call)
+        if (target.family, target.arch) != ("nvidia", "sm100"):  # exhaustive with _TARGET_FA_VERSIONS
+            raise AssertionError(f"unhandled validated target {target}")
+        if signature is not None:
+            if len(_validated) >= _VALIDATED_LIMIT:
+                _validated.clear()
+            _validated[signature] = (window, softcap)
+    else:
+        window, softcap = known
+
+    # the reference enters the tensors' device around the launch (python/atrex/api/flash_attn.py:395); switching
+    # is skipped when that device is current already
+    index = q.device.index
+    guard = torch.cuda.device(q.device) if index is not None and index != torch.cuda.current_device() \
+        else _NO_DEVICE_SWITCH
+    with guard:
         output, lse = forward(
             q=q,
             k=k,
@@ -406,6 +457,7 @@ def flash_attn_varlen_func(
             cp_world_size=cp_world_size,
             cp_rank=cp_rank,
             cp_tot_seqused_k=cp_tot_seqused_k,
+            layout_token=signature,
         )
     return (output, lse) if return_softmax_lse else output
 

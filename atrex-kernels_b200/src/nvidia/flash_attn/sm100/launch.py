@@ -48,7 +48,9 @@ def _layouts() -> dict:
 def forward(*, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, max_seqlen_q, max_seqlen_k, page_table,
             softmax_scale, causal, softcap, window_size_left, window_size_right, learnable_sink, out,
             return_lse, q_descale, k_descale, v_descale, num_splits, route=None, cp_world_size=1, cp_rank=0,
-            cp_tot_seqused_k=None):
+            cp_tot_seqused_k=None, layout_token=None):
+    """``layout_token``: optional hashable value that determines every argument except tensor addresses (the
+    public API passes its call signature); it then serves as the layout key instead of one computed here."""
     if route is None:
         route = DEFAULT_ROUTE
     if out is None:
@@ -61,7 +63,7 @@ def forward(*, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, max_seqlen_q, max
             v_descale, learnable_sink, status, int(max_seqlen_q), int(max_seqlen_k), float(softmax_scale),
             float(softcap), bool(causal), window_left, window_right, int(num_splits), int(route),
             int(cp_world_size), int(cp_rank), cp_tot_seqused_k)
-    key = runtime.layout_key(*args)
+    key = (layout_token, route) if layout_token is not None else runtime.layout_key(*args)
     layouts = _layouts()
     entry = layouts.get(key)
     if entry is None:

@@ -237,10 +237,22 @@ def launch_params(params: Params, workspace, device) -> None:
     that was planned is the block that runs)."""
     ws_ptr = None if workspace is None else workspace.data_ptr()
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _raw_stream(device)
     status = (_lib or load_library()).atrex_fa_sm100_forward(ctypes.byref(params), ws_ptr, ws_bytes, stream)
     if status:
         raise_for_status(status)
+
+
+def _raw_stream(device) -> int:
+    """cudaStream_t of torch's current stream on ``device`` as an integer."""
+    index = device.index
+    if _get_raw_stream is not None and index is not None:
+        return _get_raw_stream(index)
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# torch's own fast accessor (no Stream object is built); the public API is the fallback
+_get_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _fa_fwd_meta(*args, **kwargs):

@@ -114,7 +114,8 @@ def as_b200(monkeypatch):
 
     monkeypatch.setattr(flash_attn, "detect_device_target",
                         lambda device: DeviceTarget("nvidia", "sm100", "12.9", 0))
-    return flash_attn
+    yield flash_attn
+    flash_attn._validated.clear()   # signatures accepted under the stand-in target must not outlive it
 
 
 def _call(fp8=False, paged=True, hq=8, hkv=2, d=128, page=64):
