@@ -1,6 +1,6 @@
 """Benchmark of the sm_100a attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode_q1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--samples R] [--impl ours|reference] [--workload decode_q1]
 
 One "step" is one call of ``atrex.flash_attn_varlen_func`` over one synthetic batch.
 The default workload is the BF16 Q1 paged decode configuration (batch 64, 32 query /
@@ -8,10 +8,26 @@ The default workload is the BF16 Q1 paged decode configuration (batch 64, 32 que
 seeded permutation of a 20000-page pool, N(0,1) inputs, num_splits = 0).  Its metric
 is achieved HBM GB/s on ALGORITHMIC bytes: the K and V rows every query can see, plus
 Q, O and the page-table entries read.  Prefill workloads report TFLOP/s on algorithmic
-FLOPs (4 * D * Hq * visible pairs).  With N > 1 a "weak" workload gives every rank its
-own batch of the same shape; the "strong" prefill workload shards one fixed request
-set over the ranks, FLOP-balanced, request by request.  No collective is on the data
-path; time is the maximum over ranks, value the work of all ranks divided by it.
+FLOPs (4 * D * Hq * visible pairs).
+
+The JSON line's top-level keys describe the chosen workload; with the default workload
+the same process then measures the other configurations of the metric (speculative
+decode, FP8 head_dim-256 prefill, BF16 head_dim-128 prefill, the request-sharded
+256-request prefill set) and reports them under ``sub_results`` with their own
+roofline, end-to-end and clock records.
+
+Protocol (the reference's harness takes the median of 31 samples of 20 calls,
+op_test/nvidia/flash_attn/test_flash_attn_sm103.py:1061-1087): W warm-up steps, then R
+samples (default 7) of exactly K steps each, every sample bracketed by a barrier and a
+device synchronise and timed with CUDA events; per sample the MAXIMUM over ranks counts;
+``ms_per_step`` / ``value`` come from the median sample and ``spread`` gives min and max.
+
+With N > 1 the requests of all ranks (N batches for a "weak" workload, one fixed set for
+the "strong" one) are pooled and dealt to the ranks by cost, longest first
+(``sharding.partition_requests``); every rank derives the same partition.  No collective
+is on the data path of the request-sharded workloads; ``decode_q1_headsplit`` (KV heads
+split over the ranks, O all-gathered) and ``decode_cp`` (every request's keys dealt to
+the ranks, (O, LSE) gathered and merged) are the variants with a real exchange step.
 
 ``--impl reference`` times the CPU FP32 attention (the oracle port of the reference's
 ``reference()`` in op_test/utils/flash_attn_contract.py:81-111) on the host cores on a
@@ -73,6 +89,13 @@ WORKLOADS = {
     "kv_write_fp8_scaled": dict(kind="kv_write", tokens=131072, hkv=8, d=128, page=64, fp8=True, scales="computed",
                                 scaling="weak"),
     "kv_write_small": dict(kind="kv_write", tokens=65536, hkv=8, d=128, page=64, fp8=False, scaling="weak"),
+    # variants with an exchange step (N >= 2): the decode batch with the KV heads split over the ranks and O
+    # all-gathered; 16 requests of 131072 keys whose keys are dealt to the ranks (context parallelism)
+    "decode_q1_headsplit": dict(kind="decode", batch=64, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=1024,
+                                kv_hi=16384, pool=20000, window=None, sink=False, lse=False, scaling="strong",
+                                variant="headsplit"),
+    "decode_cp": dict(kind="decode", batch=16, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=131072, kv_hi=131072,
+                      pool=None, window=None, sink=False, lse=True, scaling="strong", variant="cp"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
 }
@@ -211,18 +234,6 @@ class ClockSampler(threading.Thread):
         self.join(timeout=2)
         return dict(sm_mhz=statistics.median(self.samples) if self.samples else None, sm_max_mhz=self.max_mhz,
                     reasons=sorted(self.reasons), samples=len(self.samples))
-
-
-def physical_gpu_index(local_index):
-    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-    if visible:
-        try:
-            return int(visible.split(",")[local_index])
-        except (ValueError, IndexError):
-            return local_index
-    return local_index
-
-
 
 def physical_gpu_index(local_index):
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
@@ -537,19 +548,399 @@ def run_kv_write(args, spec, rank, world, local):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# Measurement of one attention workload
+# ---------------------------------------------------------------------------------------------------------------
+SUB_RESULTS = ("decode_q4_window", "prefill_fp8_hd256", "prefill_hd128", "prefill_sharded")
+SUB_BUDGET_S = 8.0      # device time one sub-result's timed samples may take: steps per sample are cut to fit
+
+
+def shard_requests(spec, world, rank, base_seed=1729):
+    """The requests rank ``rank`` of ``world`` serves, and the per-rank loads of the partition.
+
+    "strong" workloads are one fixed request set; "weak" ones pool the batches of all ranks (seed
+    ``base_seed + 1000 * r`` for rank r, so the one-GPU run is the plain seeded batch).  The pool is dealt by cost,
+    longest first (``sharding.partition_requests``); cost = the request's algorithmic work.  Pure host arithmetic:
+    every rank derives the same partition without communicating."""
+    from atrex.src.nvidia.flash_attn.sm100 import sharding
+
+    if spec["scaling"] == "strong":
+        all_q, all_kv = draw_lengths(spec, base_seed)
+    else:
+        all_q, all_kv = [], []
+        for r in range(world):
+            q, kv = draw_lengths(spec, base_seed + 1000 * r)
+            all_q += q
+            all_kv += kv
+    costs = [work_units(spec, [a], [b]) for a, b in zip(all_q, all_kv)]
+    shards = sharding.partition_requests(costs, world)
+    loads = sharding.shard_loads(costs, shards)
+    mine = shards[rank]
+    return [all_q[i] for i in mine], [all_kv[i] for i in mine], loads
+
+
+class Job:
+    """Rank, devices and the modules a measurement needs."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        self.args, self.torch, self.dist = args, torch, dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.device = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.device)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def reduce(self, values, op="max"):
+        t = self.torch.tensor(list(values), dtype=self.torch.float64, device=self.device)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX if op == "max" else self.dist.ReduceOp.SUM)
+        return t.tolist()
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def fp8_gemm_yardstick(torch, device, seconds=2.0):
+    """E4M3 x E4M3 -> BF16 GEMM rate of the vendor library (torch._scaled_mm, 8192^3): best single call and the
+    rate of a loop of ``seconds``.  A yardstick for the FP8 roofline fraction only; nothing on the attention path
+    calls it."""
+    n = 8192
+    try:
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=device)
+        run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            run()
+            e.record()
+            torch.cuda.synchronize()
+            best = min(best, s.elapsed_time(e))
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count, t0 = 0, time.perf_counter()
+        s.record()
+        while time.perf_counter() - t0 < seconds:
+            for _ in range(20):
+                run()
+            count += 20
+            torch.cuda.synchronize()
+        e.record()
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        return dict(burst=flops / (best * 1e-3) / 1e12, sustained=flops * count / (s.elapsed_time(e) * 1e-3) / 1e12,
+                    how=f"torch._scaled_mm E4M3 {n}^3 -> BF16: best of 10 calls, and a {seconds:.0f} s loop")
+    except Exception as exc:  # the library call is optional evidence, never a dependency
+        return dict(burst=None, sustained=None, how=f"torch._scaled_mm unavailable: {type(exc).__name__}: {exc}"[:200])
+
+
+def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, route_name="auto", budget_s=None,
+                      with_cpu_baseline=False):
+    """Time one attention workload on this job's ranks.  Returns the result dict on rank 0, None elsewhere."""
+    torch, dist, device, rank, world = job.torch, job.dist, job.device, job.rank, job.world
+    import atrex
+    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime, sharding
+
+    kind = KIND[spec["kind"]]
+    route = dict(auto=runtime.ROUTE_AUTO, mma=runtime.ROUTE_MMA, umma=runtime.ROUTE_UMMA)[route_name]
+    launch.DEFAULT_ROUTE = route
+    variant = spec.get("variant")
+    seed = 1729 + 1000 * rank
+    work_spec, extra_call = spec, {}
+    if variant is None:
+        q_lens, kv_lens, loads = shard_requests(spec, world, rank)
+        case_kv = kv_lens
+        sharding_note = ("one request pool (the N ranks' batches), dealt by cost longest-first, no collective"
+                         if spec["scaling"] == "weak" else
+                         "one fixed request set, dealt by cost longest-first, no collective")
+    else:
+        q_lens, kv_lens = draw_lengths(spec, 1729)          # every rank serves every request
+        loads = None
+        if variant == "cp":
+            case_kv = [len(range(rank, n, world)) for n in kv_lens]     # keys rank, rank + W, ... of each request
+            sharding_note = "keys of every request dealt round-robin to the ranks; (O, LSE) all-gathered and merged"
+        else:
+            case_kv = kv_lens
+            if spec["hkv"] % world:
+                raise SystemExit(f"{name}: {spec['hkv']} KV heads do not divide over {world} ranks")
+            work_spec = dict(spec, hq=spec["hq"] // world, hkv=spec["hkv"] // world)
+            sharding_note = "KV heads (and their query heads) split over the ranks; O all-gathered"
+            seed = 1729
+    case, host = build_device_case(spec, q_lens, case_kv, seed, device)
+    case["num_splits"] = num_splits
+    if variant == "cp" and world > 1:
+        extra_call = dict(cp_world_size=world, cp_rank=rank,
+                          cp_tot_seqused_k=torch.tensor(kv_lens, dtype=torch.int32, device=device))
+        case.update(extra_call)
+    if variant == "headsplit" and world > 1:
+        qh, kh = sharding.split_heads(spec["hq"], spec["hkv"], world, rank)
+        case["q"] = case["q"][:, qh].contiguous()
+        case["k"], case["v"] = case["k"][:, :, kh], case["v"][:, :, kh]       # views: strides unchanged
+        case["out"] = torch.empty(case["q"].shape, dtype=torch.bfloat16, device=device)
+        host["q"] = case["q"].cpu().pin_memory()
+    my_work = work_units(work_spec, q_lens, case_kv)
+
+    def step():
+        result = atrex.flash_attn_varlen_func(**case)
+        if variant == "cp":
+            return sharding.gather_context_parallel(result[0], result[1], world)[0]
+        out = result[0] if isinstance(result, tuple) else result
+        if variant == "headsplit":
+            return sharding.gather_heads(out, world)
+        return out
+
+    # ---------------- steps per sample: all of --steps unless a time budget asks for fewer ----------------
+    warmup = max(3, warmup)
+    step()
+    job.barrier()
+    if budget_s is not None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        one_ms = job.reduce([a.elapsed_time(b)])[0]
+        fit = int(budget_s * 1e3 / max(one_ms, 1e-3) / samples)
+        if fit < 1:
+            samples = max(3, min(samples, int(budget_s * 1e3 / max(one_ms, 1e-3))))
+            fit = 1
+        steps = max(1, min(steps, fit))
+        warmup = max(3, min(warmup, steps))
+
+    # ---------------- inputs resident: R samples of exactly `steps` steps ----------------
+    for _ in range(warmup):
+        step()
+    job.barrier()
+    sampler = ClockSampler(physical_gpu_index(job.local))
+    sampler.start()
+    sample_ms = []
+    for _ in range(samples):
+        job.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            step()
+        stop.record()
+        job.barrier()
+        sample_ms.append(start.elapsed_time(stop))
+    clocks = sampler.stop()
+
+    # ---------------- dominant kernel alone (events recorded by the launcher around it) ----------------
+    window = spec["window"] or (-1, -1)
+    lse_buf = (torch.empty((case["q"].shape[1], case["q"].shape[0]), dtype=torch.float32, device=device)
+               if spec["lse"] else None)
+    params = runtime.build_params(case["q"], case["k"], case["v"], case["out"], lse_buf, case["cu_seqlens_q"], None,
+                                  case["seqused_k"], case["block_table"], case.get("q_descale"), case.get("k_descale"),
+                                  case.get("v_descale"), case.get("s_aux"), None, case["max_seqlen_q"],
+                                  case["max_seqlen_k"], case["softmax_scale"], 0.0, True, window[0], window[1],
+                                  num_splits, route, extra_call.get("cp_world_size", 1), extra_call.get("cp_rank", 0),
+                                  extra_call.get("cp_tot_seqused_k"))
+    info = runtime.plan(params)
+    workspace = torch.empty(max(1, info.workspace_bytes), dtype=torch.uint8, device=device)
+    lib = runtime.load_library()
+    stream = torch.cuda.current_stream().cuda_stream
+    # Calls are queued back to back, each with its own event pair, so that an event is recorded when the previous
+    # call's last kernel retires and the attention kernel starts right behind it (no idle-GPU launch latency inside
+    # the measured interval).
+    n_timed = max(3, min(steps * samples, 50))
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
+    for a, b in pairs:
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+    for i in range(3 + n_timed):
+        a, b = pairs[max(i - 3, 0)]
+        params.profile_event_begin, params.profile_event_end = a.cuda_event, b.cuda_event
+        runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(params), workspace.data_ptr(),
+                                                             workspace.numel(), stream))
+    torch.cuda.synchronize()
+    kernel_ms = sorted(a.elapsed_time(b) for a, b in pairs)
+    kernel_ms_avg = sum(kernel_ms) / len(kernel_ms)
+
+    # ---------------- end to end: host inputs in, host result out ----------------
+    skip_e2e = case["q"].numel() * case["q"].element_size() > E2E_MAX_BYTES
+    dev_in = {key: case[key] for key in host}
+    out_shape = (1,) if skip_e2e else ((case["q"].shape[0], spec["hq"], spec["d"]) if variant == "headsplit"
+                                       else tuple(case["out"].shape))
+    out_host = torch.empty(out_shape, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step(sync=True):
+        for key, src in host.items():
+            dev_in[key].copy_(src, non_blocking=True)
+        out_host.copy_(step(), non_blocking=True)
+        if sync:
+            torch.cuda.current_stream().synchronize()
+
+    e2e_steps = steps if spec["kind"] == "decode" else max(1, min(steps, 5))
+    e2e_samples = max(3, min(samples, 5))
+    e2e_sample_ms, e2e_pipelined_ms = [float("nan")], float("nan")
+    if not skip_e2e:
+        for _ in range(3):
+            e2e_step()
+        e2e_sample_ms = []
+        for _ in range(e2e_samples):
+            job.barrier()
+            t0 = time.perf_counter()
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s2.record()
+            for _ in range(e2e_steps):
+                e2e_step()
+            e2.record()
+            job.barrier()
+            # every step ends with a host-side stream synchronise: wall clock and device events bracket the same work
+            e2e_sample_ms.append(max(s2.elapsed_time(e2), (time.perf_counter() - t0) * 1e3) / e2e_steps)
+        # the same steps queued without waiting for each result (one synchronise at the end), the way a serving
+        # loop issues them: the host's per-call work then overlaps the previous step's kernel
+        job.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step(sync=False)
+        job.barrier()
+        e2e_pipelined_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    status = runtime.check_device_status(device)
+
+    # ---------------- reduce over ranks: per sample the slowest rank counts ----------------
+    sample_ms = job.reduce(sample_ms)
+    e2e_sample_ms = job.reduce(e2e_sample_ms)
+    e2e_pipelined_ms = job.reduce([e2e_pipelined_ms])[0]
+    total = job.reduce([float(my_work)], op="sum")[0]
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    peak = peaks[kind["bound"]]
+    med_ms = statistics.median(sample_ms)
+    to_value = lambda ms_total: total * steps / (ms_total * 1e-3) / kind["scale"]  # noqa: E731
+    achieved = my_work / (kernel_ms_avg * 1e-3) / kind["scale"]
+    kernel_name = "atrex_sm100_fwd_mma_kernel"
+    if info.route == runtime.ROUTE_UMMA:
+        kernel_name = "atrex_sm100_fwd_umma_kernel" if info.m_rows == 256 else "atrex_sm100_fwd_umma1_kernel"
+    ratio = NCU_TRAFFIC_RATIO.get(name)
+    roofline = dict(bound=kind["bound"], achieved=achieved, peak=peak, unit=kind["unit"], frac=achieved / peak,
+                    traffic=None if ratio is None else ratio * my_work, peak_source=peaks["source"],
+                    kernel=kernel_name, kernel_ms=kernel_ms_avg, kernel_ms_min=kernel_ms[0],
+                    kernel_ms_max=kernel_ms[-1], kernel_launches_timed=len(kernel_ms))
+    if ratio is not None:
+        roofline["traffic_note"] = ("bytes per launch: ncu dram read+write of a small case of this kernel, scaled by "
+                                    "bytes processed")
+    if kind["bound"] == "hbm":
+        roofline["frac_of_nominal_8tbs"] = achieved / 8000.0
+    else:
+        roofline["peak_kind"] = "sustained cuBLAS bf16 (kernel timed inside a long step)"
+        roofline["frac_of_burst_peak"] = achieved / peaks["tensor_burst"]
+        roofline["frac_of_nominal_2250"] = achieved / 2250.0
+        if spec.get("fp8"):
+            yard = fp8_gemm_yardstick(torch, device)
+            roofline["peak_fp8_measured"] = yard
+            roofline["frac_of_nominal_fp8_4500"] = achieved / 4500.0
+            if yard["sustained"]:
+                roofline["frac_bf16_peak"] = roofline["frac"]
+                roofline["peak"], roofline["frac"] = yard["sustained"], achieved / yard["sustained"]
+                roofline["frac_of_burst_peak"] = achieved / yard["burst"]
+                roofline["peak_kind"] = "sustained E4M3 GEMM of the vendor library (torch._scaled_mm), measured in this run"
+            else:
+                roofline["note"] = "no FP8 GEMM rate could be measured here: frac is against the measured BF16 rate"
+    e2e_med = statistics.median(e2e_sample_ms)
+    per_step = info.kernel_launches
+    result = dict(
+        metric=kind["metric"], value=to_value(med_ms), unit=kind["unit"], n_gpus=world, steps=steps, warmup=warmup,
+        samples=len(sample_ms), ms_per_step=med_ms / steps,
+        spread=dict(ms_per_step_min=min(sample_ms) / steps, ms_per_step_max=max(sample_ms) / steps,
+                    value_min=to_value(max(sample_ms)), value_max=to_value(min(sample_ms)),
+                    note="median of the samples is reported; each sample = `steps` calls, slowest rank"),
+        higher_is_better=True, scaling=spec["scaling"], vs_baseline=None,
+        dtype="fp8_e4m3" if spec.get("fp8") else "bf16", data="synthetic",
+        config=dict(workload=name, requests_on_rank0=len(q_lens), batch=spec["batch"], num_q_heads=spec["hq"],
+                    num_kv_heads=spec["hkv"], head_dim=spec["d"], page_size=spec["page"], q_tokens_rank0=sum(q_lens),
+                    kv_tokens_rank0=sum(case_kv), max_kv_len=max(case_kv), num_splits=info.num_splits,
+                    route=route_name, sharding=sharding_note,
+                    rank_loads_max_over_mean=(None if not loads else max(loads) / (sum(loads) / len(loads))),
+                    l2="inputs larger than L2 (K/V + Q touched per step >> 126 MB)",
+                    algorithmic_work_per_step_rank0=my_work),
+        roofline=roofline,
+        e2e=dict(value=None if skip_e2e else total / (e2e_med * 1e-3) / kind["scale"], unit=kind["unit"],
+                 h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, steps=0 if skip_e2e else e2e_steps,
+                 samples=0 if skip_e2e else len(e2e_sample_ms),
+                 value_min=None if skip_e2e else total / (max(e2e_sample_ms) * 1e-3) / kind["scale"],
+                 value_max=None if skip_e2e else total / (min(e2e_sample_ms) * 1e-3) / kind["scale"],
+                 pipelined_value=None if skip_e2e else total / (e2e_pipelined_ms * 1e-3) / kind["scale"],
+                 skipped="Q exceeds the pinned staging limit of this benchmark" if skip_e2e else None,
+                 note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory, "
+                      "O copied back; the paged KV cache is resident device state; `value` waits for every step's "
+                      "result before issuing the next, `pipelined_value` queues the same steps and waits once"),
+        gpu_launches=per_step * steps * len(sample_ms), gpu_launches_per_step=per_step,
+        clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"], reasons=clocks["reasons"]),
+        device_status=status,
+    )
+    if with_cpu_baseline:
+        result["cpu_baseline"], _ = cpu_baseline(spec, q_lens, kv_lens, seed)
+    return result
+
+
+def measure_host_path(job, spec):
+    """Host time of one public call on rank 0: enqueue-only loop (nothing waits for the GPU inside it), best of 5
+    runs of 200 calls, and the same for the eligibility check alone (the full validation, which a repeated call
+    signature skips)."""
+    torch = job.torch
+    import atrex
+
+    if job.rank != 0:
+        return None
+    q_lens, kv_lens = draw_lengths(spec, 1729)
+    case, _ = build_device_case(spec, q_lens, kv_lens, 1729, job.device)
+    for _ in range(20):
+        atrex.flash_attn_varlen_func(**case)
+    torch.cuda.synchronize()
+
+    def best_of(fn):
+        best = float("inf")
+        for _ in range(5):
+            t0 = time.perf_counter()
+            for _ in range(200):
+                fn()
+            best = min(best, (time.perf_counter() - t0) / 200 * 1e6)
+            torch.cuda.synchronize()
+        return best
+
+    call_us = best_of(lambda: atrex.flash_attn_varlen_func(**case))
+    check_us = best_of(lambda: atrex.can_use_flash_attn_varlen_func(**case))
+    return dict(host_us_per_call=call_us, full_validation_us=check_us,
+                how="200 public calls enqueued back to back without waiting for the GPU, best of 5 runs; "
+                    "full_validation_us = can_use_flash_attn_varlen_func alone (every check, no launch)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--samples", type=int, default=7, help="timed samples of --steps calls each (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_q1", choices=sorted(WORKLOADS))
     ap.add_argument("--num-splits", type=int, default=0)
     ap.add_argument("--route", default="auto", choices=["auto", "mma", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sub-results", default=None,
+                    help="comma-separated workloads measured after the main one and reported under sub_results "
+                         "(default: the other configurations of the metric when the workload is decode_q1; 'none')")
     args = ap.parse_args()
     spec = WORKLOADS[args.workload]
-    kind = KIND[spec["kind"]]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -560,191 +951,39 @@ def main():
         run_kv_write(args, spec, rank, world, local)
         return
 
-    import torch
-    import torch.distributed as dist
+    job = Job(args)
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
 
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    import atrex
-    from atrex.src.nvidia.flash_attn.sm100 import launch, runtime, sharding
-
-    runtime.prewarm(device)
-    route = dict(auto=runtime.ROUTE_AUTO, mma=runtime.ROUTE_MMA, umma=runtime.ROUTE_UMMA)[args.route]
-    launch.DEFAULT_ROUTE = route
-    warmup = max(3, args.warmup)
-    if spec["scaling"] == "strong":
-        # one fixed request set for the whole job; every rank derives the same FLOP-balanced partition
-        seed = 1729
-        all_q, all_kv = draw_lengths(spec, seed)
-        costs = [sharding.request_cost(a, b) for a, b in zip(all_q, all_kv)]
-        mine = sharding.partition_requests(costs, world)[rank]
-        q_lens, kv_lens = [all_q[i] for i in mine], [all_kv[i] for i in mine]
-        seed += 1000 * rank
+    runtime.prewarm(job.device)
+    samples = max(1, args.samples)
+    line = measure_attention(job, args.workload, spec, max(1, args.steps), args.warmup, samples,
+                             num_splits=args.num_splits, route_name=args.route,
+                             with_cpu_baseline=job.world == 1 and not args.no_cpu_baseline)
+    if args.sub_results is None:
+        subs = SUB_RESULTS if args.workload == "decode_q1" else ()
     else:
-        seed = 1729 + 1000 * rank
-        q_lens, kv_lens = draw_lengths(spec, seed)
-    case, host = build_device_case(spec, q_lens, kv_lens, seed, device)
-    case["num_splits"] = args.num_splits
-    my_work = work_units(spec, q_lens, kv_lens)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def step():
-        atrex.flash_attn_varlen_func(**case)
-
-    # ---------------- kernel-resident timing ----------------
-    for _ in range(warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local))
-    sampler.start()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        step()
-    stop.record()
-    barrier()
-    clocks = sampler.stop()
-    elapsed_ms = start.elapsed_time(stop)
-
-    # ---------------- dominant kernel alone (events recorded by the launcher around it) ----------------
-    window = spec["window"] or (-1, -1)
-    plan_args = [case["q"], case["k"], case["v"], case["out"], None, case["cu_seqlens_q"], None, case["seqused_k"],
-                 case["block_table"], case.get("q_descale"), case.get("k_descale"), case.get("v_descale"),
-                 case.get("s_aux"), None, case["max_seqlen_q"],
-                 case["max_seqlen_k"], case["softmax_scale"], 0.0, True, window[0], window[1], args.num_splits, route]
-    if spec["lse"]:
-        plan_args[4] = torch.empty((spec["hq"], case["q"].shape[0]), dtype=torch.float32, device=device)
-    params = runtime.build_params(*plan_args)
-    info = runtime.plan(params)
-    workspace = torch.empty(max(1, info.workspace_bytes), dtype=torch.uint8, device=device)
-    lib = runtime.load_library()
-    stream = torch.cuda.current_stream().cuda_stream
-    # Calls are queued back to back, each with its own event pair, so that an event is recorded when the previous
-    # call's last kernel retires and the attention kernel starts right behind it (no idle-GPU launch latency inside
-    # the measured interval).
-    n_timed = min(args.steps, 50)
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
-    for a, b in pairs:
-        a.record(); b.record()
-    torch.cuda.synchronize()
-    for i in range(3 + n_timed):
-        a, b = pairs[max(i - 3, 0)]
-        params.profile_event_begin, params.profile_event_end = a.cuda_event, b.cuda_event
-        runtime.raise_for_status(lib.atrex_fa_sm100_forward(ctypes.byref(params), workspace.data_ptr(),
-                                                             workspace.numel(), stream))
-    torch.cuda.synchronize()
-    kernel_ms = [a.elapsed_time(b) for a, b in pairs]
-    kernel_ms_avg = sum(kernel_ms) / len(kernel_ms)
-
-    # ---------------- end to end: host inputs in, host result out ----------------
-    skip_e2e = case["q"].numel() * case["q"].element_size() > E2E_MAX_BYTES
-    dev_in = {name: case[name] for name in host}
-    out_host = torch.empty((1,) if skip_e2e else case["out"].shape, dtype=case["out"].dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = out_host.numel() * out_host.element_size()
-
-    def e2e_step(sync=True):
-        for name, src in host.items():
-            dev_in[name].copy_(src, non_blocking=True)
-        out = atrex.flash_attn_varlen_func(**case)
-        out = out[0] if isinstance(out, tuple) else out
-        out_host.copy_(out, non_blocking=True)
-        if sync:
-            torch.cuda.current_stream().synchronize()
-
-    e2e_steps = args.steps if spec["kind"] == "decode" else max(1, min(args.steps, 5))
-    e2e_ms = e2e_pipelined_ms = float("nan")
-    if not skip_e2e:
-        for _ in range(min(warmup, 3)):
-            e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s2.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        e2.record()
-        barrier()
-        # every step ends with a host-side stream synchronise, so wall clock and device events bracket the same work
-        e2e_ms = max(s2.elapsed_time(e2), (time.perf_counter() - t0) * 1e3) / e2e_steps
-        # the same steps queued without waiting for each result (one synchronise at the end), the way a serving
-        # loop issues them: the host's per-call work then overlaps the previous step's kernel
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step(sync=False)
-        barrier()
-        e2e_pipelined_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-
-    status = runtime.check_device_status(device)
-
-    # ---------------- reduce over ranks ----------------
-    stats = torch.tensor([elapsed_ms, e2e_ms, kernel_ms_avg, e2e_pipelined_ms], dtype=torch.float64, device=device)
-    total_work = torch.tensor([float(my_work)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(total_work, op=dist.ReduceOp.SUM)
-    elapsed_ms, e2e_ms, _slowest_kernel_ms, e2e_pipelined_ms = stats.tolist()   # roofline: rank 0's own kernel
-    total = total_work.item()
-
-    if rank == 0:
-        peaks = measured_peaks()
-        peak = peaks[kind["bound"]]
-        value = total * args.steps / (elapsed_ms * 1e-3) / kind["scale"]
-        achieved = my_work / (kernel_ms_avg * 1e-3) / kind["scale"]
-        kernel_name = "atrex_sm100_fwd_mma_kernel"
-        if info.route == runtime.ROUTE_UMMA:
-            kernel_name = "atrex_sm100_fwd_umma_kernel" if info.m_rows == 256 else "atrex_sm100_fwd_umma1_kernel"
-        ratio = NCU_TRAFFIC_RATIO.get(args.workload)
-        roofline = dict(bound=kind["bound"], achieved=achieved, peak=peak, unit=kind["unit"], frac=achieved / peak,
-                        traffic=None if ratio is None else ratio * my_work, peak_source=peaks["source"],
-                        kernel=kernel_name, kernel_ms=kernel_ms_avg)
-        if ratio is not None:
-            roofline["traffic_note"] = "bytes per launch: ncu dram read+write of a small case of this kernel, scaled by bytes processed"
-        if kind["bound"] == "hbm":
-            roofline["frac_of_nominal_8tbs"] = achieved / 8000.0
-        else:
-            roofline["peak_kind"] = "sustained cuBLAS bf16 (kernel timed inside a long step)"
-            roofline["frac_of_burst_peak"] = achieved / peaks["tensor_burst"]
-            roofline["frac_of_nominal_2250"] = achieved / 2250.0
-            if spec.get("fp8"):
-                roofline["note"] = "no measured FP8 peak on this pool: frac is against the measured BF16 rate"
-                roofline["frac_of_nominal_fp8_4500"] = achieved / 4500.0
-        line = dict(
-            metric=kind["metric"], value=value, unit=kind["unit"], n_gpus=world, steps=args.steps, warmup=warmup,
-            ms_per_step=elapsed_ms / args.steps, higher_is_better=True, scaling=spec["scaling"], vs_baseline=None,
-            dtype="fp8_e4m3" if spec.get("fp8") else "bf16", data="synthetic",
-            config=dict(workload=args.workload, requests_on_rank0=len(q_lens), batch=spec["batch"],
-                        num_q_heads=spec["hq"], num_kv_heads=spec["hkv"], head_dim=spec["d"], page_size=spec["page"],
-                        q_tokens_rank0=sum(q_lens), kv_tokens_rank0=sum(kv_lens), max_kv_len=max(kv_lens),
-                        num_splits=info.num_splits, route=args.route,
-                        sharding=("one batch per rank, no collective" if spec["scaling"] == "weak" else
-                                  "one request set, FLOP-balanced LPT by request, no collective"),
-                        l2="inputs larger than L2 (K/V + Q touched per step >> 126 MB)",
-                        algorithmic_work_per_step_rank0=my_work),
-            roofline=roofline,
-            e2e=dict(value=None if skip_e2e else total / (e2e_ms * 1e-3) / kind["scale"], unit=kind["unit"],
-                     h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, steps=0 if skip_e2e else e2e_steps,
-                     pipelined_value=None if skip_e2e else total / (e2e_pipelined_ms * 1e-3) / kind["scale"],
-                     skipped="Q exceeds the pinned staging limit of this benchmark" if skip_e2e else None,
-                     note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory, "
-                          "O copied back; the paged KV cache is resident device state; `value` waits for every step's "
-                          "result before issuing the next, `pipelined_value` queues the same steps and waits once"),
-            gpu_launches=info.kernel_launches * args.steps,
-            clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"], reasons=clocks["reasons"]),
-            device_status=status,
-        )
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"], _ = cpu_baseline(spec, q_lens, kv_lens, seed)
+        subs = tuple(n for n in args.sub_results.split(",") if n and n != "none")
+    sub_results = {}
+    for name in subs:
+        job.torch.cuda.empty_cache()
+        try:
+            sub = measure_attention(job, name, WORKLOADS[name], max(1, args.steps), args.warmup, samples,
+                                    budget_s=SUB_BUDGET_S)
+        except Exception as exc:  # noqa: BLE001 - a failed sub-result must not lose the main line
+            sub = dict(error=f"{type(exc).__name__}: {exc}"[:300])
+        if job.rank == 0:
+            sub_results[name] = sub
+    if subs and job.rank == 0:
+        job.torch.cuda.empty_cache()
+        try:
+            sub_results["host_path"] = measure_host_path(job, spec)
+        except Exception as exc:  # noqa: BLE001
+            sub_results["host_path"] = dict(error=f"{type(exc).__name__}: {exc}"[:300])
+    if job.rank == 0:
+        if sub_results:
+            line["sub_results"] = sub_results
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    job.close()
 
 
 if __name__ == "__main__":

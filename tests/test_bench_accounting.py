@@ -48,3 +48,35 @@ def test_every_workload_has_work_units():
         small = dict(spec, batch=2)
         q, kv = b.draw_lengths(small, 1)
         assert b.work_units(small, q, kv) > 0, name
+
+
+def test_pooled_partition_balances_the_ranks():
+    """With N ranks the benchmark pools the N seeded batches and deals the requests by cost, longest first: every
+    request is served exactly once, every rank derives the same partition, the one-rank job is the plain seeded
+    batch, and the ranks' work is level (decode: within 0.1 % at 8 ranks, where independent per-rank batches
+    differ by more than 10 %)."""
+    b = _bench()
+    spec = b.WORKLOADS["decode_q1"]
+    q1, kv1, loads1 = b.shard_requests(spec, 1, 0)
+    assert (q1, kv1) == b.draw_lengths(spec, 1729) and len(loads1) == 1
+    for world in (2, 4, 8):
+        pooled = sorted(kv for r in range(world) for kv in b.draw_lengths(spec, 1729 + 1000 * r)[1])
+        served, loads = [], None
+        for rank in range(world):
+            q, kv, loads_r = b.shard_requests(spec, world, rank)
+            assert loads is None or loads == loads_r
+            loads = loads_r
+            assert b.work_units(spec, q, kv) == loads[rank]
+            served += kv
+        assert sorted(served) == pooled
+        assert max(loads) / (sum(loads) / world) < 1.001
+    # the strong prefill set: one fixed draw, the same 256 requests whatever the rank count
+    strong = b.WORKLOADS["prefill_sharded"]
+    all_kv = sorted(b.draw_lengths(strong, 1729)[1])
+    for world in (1, 2, 8):
+        served, loads = [], None
+        for rank in range(world):
+            _, kv, loads = b.shard_requests(strong, world, rank)
+            served += kv
+        assert sorted(served) == all_kv
+        assert max(loads) / (sum(loads) / world) < 1.02
