@@ -72,6 +72,9 @@ WORKLOADS = {
                           clip=(1024, 131072), window=None, sink=False, lse=False, scaling="weak"),
     "prefill_small": dict(kind="prefill", batch=4, hq=64, hkv=8, d=128, page=64, median=4096, sigma=0.5,
                           clip=(1024, 16384), window=None, sink=False, lse=False, scaling="weak"),
+    # two requests of 32768 tokens: the long-request case profiler captures run on (K/V of one KV head = 16 MB)
+    "prefill_long2": dict(kind="prefill", batch=2, hq=64, hkv=8, d=128, page=64, median=32768, sigma=0.0,
+                          clip=(32768, 32768), window=None, sink=False, lse=False, scaling="weak"),
     # FP8 E4M3 causal paged prefill with a cached prefix, head_dim 256, per-(request, KV head) descales = amax / 448
     "prefill_fp8_hd256": dict(kind="prefill", batch=16, hq=24, hkv=2, d=256, page=128, q_range=(512, 4096),
                               prefix_range=(0, 4096), fp8=True, window=None, sink=False, lse=False, scaling="weak"),
