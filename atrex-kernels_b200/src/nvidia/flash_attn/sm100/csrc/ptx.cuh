@@ -15,7 +15,8 @@ enum DeviceStatus : int {
   kWaitEmptyTimeout = 102,  // producer never saw a stage released
   kWaitMmaTimeout = 103,    // tcgen05 completion barrier never fired
   kWaitMiscTimeout = 104,
-  kBadSmemAlignment = 105
+  kBadSmemAlignment = 105,
+  kWaitPeerTimeout = 106    // context-parallel merge: a peer rank never reported its partial result
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -137,3 +137,132 @@ def _merge_parts_native(outs, lses):
                                     heads, dim, stream))
     return out, lse
 
+
+
+class ContextParallelExchange:
+    """Context parallelism with the exchange and the merge as ONE kernel over peer memory.
+
+    Every rank attends its share of each request's keys (``flash_attn_varlen_func(..., cp_world_size, cp_rank,
+    cp_tot_seqused_k, return_softmax_lse=True, out=exchange.out_buffer(total_q))``) and then calls
+    ``merge(total_q, lse)``: one launch of ``atrex_sm100_cp_merge_kernel`` announces this rank's ``(O, LSE)`` to
+    the peers, waits (bounded) for theirs and reads them with plain peer loads over NVLink; no collective library
+    call and no staging copy sit on the data path.  The partial results live in a symmetric-memory allocation
+    (``torch.distributed._symmetric_memory``: the same virtual layout on every rank, mapped into every rank's
+    address space), two alternating slots so that a rank that runs ahead never overwrites a slot a slower rank is
+    still reading.  ``world_size == 1`` needs no peer memory and ``merge`` just hands the local pair back.
+
+    Capacity is fixed at construction (``max_total_q`` query tokens); nothing is allocated per step except the
+    result tensors.
+    """
+
+    _COUNTER_BYTES = 256
+
+    def __init__(self, max_total_q: int, num_q_heads: int, head_dim: int, device, group=None):
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.device = torch, torch.device(device)
+        self.heads, self.dim, self.capacity = int(num_q_heads), int(head_dim), int(max_total_q)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.step = 0
+        self._o_bytes = self.capacity * self.heads * self.dim * 2
+        self._lse_bytes = self.capacity * self.heads * 4
+        slot = (self._o_bytes + 255) // 256 * 256 + (self._lse_bytes + 255) // 256 * 256
+        self._slot_bytes = slot
+        total = self._COUNTER_BYTES + 2 * slot
+        if self.world > 1:
+            # plain peer mappings only: no multicast object is bound to these buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self._buffer = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+            self._buffer.zero_()
+            handle = symm_mem.rendezvous(self._buffer, dist.group.WORLD if group is None else group)
+            self._peer_base = [int(ptr) for ptr in handle.buffer_ptrs]
+            self._handle = handle
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)            # every rank's counters are zero before anyone signals
+        else:
+            self._buffer = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            self._peer_base = [self._buffer.data_ptr()]
+
+    def _slot_offset(self, step: int) -> int:
+        return self._COUNTER_BYTES + (step & 1) * self._slot_bytes
+
+    def out_buffer(self, total_q: int):
+        """The BF16 ``[total_q, Hq, D]`` tensor this step's attention call must write (pass it as ``out=``)."""
+        if total_q > self.capacity:
+            raise ValueError(f"{total_q} query tokens exceed the exchange capacity of {self.capacity}")
+        begin = self._slot_offset(self.step)
+        flat = self._buffer[begin: begin + total_q * self.heads * self.dim * 2]
+        return flat.view(self.torch.bfloat16).view(total_q, self.heads, self.dim)
+
+    def merge(self, total_q: int, lse):
+        """Exchange and merge this step's partial results; returns ``(out, lse)`` over all keys on every rank.
+        ``lse`` is the FP32 ``[Hq, total_q]`` tensor the attention call returned."""
+        import ctypes
+
+        from . import runtime
+
+        torch = self.torch
+        local_out = self.out_buffer(total_q)
+        if self.world == 1:
+            self.step += 1
+            return local_out.clone(), lse
+        begin = self._slot_offset(self.step)
+        lse_off = begin + (self._o_bytes + 255) // 256 * 256
+        self._buffer[lse_off: lse_off + total_q * self.heads * 4].view(torch.float32).view(self.heads, total_q).copy_(lse)
+        self.step += 1
+        out = torch.empty((total_q, self.heads, self.dim), dtype=torch.bfloat16, device=self.device)
+        merged_lse = torch.empty((self.heads, total_q), dtype=torch.float32, device=self.device)
+        params = CpMergeParams()
+        params.struct_bytes, params.abi_version = ctypes.sizeof(CpMergeParams), runtime.ABI_VERSION
+        for w, base in enumerate(self._peer_base):
+            params.parts[w] = base + begin
+            params.part_lse[w] = base + lse_off
+            params.counters[w] = base
+        params.out, params.lse = out.data_ptr(), merged_lse.data_ptr()
+        status = runtime.device_status(self.device)
+        params.device_status = None if status is None else status.data_ptr()
+        params.total_q, params.num_q_heads, params.head_dim = total_q, self.heads, self.dim
+        params.world, params.rank, params.step = self.world, self.rank, self.step
+        lib = runtime.load_library()
+        _bind_cp_merge(lib)
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            runtime.raise_for_status(lib.atrex_fa_sm100_cp_merge(ctypes.byref(params), stream))
+        return out, merged_lse
+
+
+def _cp_merge_struct():
+    import ctypes
+
+    class CpMergeParams(ctypes.Structure):
+        """Mirror of ``atrex_fa_sm100_cp_merge_params`` (include/atrex_fa_sm100.h)."""
+
+        _fields_ = [("struct_bytes", ctypes.c_uint32), ("abi_version", ctypes.c_uint32),
+                    ("parts", ctypes.c_void_p * 8), ("part_lse", ctypes.c_void_p * 8),
+                    ("counters", ctypes.c_void_p * 8),
+                    ("out", ctypes.c_void_p), ("lse", ctypes.c_void_p), ("device_status", ctypes.c_void_p),
+                    ("total_q", ctypes.c_int64),
+                    ("num_q_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("world", ctypes.c_int32),
+                    ("rank", ctypes.c_int32), ("step", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+    return CpMergeParams
+
+
+CpMergeParams = _cp_merge_struct()
+
+
+def _bind_cp_merge(lib):
+    import ctypes
+
+    if getattr(lib, "_atrex_cp_merge_bound", False):
+        return
+    lib.atrex_fa_sm100_cp_merge.restype = ctypes.c_int
+    lib.atrex_fa_sm100_cp_merge.argtypes = [ctypes.POINTER(CpMergeParams), ctypes.c_void_p]
+    lib._atrex_cp_merge_bound = True

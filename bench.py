@@ -698,7 +698,18 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
         host["q"] = case["q"].cpu().pin_memory()
     my_work = work_units(work_spec, q_lens, case_kv)
 
+    exchange = None
+    if variant == "cp" and world > 1 and job.args.cp_exchange == "fused":
+        exchange = sharding.ContextParallelExchange(case["q"].shape[0], spec["hq"], spec["d"], device)
+        sharding_note += "; exchange + merge = one kernel over peer loads (symmetric memory)"
+    elif variant == "cp":
+        sharding_note += "; exchange = two NCCL all-gathers, then the merge kernel"
+
     def step():
+        if exchange is not None:
+            case["out"] = exchange.out_buffer(case["q"].shape[0])
+            result = atrex.flash_attn_varlen_func(**case)
+            return exchange.merge(case["q"].shape[0], result[1])[0]
         result = atrex.flash_attn_varlen_func(**case)
         if variant == "cp":
             return sharding.gather_context_parallel(result[0], result[1], world)[0]
@@ -939,6 +950,8 @@ def main():
     ap.add_argument("--num-splits", type=int, default=0)
     ap.add_argument("--route", default="auto", choices=["auto", "mma", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cp-exchange", default="fused", choices=["fused", "nccl"],
+                    help="decode_cp: exchange + merge as one kernel over peer memory, or NCCL all-gathers + merge")
     ap.add_argument("--sub-results", default=None,
                     help="comma-separated workloads measured after the main one and reported under sub_results "
                          "(default: the other configurations of the metric when the workload is decode_q1; 'none')")

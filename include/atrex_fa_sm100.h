@@ -272,6 +272,39 @@ ATREX_FA_API int atrex_fa_sm100_merge_parts(const void* parts, const float* part
                                             void* stream);
 
 /*
+ * Context parallelism, exchange and merge as ONE kernel over peer memory (no counterpart in the reference).
+ * Rank `rank` of `world` (<= 8) calls this after its attention call (atrex_fa_sm100_forward with cp_world_size,
+ * return_lse) has been enqueued on `stream`.  parts[w] / part_lse[w] are rank w's O [total_q, num_q_heads,
+ * head_dim] BF16 and LSE [num_q_heads, total_q] FP32 as THIS process addresses them (its own buffers for
+ * w == rank, peer mappings - CUDA IPC, a symmetric-memory allocation - for the others); counters[w] is rank w's
+ * array of 8 uint32 step counters in such memory too, zero before the first step.  `step` is the same on all
+ * ranks for one exchange and grows by one per exchange.  The kernel stores `step` into slot `rank` of every
+ * rank's counters, waits until all slots of its own array have reached `step`, then reads every rank's pair with
+ * plain loads and writes out [total_q, num_q_heads, head_dim] BF16 and lse [num_q_heads, total_q]:
+ * out = sum_w exp(lse_w - lse) out_w, lse = logsumexp_w lse_w; a part whose lse is -inf is not read.
+ * The wait is bounded: if a peer never arrives, 106 is stored in *device_status and nothing is written.
+ * The caller keeps the peers from overwriting parts[w] while slower ranks still read them: with two alternating
+ * buffers a rank that has passed exchange n + 1 knows that exchange n was finished everywhere.
+ * With all pointers on one GPU and every counter already at `step` the call is a plain merge (how a one-GPU
+ * test emulates the ranks).  head_dim 128 or 256; parts and out 16-byte aligned.  Allocates nothing.
+ */
+typedef struct atrex_fa_sm100_cp_merge_params {
+  uint32_t struct_bytes; /* sizeof(atrex_fa_sm100_cp_merge_params) */
+  uint32_t abi_version;  /* ATREX_FA_SM100_ABI_VERSION */
+  const void* parts[8];
+  const float* part_lse[8];
+  uint32_t* counters[8];
+  void* out;
+  float* lse;
+  int32_t* device_status; /* optional */
+  int64_t total_q;
+  int32_t num_q_heads, head_dim, world, rank;
+  uint32_t step;
+  uint32_t reserved;
+} atrex_fa_sm100_cp_merge_params;
+ATREX_FA_API int atrex_fa_sm100_cp_merge(const atrex_fa_sm100_cp_merge_params* p, void* stream);
+
+/*
  * Self-test of the bounded device-side wait (no counterpart in the reference; its precedent for a wait
  * with a limit is _tma_mbarrier_try_wait_parity(..., time_limit), src/nvidia/flash_attn/sm120/attention_cutedsl.py:2434).
  * Every wait inside the kernels gives up after an iteration limit, stores a code in
