@@ -47,8 +47,9 @@ def _emulated(world, total_q, heads, dim, *, rank, step, counters_at, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     parts = torch.randn(world, total_q, heads, dim, generator=g, device="cuda").bfloat16()
     lses = torch.randn(world, heads, total_q, generator=g, device="cuda") * 3
-    lses[1, :, ::3] = float("-inf")                       # a rank without keys for some rows
-    parts[1, ::3] = float("nan")                          # ... whose O must not be read
+    if world > 1:
+        lses[1, :, ::3] = float("-inf")                   # a rank without keys for some rows
+        parts[1, ::3] = float("nan")                      # ... whose O must not be read
     if world > 2:
         lses[:, 0, 1] = float("-inf")                     # a row no rank has keys for
     counters = torch.full((world, 8), counters_at, dtype=torch.int32, device="cuda")
