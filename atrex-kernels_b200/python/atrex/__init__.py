@@ -4,8 +4,8 @@ Importing this package is free: no torch import, no library load, no compile.
 Each public name is a small proxy that imports its implementation module on the
 first call and then replaces itself with the real function, as
 ``_lazy_import_and_call`` does in the reference (python/atrex/__init__.py:13-39).
-Only the FlashAttention entry points exist in this build
-(python/atrex/__init__.py:66-73 in the reference).
+This build exports the FlashAttention entry points
+(python/atrex/__init__.py:66-73 in the reference) and compact sparse attention (:74-77).
 """
 
 from __future__ import annotations
@@ -50,4 +50,6 @@ flash_attn_varlen_func = _lazy_import_and_call(
     "flash_attn_varlen_func", "atrex.api.flash_attn"
 )
 
-__all__ = ("can_use_flash_attn_varlen_func", "flash_attn_varlen_func")
+qsa_compact = _lazy_import_and_call("qsa_compact", "atrex.api.qsa")
+
+__all__ = ("can_use_flash_attn_varlen_func", "flash_attn_varlen_func", "qsa_compact")

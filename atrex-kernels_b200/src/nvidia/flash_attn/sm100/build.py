@@ -22,6 +22,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
+# sources of the sibling operator that ships in the same library (src/nvidia/qsa/sm100)
+QSA_CSRC = HERE.parents[1] / "qsa" / "sm100" / "csrc"
 REPO_INCLUDE = HERE.parents[4] / "include"
 LIB = HERE / "libatrex_fa_sm100.so"
 STAMP = HERE / "build" / "stamp.txt"
@@ -44,7 +46,8 @@ def include_dir() -> Path:
 
 def source_hash() -> str:
     h = hashlib.sha256()
-    files = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [include_dir() / "atrex_fa_sm100.h", Path(__file__)]
+    files = (sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(QSA_CSRC.glob("*.cu"))
+             + sorted(include_dir().glob("atrex_*_sm100.h")) + [Path(__file__)])
     for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
@@ -62,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     obj_dir.mkdir(exist_ok=True)
     flags = NVCC_FLAGS + ["-I", str(include_dir()), "-I", str(CSRC)] + (["-Xptxas", "-v"] if verbose else [])
     objs, procs = [], []
-    for src in sorted(CSRC.glob("*.cu")):
+    for src in sorted(CSRC.glob("*.cu")) + sorted(QSA_CSRC.glob("*.cu")):
         obj = obj_dir / (src.stem + ".o")
         objs.append(obj)
         procs.append((src, subprocess.Popen([nvcc, *flags, "-c", str(src), "-o", str(obj)],

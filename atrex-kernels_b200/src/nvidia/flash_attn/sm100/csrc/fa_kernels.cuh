@@ -1,5 +1,7 @@
 // Entry points each kernel translation unit gives the C-ABI launcher.
 #pragma once
+#include <atomic>
+
 #include <cuda_bf16.h>
 
 #include "fa_params.cuh"
@@ -19,6 +21,13 @@ inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 
   cfg.stream = stream;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
 }
+
+// ---- launcher.cu: shared by every entry point of the library ----
+// Record the detail text of a failure for atrex_fa_sm100_last_error() on this thread and return `status`.
+int report_failure(int status, const char* what, cudaError_t cuda = cudaSuccess);
+void clear_failure();
+// SM count of the current device; fails with ATREX_FA_WRONG_DEVICE unless it is compute capability 10.0.
+int current_sm_count(int* sm_count);
 
 // ---- fa_mma.cu: split-KV mma.sync kernel ----
 int mma_rows_for(int packed_rows);            // 16, 32 or 64 rows per CTA

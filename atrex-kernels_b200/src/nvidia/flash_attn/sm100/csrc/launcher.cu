@@ -287,6 +287,16 @@ int encode_q_map(CUtensorMap* map, const void* base, int64_t head_stride, int64_
 }
 
 }  // namespace
+
+int report_failure(int status, const char* what, cudaError_t cuda) { return fail(status, what, cuda); }
+void clear_failure() { g_last_error[0] = 0; }
+int current_sm_count(int* sm_count) {
+  DeviceInfo* info = nullptr;
+  const int st = current_device(&info);
+  if (st == ATREX_FA_OK) *sm_count = info->sm_count;
+  return st;
+}
+
 }  // namespace atrex_sm100
 
 using namespace atrex_sm100;

@@ -1,0 +1,567 @@
+// Compact sparse attention (atrex.qsa_compact) for sm_100a: gated attention of every query row over the tokens of
+// its 512 selected four-token blocks, gathered through the page table.
+//
+// Native counterpart of the reference's sm100 kernels (src/nvidia/qsa/sm100/decode_fp8.py, prefill_bf16.py,
+// prefill_fp8.py; contract python/atrex/api/qsa.py:19-47), designed for B200 rather than translated.  The operator
+// is a gather: a row reads at most 2051 K and V rows of 256 elements per KV head (2.1 MB in BF16) and does
+// 8 - 12 heads x 2051 x 256 x 4 FLOP on them, two FLOP per byte gathered, so the kernel is built around keeping
+// many 512-byte row fetches in flight, not around tensor throughput:
+//
+//   * one CTA = (row, KV head, split of the row's token list); the 8 or 12 query heads of the KV head are the
+//     rows of one 16-row MMA tile (pack-GQA: one fetch of a K/V row serves the whole group);
+//   * each of the four warps is its own pipeline: it takes every fourth 16-token tile (four blocks), resolves
+//     the sixteen tokens to cache rows (block id -> token -> page table -> address, one lane per token),
+//     fetches K and V with 16-byte cp.async copies into its private double buffer (a row is one coalesced
+//     512-byte request) and computes S = Q K^T, the online softmax (log2 domain) and O += P V with mma.sync
+//     while the next tile's copies are in flight; no block-wide barrier inside the loop;
+//   * tokens that do not count (hidden block, request id out of range, page outside the table or the pool) are
+//     zero-filled in shared memory and masked in S, so no address is formed from them;
+//   * E4M3 caches are copied as bytes (half the traffic) and widened to BF16 in shared memory when a tile is
+//     consumed - every E4M3 value is exact in BF16 - so one MMA path serves both types; sm_scale carries the
+//     Q and K scales, v_scale multiplies the result;
+//   * the warps' partial states merge through shared memory; the epilogue rounds A to BF16, multiplies by
+//     sigmoid(gate) and stores BF16 (or writes a normalised FP32 partial + log2 LSE for the split combine).
+#include <cuda_fp8.h>
+
+#include "atrex_qsa_sm100.h"
+#include "fa_kernels.cuh"
+#include "ptx.cuh"
+
+namespace atrex_sm100 {
+namespace {
+
+constexpr int kD = ATREX_QSA_SM100_HEAD_DIM;
+constexpr int kTopk = ATREX_QSA_SM100_TOPK;
+constexpr int kTile = 16;                 // tokens per warp tile = four blocks
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxSplits = 16;
+constexpr int kQBytes = 16 * kD * 2;      // Q tile: 16 rows (8 or 12 used) x 256 BF16
+constexpr int kOperandBytes = kTile * kD * 2;          // one K or V tile as BF16: 8 KB
+constexpr int kWarpBytes = 4 * kOperandBytes;          // per warp: two stages of K + V (BF16), or raw stages + one widened tile (E4M3)
+constexpr int kMetaBytes = kWarps * 2 * kTile * 8;     // per warp and stage: 16 row offsets (int64, -1 = does not count)
+constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes;
+static_assert(kWarps * 16 * (kD + 2) * 4 <= kWarps * kWarpBytes, "merge buffer aliases the tile buffers");
+
+struct QsaParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int32_t* ids;
+  const void* pos;
+  const int32_t* table;
+  const int32_t* req;
+  const __nv_bfloat16* gate;
+  __nv_bfloat16* out;
+  float* part_o;      // [splits, rows, Hq, 256] normalised partial A (before v_scale)
+  float* part_lse;    // [splits, rows, Hq] log2-domain LSE
+  int32_t* status;
+  long long q_row_stride, q_head_stride, kv_page_stride, kv_row_stride, kv_head_stride;
+  int rows, hq, hkv, group, num_pages, page_size, batch, table_width, pos64, num_splits;
+  float scale_log2, v_scale;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
+  const uint32_t bytes = valid ? 16u : 0u;   // 0: the destination is zero-filled and nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 16 E4M3 bytes -> 16 BF16 (two 16-byte vectors), exact.
+__device__ __forceinline__ void widen_e4m3x16(const uint4& raw, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w[i] >> (16 * half)) & 0xFFFFu);
+      const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+      o[2 * i + half] = pack_bf16(f.x, f.y);
+    }
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreads, 1)
+atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_smem = smem;
+  uint8_t* tiles = smem + kQBytes;
+  long long* meta = reinterpret_cast<long long*>(smem + kQBytes + kWarps * kWarpBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = blockIdx.x / p.hkv, h = blockIdx.x % p.hkv;
+  const int split = blockIdx.y;
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (tid == 0 && p.status) atomicExch(p.status, kBadSmemAlignment);
+    return;
+  }
+
+  // ---- the row's token list: complete blocks from the id list, then the unfinished block ----
+  const long long position = p.pos64 ? reinterpret_cast<const long long*>(p.pos)[t]
+                                     : (long long)reinterpret_cast<const int*>(p.pos)[t];
+  const long long visible = position + 1;
+  const int request = p.req[t];
+  const bool live = visible > 0 && request >= 0 && request < p.batch;
+  const int complete = live ? (int)min((long long)kTopk, visible / 4) : 0;
+  const int listed = complete * 4;
+  const int n_tok = live ? listed + (int)(visible % 4) : 0;
+  const long long tail_start = (visible / 4) * 4;
+  const int n_tiles_row = (n_tok + kTile - 1) / kTile;
+  const int tile_lo = (int)(((long long)n_tiles_row * split) / p.num_splits);
+  const int tile_hi = (int)(((long long)n_tiles_row * (split + 1)) / p.num_splits);
+  const int32_t* row_ids = p.ids + (long long)t * kTopk;
+  const int32_t* table_row = p.table + (long long)(live ? request : 0) * p.table_width;
+
+  // ---- Q rows of this KV head's group -> shared memory as BF16 (swizzled like K) ----
+  {
+    constexpr int kChunks = kD / 8;   // 16-byte BF16 chunks per row
+    for (int idx = tid; idx < 16 * kChunks; idx += kThreads) {
+      const int r = idx / kChunks, c = idx % kChunks;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < p.group) {
+        const long long e = (long long)t * p.q_row_stride + (long long)(h * p.group + r) * p.q_head_stride + c * 8;
+        if (kFp8) {
+          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.q) + e));
+          uint4 lo, hi;
+          widen_e4m3x16(make_uint4(raw.x, raw.y, 0, 0), lo, hi);
+          val = lo;
+        } else {
+          val = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + e * 2));
+        }
+      }
+      *reinterpret_cast<uint4*>(q_smem + (c / 8) * (16 * 128) + swz128(r, c % 8)) = val;
+    }
+  }
+  __syncthreads();
+
+  // ---- per-warp pipeline over its tiles ----
+  uint8_t* my = tiles + warp * kWarpBytes;
+  long long* my_meta = meta + warp * 2 * kTile;
+  constexpr int kEsz = kFp8 ? 1 : 2;
+  constexpr int kRowBytes = kD * kEsz;                 // bytes of one cache row for one head
+  constexpr int kRawOperand = kTile * kRowBytes;       // raw bytes of one K or V tile
+  // BF16: stage s holds K at s * 2 * kOperandBytes, V right behind.  E4M3: raw stage s at s * 2 * kRawOperand
+  // (K then V); the widened tile (K then V) sits in the second half of the warp's region.
+  auto raw_k = [&](int s) { return my + s * 2 * kRawOperand; };
+  auto raw_v = [&](int s) { return my + s * 2 * kRawOperand + kRawOperand; };
+
+  // resolve the 16 tokens of tile `ti` (one lane per token) and start its copies into stage s
+  auto issue_tile = [&](int ti, int s) {
+    long long off = -1;
+    if (lane < kTile) {
+      const int i = ti * kTile + lane;
+      long long tok = -1;
+      if (i < listed) {
+        const int blk = row_ids[i >> 2];
+        if (blk >= 0) tok = (long long)blk * 4 + (i & 3);
+      } else if (i < n_tok) {
+        tok = tail_start + (i - listed);
+      }
+      if (tok >= 0) {
+        const long long lp = tok / p.page_size;
+        if (lp < p.table_width) {
+          const int phys = table_row[lp];
+          if (phys >= 0 && phys < p.num_pages)
+            off = (long long)phys * p.kv_page_stride + (tok - lp * p.page_size) * p.kv_row_stride +
+                  (long long)h * p.kv_head_stride;
+        }
+      }
+      my_meta[s * kTile + lane] = off;
+    }
+    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.k);
+    const uint8_t* vbase = reinterpret_cast<const uint8_t*>(p.v);
+    if (kFp8) {
+      // a row is 256 bytes = 16 chunks: two rows per warp instruction
+#pragma unroll
+      for (int j = 0; j < kTile / 2; ++j) {
+        const int r = 2 * j + (lane >> 4), c = lane & 15;
+        const long long row_off = __shfl_sync(0xffffffffu, off, r);
+        const bool ok = row_off >= 0;
+        const long long byte = ok ? row_off + c * 16 : 0;
+        cp_async16(raw_k(s) + r * kRowBytes + c * 16, kbase + byte, ok);
+        cp_async16(raw_v(s) + r * kRowBytes + c * 16, vbase + byte, ok);
+      }
+    } else {
+      // a row is 512 bytes = 32 chunks: one row per warp instruction, written in the swizzled MMA layout
+#pragma unroll
+      for (int r = 0; r < kTile; ++r) {
+        const long long row_off = __shfl_sync(0xffffffffu, off, r);
+        const bool ok = row_off >= 0;
+        const long long byte = ok ? row_off * 2 + lane * 16 : 0;
+        const uint32_t dst = (lane / 8) * (kTile * 128) + swz128(r, lane % 8);
+        cp_async16(raw_k(s) + dst, kbase + byte, ok);
+        cp_async16(raw_v(s) + dst, vbase + byte, ok);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o_acc[kD / 8][4];
+#pragma unroll
+  for (int i = 0; i < kD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+  const int g = lane >> 2, tq = lane & 3;
+  const int mat = lane >> 3, mrow = lane & 7;
+  const uint32_t q_addr = smem_u32(q_smem);
+  const uint32_t q_lane_row = mrow + (mat & 1) * 8, q_lane_chunk = mat >> 1;
+  const uint32_t k_lane_row = mrow + (mat >> 1) * 8, k_lane_chunk = mat & 1;
+  const uint32_t v_lane_row = mrow + (mat & 1) * 8, v_lane_chunk = mat >> 1;
+
+  int stage = 0;
+  const int first = tile_lo + warp;
+  if (first < tile_hi) issue_tile(first, 0);
+  for (int ti = first; ti < tile_hi; ti += kWarps) {
+    const int next = ti + kWarps;
+    if (next < tile_hi) {
+      issue_tile(next, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+    // which of the tile's 16 tokens count (bit r = token r)
+    const unsigned live_mask = __ballot_sync(0xffffffffu, lane < kTile && my_meta[stage * kTile + lane] >= 0) & 0xFFFFu;
+
+    uint32_t k_addr, v_addr;
+    if (kFp8) {
+      // widen the raw tile into the BF16 tile (second half of the warp's region), swizzled for the MMA
+      uint8_t* wide_k = my + 2 * kOperandBytes;
+      uint8_t* wide_v = wide_k + kOperandBytes;
+#pragma unroll
+      for (int j = 0; j < kTile / 2; ++j) {
+        const int r = 2 * j + (lane >> 4), c = lane & 15;   // raw chunk c = elements 16c .. 16c + 15 = BF16 chunks 2c, 2c + 1
+        uint4 lo, hi;
+        widen_e4m3x16(*reinterpret_cast<const uint4*>(raw_k(stage) + r * kRowBytes + c * 16), lo, hi);
+        *reinterpret_cast<uint4*>(wide_k + ((2 * c) / 8) * (kTile * 128) + swz128(r, (2 * c) % 8)) = lo;
+        *reinterpret_cast<uint4*>(wide_k + ((2 * c + 1) / 8) * (kTile * 128) + swz128(r, (2 * c + 1) % 8)) = hi;
+        widen_e4m3x16(*reinterpret_cast<const uint4*>(raw_v(stage) + r * kRowBytes + c * 16), lo, hi);
+        *reinterpret_cast<uint4*>(wide_v + ((2 * c) / 8) * (kTile * 128) + swz128(r, (2 * c) % 8)) = lo;
+        *reinterpret_cast<uint4*>(wide_v + ((2 * c + 1) / 8) * (kTile * 128) + swz128(r, (2 * c + 1) % 8)) = hi;
+      }
+      __syncwarp();
+      k_addr = smem_u32(wide_k);
+      v_addr = smem_u32(wide_v);
+    } else {
+      k_addr = smem_u32(raw_k(stage));
+      v_addr = smem_u32(raw_v(stage));
+    }
+
+    // ---- S = Q K^T : 16 rows x 16 tokens ----
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kb = 0; kb < kD / 64; ++kb) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t a[4], b0, b1, b2, b3;
+        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + kb * (16 * 128) + swz128(q_lane_row, ks * 2 + q_lane_chunk));
+        ldmatrix_x4(b0, b1, b2, b3, k_addr + kb * (kTile * 128) + swz128(k_lane_row, ks * 2 + k_lane_chunk));
+        mma_bf16_16816(s[0], a, b0, b1);
+        mma_bf16_16816(s[1], a, b2, b3);
+      }
+    }
+    // ---- scale, hide the tokens that do not count, online softmax (log2 domain) ----
+    float alpha[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = j * 8 + 2 * tq + (e & 1);
+        s[j][e] = (live_mask >> col) & 1u ? s[j][e] * p.scale_log2 : -INFINITY;
+      }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float mx = fmaxf(fmaxf(s[0][2 * hh], s[0][2 * hh + 1]), fmaxf(s[1][2 * hh], s[1][2 * hh + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hh], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[hh] = fast_exp2(m_run[hh] - m_use);
+      m_run[hh] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        s[j][2 * hh] = fast_exp2(s[j][2 * hh] - m_use);
+        s[j][2 * hh + 1] = fast_exp2(s[j][2 * hh + 1] - m_use);
+        sum += s[j][2 * hh] + s[j][2 * hh + 1];
+      }
+      l_run[hh] = l_run[hh] * alpha[hh] + sum;
+    }
+#pragma unroll
+    for (int n = 0; n < kD / 8; ++n) {
+      o_acc[n][0] *= alpha[0];
+      o_acc[n][1] *= alpha[0];
+      o_acc[n][2] *= alpha[1];
+      o_acc[n][3] *= alpha[1];
+    }
+    // ---- O += P V : one 16-token step ----
+    {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[0][0], s[0][1]);
+      a[1] = pack_bf16(s[0][2], s[0][3]);
+      a[2] = pack_bf16(s[1][0], s[1][1]);
+      a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int kb = 0; kb < kD / 64; ++kb) {
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, v_addr + kb * (kTile * 128) + swz128(v_lane_row, cp * 2 + v_lane_chunk));
+          mma_bf16_16816(o_acc[kb * 8 + cp * 2], a, b0, b1);
+          mma_bf16_16816(o_acc[kb * 8 + cp * 2 + 1], a, b2, b3);
+        }
+      }
+    }
+    __syncwarp();          // every lane is done with this stage before the next iteration's copies may land in it
+    stage ^= 1;
+  }
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+  }
+
+  // ---- merge the four warps' states through shared memory (aliases the tile buffers) ----
+  __syncthreads();
+  float* red_o = reinterpret_cast<float*>(tiles);           // [warp][16][256]
+  float* red_m = red_o + kWarps * 16 * kD;                  // [warp][16]
+  float* red_l = red_m + kWarps * 16;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = g + hh * 8;
+    float* dst = red_o + ((size_t)warp * 16 + r) * kD;
+#pragma unroll
+    for (int n = 0; n < kD / 8; ++n)
+      *reinterpret_cast<float2*>(dst + n * 8 + 2 * tq) = make_float2(o_acc[n][2 * hh], o_acc[n][2 * hh + 1]);
+    if (tq == 0) {
+      red_m[warp * 16 + r] = m_run[hh];
+      red_l[warp * 16 + r] = l_run[hh];
+    }
+  }
+  __syncthreads();
+  const bool split_mode = p.num_splits > 1;
+  for (int idx = tid; idx < p.group * (kD / 4); idx += kThreads) {
+    const int r = idx / (kD / 4), c4 = idx % (kD / 4);
+    const int head = h * p.group + r;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, red_m[w * 16 + r]);
+    const float m_use = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = red_m[w * 16 + r];
+      if (mw == -INFINITY) continue;
+      const float sc = fast_exp2(mw - m_use);
+      l += red_l[w * 16 + r] * sc;
+      const float4 ow = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * kD + c4 * 4);
+      o.x += ow.x * sc; o.y += ow.y * sc; o.z += ow.z * sc; o.w += ow.w * sc;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+    const long long slot = (long long)t * p.hq + head;
+    if (split_mode) {
+      const long long ps = (long long)split * p.rows * p.hq + slot;
+      *reinterpret_cast<float4*>(p.part_o + ps * kD + c4 * 4) = o;
+      if (c4 == 0) p.part_lse[ps] = l > 0.f ? m_use + log2f(l) : -INFINITY;
+    } else {
+      const uint2 graw = *reinterpret_cast<const uint2*>(p.gate + slot * kD + c4 * 4);
+      const float gt[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xFFFF0000u),
+                           __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xFFFF0000u)};
+      const float av[4] = {o.x * p.v_scale, o.y * p.v_scale, o.z * p.v_scale, o.w * p.v_scale};
+      float res[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a_bf16 = __bfloat162float(__float2bfloat16(av[i]));       // A leaves the attention as BF16
+        res[i] = a_bf16 * (1.f / (1.f + __expf(-gt[i])));
+      }
+      uint2 packed;
+      packed.x = pack_bf16(res[0], res[1]);
+      packed.y = pack_bf16(res[2], res[3]);
+      *reinterpret_cast<uint2*>(p.out + slot * kD + c4 * 4) = packed;
+    }
+  }
+}
+
+// Split combine: out = bf16( bf16( sum_i w_i A_i / sum_i w_i * v_scale ) * sigmoid(gate) ), w_i = 2^(lse_i - max);
+// a split that saw no token has lse = -inf and its partial is not read.  One warp per (row, head).
+__global__ void __launch_bounds__(256)
+atrex_sm100_qsa_combine_kernel(const __grid_constant__ QsaParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long slot = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long slots = (long long)p.rows * p.hq;
+  if (slot >= slots) return;
+  float mx = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) mx = fmaxf(mx, p.part_lse[s * slots + slot]);
+  float acc[8], denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float l = p.part_lse[s * slots + slot];
+      if (l == -INFINITY) continue;
+      const float w = fast_exp2(l - mx);
+      denom += w;
+      const float4* src = reinterpret_cast<const float4*>(p.part_o + (s * slots + slot) * kD + lane * 8);
+      const float4 a = src[0], b = src[1];
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+      acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+    }
+  }
+  const float inv = denom > 0.f ? p.v_scale / denom : 0.f;
+  const uint4 graw = *reinterpret_cast<const uint4*>(p.gate + slot * kD + lane * 8);
+  const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w};
+  uint32_t packed[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xFFFF0000u);
+    const float a0 = __bfloat162float(__float2bfloat16(acc[2 * i] * inv));
+    const float a1 = __bfloat162float(__float2bfloat16(acc[2 * i + 1] * inv));
+    packed[i] = pack_bf16(a0 * (1.f / (1.f + __expf(-g0))), a1 * (1.f / (1.f + __expf(-g1))));
+  }
+  *reinterpret_cast<uint4*>(p.out + slot * kD + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+struct QsaResolved {
+  int splits, launches;
+  uint64_t off_lse, off_o, bytes;
+};
+
+int qsa_check(const atrex_qsa_sm100_params* p) {
+  if (p == nullptr) return report_failure(ATREX_FA_INVALID_VALUE, "parameter block is NULL");
+  if (p->struct_bytes != sizeof(atrex_qsa_sm100_params) || p->abi_version != ATREX_QSA_SM100_ABI_VERSION)
+    return report_failure(ATREX_FA_ABI_MISMATCH, "struct_bytes / abi_version do not match this library");
+  if (p->rows < 0 || p->num_pages < 1 || p->batch < 1 || p->table_width < 1)
+    return report_failure(ATREX_FA_INVALID_VALUE, "rows, num_pages, batch and table_width must be positive");
+  if (p->page_size < 16 || p->page_size % 16)
+    return report_failure(ATREX_FA_INVALID_VALUE, "page size must be a positive multiple of 16");
+  if (p->num_kv_heads != 1 && p->num_kv_heads != 2)
+    return report_failure(ATREX_FA_INVALID_VALUE, "Hkv must be 1 or 2");
+  if (p->num_q_heads != 8 * p->num_kv_heads && p->num_q_heads != 12 * p->num_kv_heads)
+    return report_failure(ATREX_FA_INVALID_VALUE, "GQA ratio must be 8 or 12");
+  if (p->dtype != ATREX_FA_BF16 && p->dtype != ATREX_FA_E4M3)
+    return report_failure(ATREX_FA_UNSUPPORTED, "dtype must be BF16 or E4M3");
+  if (p->num_splits < 0 || p->num_splits > kMaxSplits)
+    return report_failure(ATREX_FA_INVALID_VALUE, "num_splits must lie in [0, 16]");
+  if (!(p->sm_scale > 0.f) || !(p->v_scale > 0.f) || p->sm_scale > 3.0e38f || p->v_scale > 3.0e38f)
+    return report_failure(ATREX_FA_INVALID_VALUE, "sm_scale and v_scale must be positive and finite");
+  if (p->rows > 0 && (!p->q || !p->k_cache || !p->v_cache || !p->block_ids || !p->query_positions ||
+                      !p->block_table || !p->token_to_req || !p->output_gate || !p->out))
+    return report_failure(ATREX_FA_INVALID_VALUE, "a tensor pointer is NULL");
+  const uint64_t es = p->dtype == ATREX_FA_E4M3 ? 1 : 2;
+  const int64_t strides[] = {p->q_row_stride, p->q_head_stride, p->kv_page_stride, p->kv_row_stride, p->kv_head_stride};
+  for (int64_t st : strides)
+    if (st < 0 || ((uint64_t)st * es) % 16) return report_failure(ATREX_FA_UNSUPPORTED, "a Q / K / V stride is not a multiple of 16 bytes");
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k_cache) |
+                         reinterpret_cast<uintptr_t>(p->v_cache) | reinterpret_cast<uintptr_t>(p->output_gate) |
+                         reinterpret_cast<uintptr_t>(p->out);
+  if (ptrs & 15u) return report_failure(ATREX_FA_UNSUPPORTED, "Q, K, V, gate and out must be 16-byte aligned");
+  return ATREX_FA_OK;
+}
+
+void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) {
+  int splits = p->num_splits;
+  if (splits == 0) {
+    // rows x KV heads CTAs; split the token list until the machine holds two CTAs per SM's worth of work
+    const long long ctas = (long long)p->rows * p->num_kv_heads;
+    const long long want = ctas > 0 ? (2LL * sm_count + ctas - 1) / ctas : 1;
+    splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
+  }
+  r->splits = splits;
+  r->launches = splits > 1 ? 2 : 1;
+  const uint64_t slots = (uint64_t)p->rows * p->num_q_heads;
+  r->off_lse = 0;
+  r->off_o = splits > 1 ? (4ull * splits * slots + 255) / 256 * 256 : 0;
+  r->bytes = splits > 1 ? r->off_o + 4ull * splits * slots * kD : 0;
+}
+
+}  // namespace
+}  // namespace atrex_sm100
+
+using namespace atrex_sm100;
+
+extern "C" {
+
+int atrex_qsa_sm100_abi_version(void) { return ATREX_QSA_SM100_ABI_VERSION; }
+size_t atrex_qsa_sm100_params_bytes(void) { return sizeof(atrex_qsa_sm100_params); }
+
+int atrex_qsa_sm100_plan(const atrex_qsa_sm100_params* p, atrex_qsa_sm100_plan_info* plan) {
+  clear_failure();
+  if (plan == nullptr) return report_failure(ATREX_FA_INVALID_VALUE, "plan is NULL");
+  int st = qsa_check(p);
+  if (st != ATREX_FA_OK) return st;
+  int sms = p->sm_count;
+  if (sms <= 0 && (st = current_sm_count(&sms)) != ATREX_FA_OK) return st;
+  QsaResolved r;
+  qsa_resolve(p, sms, &r);
+  plan->num_splits = r.splits;
+  plan->kernel_launches = r.launches;
+  plan->workspace_bytes = r.bytes;
+  return ATREX_FA_OK;
+}
+
+int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, uint64_t workspace_bytes, void* stream_ptr) {
+  clear_failure();
+  int st = qsa_check(p);
+  if (st != ATREX_FA_OK) return st;
+  int sms = 0;
+  if ((st = current_sm_count(&sms)) != ATREX_FA_OK) return st;   // also rejects devices that are not sm_100
+  if (p->sm_count > 0) sms = p->sm_count;
+  QsaResolved r;
+  qsa_resolve(p, sms, &r);
+  if (r.bytes > 0 && (workspace == nullptr || workspace_bytes < r.bytes || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
+    return report_failure(ATREX_FA_WORKSPACE_TOO_SMALL, "workspace missing, misaligned or too small");
+  if (p->rows == 0) return ATREX_FA_OK;
+  static std::atomic<int> prepared[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !prepared[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (sparse attention kernels)", e);
+    prepared[dev].store(1, std::memory_order_release);
+  }
+  QsaParams k = {};
+  k.q = p->q; k.k = p->k_cache; k.v = p->v_cache; k.ids = p->block_ids; k.pos = p->query_positions;
+  k.table = p->block_table; k.req = p->token_to_req;
+  k.gate = static_cast<const __nv_bfloat16*>(p->output_gate);
+  k.out = static_cast<__nv_bfloat16*>(p->out);
+  k.status = p->device_status;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (r.splits > 1) {
+    k.part_lse = reinterpret_cast<float*>(ws + r.off_lse);
+    k.part_o = reinterpret_cast<float*>(ws + r.off_o);
+  }
+  k.q_row_stride = p->q_row_stride; k.q_head_stride = p->q_head_stride;
+  k.kv_page_stride = p->kv_page_stride; k.kv_row_stride = p->kv_row_stride; k.kv_head_stride = p->kv_head_stride;
+  k.rows = p->rows; k.hq = p->num_q_heads; k.hkv = p->num_kv_heads; k.group = p->num_q_heads / p->num_kv_heads;
+  k.num_pages = p->num_pages; k.page_size = p->page_size; k.batch = p->batch; k.table_width = p->table_width;
+  k.pos64 = p->positions_are_int64 ? 1 : 0;
+  k.num_splits = r.splits;
+  k.scale_log2 = p->sm_scale * kLog2e;
+  k.v_scale = p->v_scale;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const dim3 grid((unsigned)((long long)p->rows * p->num_kv_heads), (unsigned)r.splits, 1);
+  cudaError_t e = p->dtype == ATREX_FA_E4M3
+                      ? launch_kernel(atrex_sm100_qsa_kernel<true>, grid, dim3(kThreads), kSmemBytes, stream, k)
+                      : launch_kernel(atrex_sm100_qsa_kernel<false>, grid, dim3(kThreads), kSmemBytes, stream, k);
+  if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention kernel", e);
+  if (r.splits > 1) {
+    const long long slots = (long long)p->rows * p->num_q_heads;
+    e = launch_kernel(atrex_sm100_qsa_combine_kernel, dim3((unsigned)((slots + 7) / 8)), dim3(256), 0, stream, k);
+    if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention combine kernel", e);
+  }
+  return ATREX_FA_OK;
+}
+
+}  // extern "C"

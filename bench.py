@@ -99,6 +99,14 @@ WORKLOADS = {
                                 variant="headsplit"),
     "decode_cp": dict(kind="decode", batch=16, q_len=1, hq=32, hkv=8, d=128, page=64, kv_lo=131072, kv_hi=131072,
                       pool=None, window=None, sink=False, lse=True, scaling="strong", variant="cp"),
+    # compact sparse attention (atrex.qsa_compact): query-length-1 decode rows that each list 512 four-token blocks
+    # of their own request's 65536-token cache (head_dim 256, 8 query heads on 1 KV head, page 128): a gather of
+    # 2 KB pieces, 2.1 MB per row in BF16; and a ragged prefill chunk of one request
+    "qsa_decode": dict(kind="qsa", rows=64, requests=64, tokens=65536, hq=8, hkv=1, page=128, fp8=False, scaling="weak"),
+    "qsa_decode_fp8": dict(kind="qsa", rows=64, requests=64, tokens=65536, hq=8, hkv=1, page=128, fp8=True,
+                           scaling="weak"),
+    "qsa_prefill": dict(kind="qsa", rows=2048, requests=1, tokens=32768, hq=8, hkv=1, page=128, fp8=False,
+                        scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
 }
@@ -112,6 +120,7 @@ KIND = {
     "decode": dict(metric="paged_decode_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
     "prefill": dict(metric="paged_prefill_tensor_throughput", unit="TFLOP/s", scale=1e12, bound="tensor"),
     "kv_write": dict(metric="kv_cache_write_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
+    "qsa": dict(metric="sparse_attention_gather_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
 }
 
 
@@ -361,6 +370,8 @@ def run_reference(args, spec, rank, world):
     kind = KIND[spec["kind"]]
     steps, warm = max(1, args.steps), max(0, args.warmup)
     per_step = max(2.0, min(20.0, 120.0 / (steps + warm)))
+    if spec["kind"] == "qsa":
+        raise SystemExit("the CPU arm of the sparse attention workloads is their cpu_baseline (run without --impl)")
     if spec["kind"] == "kv_write":
         values, sample, total_t = [], None, 0.0
         for _ in range(min(steps, 8)):
@@ -939,6 +950,189 @@ def measure_host_path(job, spec):
                     "full_validation_us = can_use_flash_attn_varlen_func alone (every check, no launch)")
 
 
+def qsa_inputs(spec, seed, device, torch):
+    """Rows of `requests` requests, each with its own paged cache of `tokens` tokens; decode rows sit at the end of
+    their request, prefill rows are the request's last `rows` positions; every row lists 512 distinct blocks drawn
+    from the blocks it can see."""
+    rows, requests, tokens, page = spec["rows"], spec["requests"], spec["tokens"], spec["page"]
+    hq, hkv = spec["hq"], spec["hkv"]
+    g = torch.Generator(device=device).manual_seed(seed)
+    width = -(-tokens // page)
+    pages = requests * width
+    dtype = torch.float8_e4m3fn if spec["fp8"] else torch.bfloat16
+    k = (torch.randn((pages, page, hkv, 256), generator=g, device=device) * 0.5).to(dtype)
+    v = torch.randn((pages, page, hkv, 256), generator=g, device=device).to(dtype)
+    q = (torch.randn((rows, hq, 256), generator=g, device=device) * 0.5).to(dtype)
+    gate = torch.randn((rows, hq, 256), generator=g, device=device).bfloat16()
+    table = torch.randperm(pages, generator=g, device=device).int().reshape(requests, width)
+    per = rows // requests
+    req = torch.arange(requests, device=device, dtype=torch.int32).repeat_interleave(per)
+    pos = (tokens - per + torch.arange(rows, device=device) % per).long()
+    rank = torch.rand((rows, (tokens + 3) // 4), generator=g, device=device)
+    rank.masked_fill_(torch.arange(rank.shape[1], device=device)[None, :] >= ((pos + 1) // 4)[:, None], 2.0)
+    ids = rank.argsort(dim=1)[:, :512].int().contiguous()
+    del rank
+    return dict(q=q, k_cache=k, v_cache=v, indexer_block_ids=ids, query_positions=pos, block_table=table,
+                token_to_req=req, use_prefill_config=per > 4, output_gate=gate,
+                out=torch.empty((rows, hq, 256), dtype=torch.bfloat16, device=device))
+
+
+def qsa_work_bytes(spec, ids, pos):
+    """Bytes of the K and V rows the rows gather (four-token blocks and the unfinished block), Q, gate and out, and
+    the index data read per row."""
+    visible = pos + 1
+    gathered = int((np.minimum(visible // 4, 512) * 4 + visible % 4).sum())
+    es = 1 if spec["fp8"] else 2
+    rows = len(pos)
+    return gathered * spec["hkv"] * 256 * 2 * es + rows * spec["hq"] * 256 * (es + 2 + 2) + rows * (512 * 4 + 12)
+
+
+def run_qsa(args, spec, rank, world, local):
+    """Compact sparse attention workloads: same JSON contract; one or two kernels per call."""
+    import torch
+    import torch.distributed as dist
+    import atrex
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+    from atrex.src.nvidia.qsa.sm100 import runtime as qsa_runtime
+
+    kind = KIND["qsa"]
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    runtime.prewarm(device)
+    data = qsa_inputs(spec, 1729 + 1000 * rank, device, torch)
+    kwargs = dict(sm_scale=256 ** -0.5 * 0.5, v_scale=1.25) if spec["fp8"] else {}
+    work = qsa_work_bytes(spec, None, data["query_positions"].cpu().numpy())
+    info = qsa_runtime.plan(qsa_runtime.build_params(
+        data["q"], data["k_cache"], data["v_cache"], data["indexer_block_ids"], data["query_positions"],
+        data["block_table"], data["token_to_req"], data["output_gate"], data["out"],
+        kwargs.get("sm_scale", 256 ** -0.5), kwargs.get("v_scale", 1.0)))
+    warmup, steps, samples = max(3, args.warmup), max(1, args.steps), max(1, args.samples)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        return atrex.qsa_compact(**data, **kwargs)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    sample_ms = []
+    for _ in range(samples):
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            step()
+        stop.record()
+        barrier()
+        sample_ms.append(start.elapsed_time(stop))
+    clocks = sampler.stop()
+    n_timed = min(steps * samples, 50)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
+    for a, b in pairs:
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    call_ms = sorted(a.elapsed_time(b) for a, b in pairs)
+    # end to end: the step's own tensors (Q, gate, block ids, positions, request ids) come from pinned host memory,
+    # the result goes back; caches and page table are resident device state
+    names = ("q", "output_gate", "indexer_block_ids", "query_positions", "token_to_req")
+    host = {n: (data[n].view(torch.uint8) if data[n].dtype == torch.float8_e4m3fn else data[n]).cpu().pin_memory()
+            for n in names}
+    dev = {n: (data[n].view(torch.uint8) if data[n].dtype == torch.float8_e4m3fn else data[n]) for n in names}
+    out_host = torch.empty(data["out"].shape, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+
+    def e2e_step():
+        for n in names:
+            dev[n].copy_(host[n], non_blocking=True)
+        out_host.copy_(step(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = []
+    for _ in range(max(3, min(samples, 5))):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        barrier()
+        e2e_ms.append((time.perf_counter() - t0) * 1e3 / steps)
+    stats = torch.tensor(sample_ms + e2e_ms, dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    sample_ms, e2e_ms = stats.tolist()[: len(sample_ms)], stats.tolist()[len(sample_ms):]
+    if rank == 0:
+        peaks = measured_peaks()
+        med = statistics.median(sample_ms)
+        call = sum(call_ms) / len(call_ms)
+        achieved = work / (call * 1e-3) / 1e9
+        line = dict(
+            metric=kind["metric"], value=work * world * steps / (med * 1e-3) / 1e9, unit="GB/s", n_gpus=world,
+            steps=steps, warmup=warmup, samples=len(sample_ms), ms_per_step=med / steps,
+            spread=dict(ms_per_step_min=min(sample_ms) / steps, ms_per_step_max=max(sample_ms) / steps),
+            higher_is_better=True, scaling="weak", vs_baseline=None, dtype="fp8_e4m3" if spec["fp8"] else "bf16",
+            data="synthetic",
+            config=dict(workload=args.workload, rows=spec["rows"], requests=spec["requests"],
+                        tokens_per_request=spec["tokens"], num_q_heads=spec["hq"], num_kv_heads=spec["hkv"],
+                        head_dim=256, page_size=spec["page"], blocks_per_row=512, num_splits=info.num_splits,
+                        sharding="one batch per rank, no collective",
+                        l2="K/V rows gathered per step (134 MB BF16) spread over a 4.3 GB cache: above the 126 MB L2"
+                        if spec["rows"] == 64 else "one request's 32 MB cache: L2-resident gather",
+                        algorithmic_work_per_step_rank0=work),
+            roofline=dict(bound="hbm", achieved=achieved, peak=peaks["hbm"], unit="GB/s", frac=achieved / peaks["hbm"],
+                          traffic=None, peak_source=peaks["source"],
+                          kernel="atrex_sm100_qsa_kernel" + (" + atrex_sm100_qsa_combine_kernel" if info.num_splits > 1 else ""),
+                          kernel_ms=call, kernel_ms_min=call_ms[0], kernel_ms_max=call_ms[-1],
+                          frac_of_nominal_8tbs=achieved / 8000.0,
+                          note="kernel_ms is the whole call (attention kernel and, when split, its combine), timed by "
+                               "one event pair per call, calls queued back to back"),
+            e2e=dict(value=work * world / (statistics.median(e2e_ms) * 1e-3) / 1e9, unit="GB/s", h2d_bytes_per_step=h2d,
+                     d2h_bytes_per_step=out_host.numel() * 2, steps=steps, samples=len(e2e_ms),
+                     note="Q, gate, block ids, positions and request ids copied from pinned host memory each step, out "
+                          "copied back; caches and page table are resident device state"),
+            gpu_launches=info.kernel_launches * steps * len(sample_ms), gpu_launches_per_step=info.kernel_launches,
+            clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"], reasons=clocks["reasons"]),
+            device_status=runtime.check_device_status(device),
+        )
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = qsa_cpu(spec, data, kwargs, work)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def qsa_cpu(spec, data, kwargs, work_all):
+    """The numpy oracle over the first rows of the step (about 10 s)."""
+    from oracle import qsa_oracle
+
+    def host(t):
+        return (t.float() if t.is_floating_point() else t).cpu().numpy()
+
+    done, rows, t_total = 0, 0, 0.0
+    k, v, table = host(data["k_cache"]), host(data["v_cache"]), host(data["block_table"])
+    while rows < spec["rows"] and t_total < 10.0:
+        sl = slice(rows, rows + 1)
+        t0 = time.perf_counter()
+        qsa_oracle.qsa_compact(host(data["q"][sl]), k, v, host(data["indexer_block_ids"][sl]),
+                               host(data["query_positions"][sl]), table, host(data["token_to_req"][sl]),
+                               host(data["output_gate"][sl]), sm_scale=kwargs.get("sm_scale"),
+                               v_scale=kwargs.get("v_scale", 1.0))
+        t_total += time.perf_counter() - t0
+        rows += 1
+    return dict(value=work_all * rows / spec["rows"] / t_total / 1e9, unit="GB/s", cores=cpu_threads(), kind="port",
+                sample=f"first {rows} of {spec['rows']} rows of the step, {t_total:.1f} s")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -965,6 +1159,9 @@ def main():
         return
     if spec["kind"] == "kv_write":
         run_kv_write(args, spec, rank, world, local)
+        return
+    if spec["kind"] == "qsa":
+        run_qsa(args, spec, rank, world, local)
         return
 
     job = Job(args)

@@ -8,7 +8,7 @@ import sys
 
 import numpy as np
 
-from oracle import fa_oracle, kv_cache_oracle
+from oracle import fa_oracle, kv_cache_oracle, qsa_oracle
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -44,6 +44,12 @@ def test_every_workload_has_work_units():
     for name, spec in b.WORKLOADS.items():
         if spec["kind"] == "kv_write":
             assert b.kv_write_bytes(spec["tokens"], spec["hkv"], spec["d"], spec["fp8"]) > 0
+            continue
+        if spec["kind"] == "qsa":
+            pos = np.array([-1, 9, 14, 4000])
+            ids = np.zeros((4, 512), np.int32)
+            assert b.qsa_work_bytes(dict(spec, fp8=False, hq=8, hkv=1), ids, pos) == \
+                qsa_oracle.algorithmic_bytes(ids, pos, 8, 1, 2)
             continue
         small = dict(spec, batch=2)
         q, kv = b.draw_lengths(small, 1)
