@@ -9,8 +9,10 @@
 //
 //   * one CTA = (row, KV head, split of the row's token list); the 8 or 12 query heads of the KV head are the
 //     rows of one 16-row MMA tile (pack-GQA: one fetch of a K/V row serves the whole group);
-//   * each of the four warps is its own pipeline: it takes every fourth 16-token tile (four blocks), resolves
-//     the sixteen tokens to cache rows (block id -> token -> page table -> address, one lane per token),
+//   * the CTA first resolves its share of the row's blocks to cache addresses (block id -> first token -> page
+//     table -> address; a four-token block never straddles a page) into shared memory: two dependent global
+//     loads once per CTA instead of once per tile on every warp's critical path;
+//   * each of the six warps is then its own pipeline: it takes every sixth 16-token tile (four blocks),
 //     fetches K and V with 16-byte cp.async copies into its private double buffer (a row is one coalesced
 //     512-byte request) and computes S = Q K^T, the online softmax (log2 domain) and O += P V with mma.sync
 //     while the next tile's copies are in flight; no block-wide barrier inside the loop;
@@ -33,14 +35,24 @@ namespace {
 constexpr int kD = ATREX_QSA_SM100_HEAD_DIM;
 constexpr int kTopk = ATREX_QSA_SM100_TOPK;
 constexpr int kTile = 16;                 // tokens per warp tile = four blocks
-constexpr int kWarps = 4;
+// Measured on B200 (64 decode rows / 2048 prefill rows, device time per call): 4 warps x 2 stages 32.0 / 510 us,
+// 4 x 3 32.2 / 548 us, 6 x 2 33.1 / 496 us (E4M3 decode 41.6 / 40.7 / 36.9 us): six warps with double buffers.
+#ifndef ATREX_QSA_WARPS
+#define ATREX_QSA_WARPS 6
+#endif
+#ifndef ATREX_QSA_STAGES
+#define ATREX_QSA_STAGES 2
+#endif
+constexpr int kWarps = ATREX_QSA_WARPS;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxSplits = 16;
 constexpr int kQBytes = 16 * kD * 2;      // Q tile: 16 rows (8 or 12 used) x 256 BF16
 constexpr int kOperandBytes = kTile * kD * 2;          // one K or V tile as BF16: 8 KB
-constexpr int kWarpBytes = 4 * kOperandBytes;          // per warp: two stages of K + V (BF16), or raw stages + one widened tile (E4M3)
-constexpr int kMetaBytes = kWarps * 2 * kTile * 8;     // per warp and stage: 16 row offsets (int64, -1 = does not count)
-constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes;
+constexpr int kStages = ATREX_QSA_STAGES;              // tiles resident per warp: one being consumed, the others in flight
+constexpr int kWarpBytes = kStages * 2 * kOperandBytes;   // per warp: kStages x (K + V) as BF16; E4M3: raw stages + one widened tile
+constexpr int kMetaBytes = kWarps * kStages * kTile * 8;  // per warp and stage: 16 row offsets (int64, -1 = does not count)
+constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of every block's first row (-1 = does not count)
+constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
 static_assert(kWarps * 16 * (kD + 2) * 4 <= kWarps * kWarpBytes, "merge buffer aliases the tile buffers");
 
 struct QsaParams {
@@ -95,6 +107,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   uint8_t* q_smem = smem;
   uint8_t* tiles = smem + kQBytes;
   long long* meta = reinterpret_cast<long long*>(smem + kQBytes + kWarps * kWarpBytes);
+  long long* block_off = meta + kWarps * kStages * kTile;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t = blockIdx.x / p.hkv, h = blockIdx.x % p.hkv;
@@ -111,8 +124,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   const int request = p.req[t];
   const bool live = visible > 0 && request >= 0 && request < p.batch;
   const int complete = live ? (int)min((long long)kTopk, visible / 4) : 0;
-  const int listed = complete * 4;
-  const int n_tok = live ? listed + (int)(visible % 4) : 0;
+  const int n_tok = live ? complete * 4 + (int)(visible % 4) : 0;
   const long long tail_start = (visible / 4) * 4;
   const int n_tiles_row = (n_tok + kTile - 1) / kTile;
   const int tile_lo = (int)(((long long)n_tiles_row * split) / p.num_splits);
@@ -140,39 +152,49 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
       *reinterpret_cast<uint4*>(q_smem + (c / 8) * (16 * 128) + swz128(r, c % 8)) = val;
     }
   }
+  // ---- this split's blocks -> element offset of their first cache row ----
+  // list block j < complete is the j-th listed block; list block `complete` is the unfinished last block
+  for (int j = tile_lo * 4 + tid; j < tile_hi * 4 && j <= complete; j += kThreads) {
+    long long tok = -1, off = -1;
+    if (j < complete) {
+      const int blk = row_ids[j];
+      if (blk >= 0) tok = (long long)blk * 4;
+    } else {
+      tok = tail_start;
+    }
+    if (tok >= 0) {
+      const long long lp = tok / p.page_size;
+      if (lp < p.table_width) {
+        const int phys = table_row[lp];
+        if (phys >= 0 && phys < p.num_pages)
+          off = (long long)phys * p.kv_page_stride + (tok - lp * p.page_size) * p.kv_row_stride +
+                (long long)h * p.kv_head_stride;
+      }
+    }
+    block_off[j - tile_lo * 4] = off;
+  }
   __syncthreads();
 
   // ---- per-warp pipeline over its tiles ----
   uint8_t* my = tiles + warp * kWarpBytes;
-  long long* my_meta = meta + warp * 2 * kTile;
+  long long* my_meta = meta + warp * kStages * kTile;
   constexpr int kEsz = kFp8 ? 1 : 2;
   constexpr int kRowBytes = kD * kEsz;                 // bytes of one cache row for one head
   constexpr int kRawOperand = kTile * kRowBytes;       // raw bytes of one K or V tile
   // BF16: stage s holds K at s * 2 * kOperandBytes, V right behind.  E4M3: raw stage s at s * 2 * kRawOperand
-  // (K then V); the widened tile (K then V) sits in the second half of the warp's region.
+  // (K then V); the widened tile (K then V) sits behind the raw stages.
+  static_assert(!kFp8 || kStages * 2 * (kTile * kD) + 2 * kOperandBytes <= kWarpBytes, "raw stages + widened tile fit");
   auto raw_k = [&](int s) { return my + s * 2 * kRawOperand; };
   auto raw_v = [&](int s) { return my + s * 2 * kRawOperand + kRawOperand; };
 
-  // resolve the 16 tokens of tile `ti` (one lane per token) and start its copies into stage s
+  // the 16 tokens of tile `ti` (one lane per token: block base + row inside the block) and its copies into stage s
   auto issue_tile = [&](int ti, int s) {
     long long off = -1;
     if (lane < kTile) {
       const int i = ti * kTile + lane;
-      long long tok = -1;
-      if (i < listed) {
-        const int blk = row_ids[i >> 2];
-        if (blk >= 0) tok = (long long)blk * 4 + (i & 3);
-      } else if (i < n_tok) {
-        tok = tail_start + (i - listed);
-      }
-      if (tok >= 0) {
-        const long long lp = tok / p.page_size;
-        if (lp < p.table_width) {
-          const int phys = table_row[lp];
-          if (phys >= 0 && phys < p.num_pages)
-            off = (long long)phys * p.kv_page_stride + (tok - lp * p.page_size) * p.kv_row_stride +
-                  (long long)h * p.kv_head_stride;
-        }
+      if (i < n_tok) {
+        const long long base = block_off[(i >> 2) - tile_lo * 4];
+        if (base >= 0) off = base + (i & 3) * p.kv_row_stride;
       }
       my_meta[s * kTile + lane] = off;
     }
@@ -216,17 +238,21 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   const uint32_t k_lane_row = mrow + (mat >> 1) * 8, k_lane_chunk = mat & 1;
   const uint32_t v_lane_row = mrow + (mat & 1) * 8, v_lane_chunk = mat >> 1;
 
+  // One copy group per tile, and an empty group where no tile is left, so that "all but the newest two groups
+  // are complete" always means "this iteration's tile has landed".
   int stage = 0;
   const int first = tile_lo + warp;
   if (first < tile_hi) issue_tile(first, 0);
+#pragma unroll
+  for (int d = 1; d < kStages - 1; ++d) {
+    if (first + d * kWarps < tile_hi) issue_tile(first + d * kWarps, d);
+    else cp_async_commit();
+  }
   for (int ti = first; ti < tile_hi; ti += kWarps) {
-    const int next = ti + kWarps;
-    if (next < tile_hi) {
-      issue_tile(next, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int ahead = ti + (kStages - 1) * kWarps;
+    if (ahead < tile_hi) issue_tile(ahead, (stage + kStages - 1) % kStages);
+    else cp_async_commit();
+    cp_async_wait<kStages - 1>();
     __syncwarp();
     // which of the tile's 16 tokens count (bit r = token r)
     const unsigned live_mask = __ballot_sync(0xffffffffu, lane < kTile && my_meta[stage * kTile + lane] >= 0) & 0xFFFFu;
@@ -234,7 +260,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     uint32_t k_addr, v_addr;
     if (kFp8) {
       // widen the raw tile into the BF16 tile (second half of the warp's region), swizzled for the MMA
-      uint8_t* wide_k = my + 2 * kOperandBytes;
+      uint8_t* wide_k = my + kStages * 2 * kRawOperand;
       uint8_t* wide_v = wide_k + kOperandBytes;
 #pragma unroll
       for (int j = 0; j < kTile / 2; ++j) {
@@ -256,18 +282,28 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     }
 
     // ---- S = Q K^T : 16 rows x 16 tokens ----
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // four independent accumulator pairs (one per 64-element block of the head dimension) instead of one chain
+    // of sixteen dependent MMAs: a warp is alone on its scheduler here, so only instruction-level parallelism
+    // hides the MMA latency
+    float s4[kD / 64][2][4];
 #pragma unroll
     for (int kb = 0; kb < kD / 64; ++kb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s4[kb][0][e] = s4[kb][1][e] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         uint32_t a[4], b0, b1, b2, b3;
         ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + kb * (16 * 128) + swz128(q_lane_row, ks * 2 + q_lane_chunk));
         ldmatrix_x4(b0, b1, b2, b3, k_addr + kb * (kTile * 128) + swz128(k_lane_row, ks * 2 + k_lane_chunk));
-        mma_bf16_16816(s[0], a, b0, b1);
-        mma_bf16_16816(s[1], a, b2, b3);
+        mma_bf16_16816(s4[kb][0], a, b0, b1);
+        mma_bf16_16816(s4[kb][1], a, b2, b3);
       }
     }
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = (s4[0][j][e] + s4[1][j][e]) + (s4[2][j][e] + s4[3][j][e]);
     // ---- scale, hide the tokens that do not count, online softmax (log2 domain) ----
     float alpha[2];
 #pragma unroll
@@ -321,7 +357,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
       }
     }
     __syncwarp();          // every lane is done with this stage before the next iteration's copies may land in it
-    stage ^= 1;
+    stage = (stage + 1) % kStages;
   }
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
@@ -471,9 +507,10 @@ int qsa_check(const atrex_qsa_sm100_params* p) {
 void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) {
   int splits = p->num_splits;
   if (splits == 0) {
-    // rows x KV heads CTAs; split the token list until the machine holds two CTAs per SM's worth of work
+    // rows x KV heads CTAs, one resident per SM: split the token lists while all CTAs still run in ONE wave
+    // (measured on 64 decode rows: 2 splits = 128 CTAs 37 us, 3 splits = 192 CTAs in two waves 46 us)
     const long long ctas = (long long)p->rows * p->num_kv_heads;
-    const long long want = ctas > 0 ? (2LL * sm_count + ctas - 1) / ctas : 1;
+    const long long want = ctas > 0 ? sm_count / ctas : 1;
     splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
   }
   r->splits = splits;

@@ -137,6 +137,7 @@ def test_launcher_checks_the_block_and_plans_from_static_sizes():
 
     few, many = runtime.plan(block(8)), runtime.plan(block(4096))
     assert few.num_splits == 16 and few.kernel_launches == 2 and few.workspace_bytes >= 16 * 8 * 8 * 257 * 4
+    assert runtime.plan(block(64)).num_splits == 2 and runtime.plan(block(100)).num_splits == 1
     assert many.num_splits == 1 and many.kernel_launches == 1 and many.workspace_bytes == 0
     assert runtime.plan(block(8, num_splits=3)).num_splits == 3
     for over, exc, match in ((dict(page_size=24), ValueError, "multiple of 16"), (dict(num_kv_heads=3), ValueError, "Hkv"),
