@@ -30,6 +30,8 @@ atrex_sm100_combine_kernel(const __grid_constant__ FwdParams p) {
   if (row_id >= live_rows) return;
   const int head = (int)(row_id % p.num_q_heads);
   const int64_t q_row = row_id / p.num_q_heads;
+  // tail split: the rows of the requests before tail_first were written in final form by the attention kernel
+  if (p.tail_splits > 1 && q_row < p.cu_seqlens_q[p.tail_first]) return;
   const int64_t split_stride = (int64_t)p.total_q * p.num_q_heads;
 
   float mx = -INFINITY;

@@ -67,6 +67,12 @@ struct alignas(64) FwdParams {
   int32_t kv_cap;         // paged: block_table width x page_size, the most keys a request's table row can name
   int32_t cp_world_size;  // context-parallel ranks (1 = off): local key j is the request's key j * world + rank
   int32_t cp_rank;
+  // Tail split of the single-tile tcgen05 kernel's decode path (0 / 1 = off): the items of requests
+  // [tail_first, batch) are cut into tail_splits KV splits each, all earlier items run unsplit.  With equal items
+  // on a persistent grid the last round is otherwise only partly filled (512 items on 148 CTAs: 4 rounds for 3.46
+  // rounds of work); splitting just the last round's items fills it, and only their rows go through the combine.
+  int32_t tail_first;
+  int32_t tail_splits;
   float softmax_scale;
   float softcap;
   // position (1..3, minus 1) of the head / row / page coordinate in each tensor map

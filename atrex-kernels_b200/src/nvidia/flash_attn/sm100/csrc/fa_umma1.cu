@@ -80,7 +80,7 @@ __device__ long long g_umma1_trace[8192];
 enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
 
 struct Item256 {
-  int b, kvh, split, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
+  int b, kvh, split, n_splits, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
 };
 
 // Work item `item` -> (row tile, KV head, KV split), split fastest.  Row tiles come from the device-side plan
@@ -88,8 +88,25 @@ struct Item256 {
 // row tile, are simply the requests.  False when past the end.
 template <int BN>
 __device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Item256& it) {
-  it.split = item % p.num_splits;
-  const int rest = item / p.num_splits;
+  int rest;
+  if (p.tail_splits > 1) {
+    // unsplit items of the first requests, then tail_splits items per (request, KV head) of the last ones
+    const int n_unsplit = p.tail_first * p.num_kv_heads;
+    if (item < n_unsplit) {
+      rest = item;
+      it.split = 0;
+      it.n_splits = 1;
+    } else {
+      const int j = item - n_unsplit;
+      it.split = j % p.tail_splits;
+      rest = n_unsplit + j / p.tail_splits;
+      it.n_splits = p.tail_splits;
+    }
+  } else {
+    it.split = item % p.num_splits;
+    rest = item / p.num_splits;
+    it.n_splits = p.num_splits;
+  }
   it.kvh = rest % p.num_kv_heads;
   const int tile_rank = rest / p.num_kv_heads;
   if (p.order == nullptr) {
@@ -122,8 +139,8 @@ __device__ __forceinline__ bool decode_item256(const FwdParams& p, int item, Ite
   if (p.window_left >= 0) kv_begin = max(0, qi_lo + it.off - p.window_left);
   if (kv_end > kv_begin) {
     const int t0 = kv_begin / BN, n = (kv_end + BN - 1) / BN - t0;
-    const int lo_t = (int)(((long long)n * it.split) / p.num_splits);
-    const int hi_t = (int)(((long long)n * (it.split + 1)) / p.num_splits);
+    const int lo_t = (int)(((long long)n * it.split) / it.n_splits);
+    const int hi_t = (int)(((long long)n * (it.split + 1)) / it.n_splits);
     it.tile_lo = t0 + lo_t;
     it.n_tiles = hi_t - lo_t;
   }
@@ -583,7 +600,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         break;
       }
       const float l_row = l_run + slot[(h ^ 1) * kRows + r];
-      const bool split_mode = p.num_splits > 1;   // the combine kernel adds the sink and converts to BF16
+      const bool split_mode = it.n_splits > 1;    // the combine kernel adds the sink and converts to BF16
       float sink_l2 = -INFINITY;
       if (p.sink != nullptr && !split_mode && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
       const float m_f = fmaxf(m_run, sink_l2);
@@ -673,7 +690,9 @@ cudaError_t umma1_prepare() {
 }
 
 cudaError_t umma1_launch(const FwdParams& p, int head_dim, bool fp8, int sm_count, cudaStream_t stream) {
-  const long long items = (long long)p.num_row_tiles * p.num_kv_heads * p.num_splits;
+  long long items = (long long)p.num_row_tiles * p.num_kv_heads * p.num_splits;
+  if (p.tail_splits > 1)
+    items = (long long)p.num_kv_heads * (p.tail_first + (long long)(p.batch - p.tail_first) * p.tail_splits);
   const unsigned grid = (unsigned)(items < sm_count ? (items < 1 ? 1 : items) : sm_count);
 #define X(D, F)                                                                                            \
   if (head_dim == D && fp8 == F)                                                                           \

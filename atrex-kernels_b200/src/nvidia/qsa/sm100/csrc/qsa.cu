@@ -365,7 +365,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
   }
 
-  // ---- merge the four warps' states through shared memory (aliases the tile buffers) ----
+  // ---- merge the warps' states through shared memory (aliases the tile buffers) ----
   __syncthreads();
   float* red_o = reinterpret_cast<float*>(tiles);           // [warp][16][256]
   float* red_m = red_o + kWarps * 16 * kD;                  // [warp][16]

@@ -491,3 +491,28 @@ def test_repeated_layouts_reuse_the_filled_block_but_never_addresses(as_b200, mo
     c["block_table"] = torch.zeros(2, 8, dtype=torch.int32)
     atrex.flash_attn_varlen_func(**c, num_splits=1, out=out_a)
     assert len(plans) == 2
+
+
+def test_tail_split_plan_of_the_speculative_decode_shape():
+    """One work item per (request, KV head) on a persistent grid: 128 requests x 4 KV heads = 512 items on 148 SMs
+    would run 4 rounds for 3.46 rounds of work; the planner cuts the last 68 items (17 requests) in two, so the
+    call needs scratch and a combine launch, and a batch that fills its rounds does not."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    def spec(batch):
+        q = torch.zeros(4 * batch, 64, 128, dtype=torch.bfloat16)
+        k = torch.zeros(4, 128, 4, 128, dtype=torch.bfloat16)
+        cu = torch.arange(0, 4 * batch + 1, 4, dtype=torch.int32)
+        p = runtime.build_params(q, k, k, torch.empty_like(q), None, cu, None, torch.zeros(batch, dtype=torch.int32),
+                                 torch.zeros(batch, 256, dtype=torch.int32), None, None, None, None, None, 4, 32768,
+                                 0.1, 0.0, True, 4095, 0, 0, 0)
+        p.sm_count = 148
+        return runtime.plan(p)
+
+    tail = spec(128)
+    assert tail.route == runtime.ROUTE_UMMA and tail.num_splits == 2 and tail.kernel_launches == 2
+    assert tail.workspace_bytes >= 2 * 512 * 64 * 129 * 4
+    full = spec(74)                                     # 296 items: exactly two rounds
+    assert full.num_splits == 1 and full.kernel_launches == 1 and full.workspace_bytes == 0
+    assert spec(80).num_splits == 4                     # 320 items: the last 24 (6 requests) cut in four (the cap)
+    assert spec(37).num_splits == 2                     # fewer than two rounds of items: every item is split

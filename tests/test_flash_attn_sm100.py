@@ -811,3 +811,16 @@ def test_a_bounded_wait_that_expires_reports_and_returns():
     assert runtime.check_device_status(device) == 0
     assert fn(word.data_ptr(), None, 256, stream) == 1          # a result pointer is required
     T.check(T.make_case(64, [1, 2], [300, 70], hq=8, hkv=2))
+
+
+def test_tail_split_of_the_last_round():
+    """80 requests x 4 KV heads = 320 work items on a 148-SM persistent grid: the planner cuts the last round's items
+    (6 requests, 24 items) into four KV splits and only their rows go through the combine; rows before and inside
+    the tail, with a window, sinks and LSE, against the oracle; scratch poisoned beforehand."""
+    kv = [700 + 17 * i for i in range(80)]
+    case = T.make_case(128, [4] * 79 + [3], kv, hq=64, hkv=4, spare_pages=2, seed=31)
+    sink = torch.randn(64, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    poison = torch.full((64 << 20,), 0xFF, dtype=torch.uint8, device="cuda")
+    del poison
+    T.check(case, requests=[0, 40, 73, 74, 75, 79], window_size=(511, 0), s_aux=sink)
+    T.check(case, requests=[0, 73, 74, 79])
