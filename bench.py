@@ -105,6 +105,8 @@ WORKLOADS = {
     "qsa_decode": dict(kind="qsa", rows=64, requests=64, tokens=65536, hq=8, hkv=1, page=128, fp8=False, scaling="weak"),
     "qsa_decode_fp8": dict(kind="qsa", rows=64, requests=64, tokens=65536, hq=8, hkv=1, page=128, fp8=True,
                            scaling="weak"),
+    "qsa_decode_small": dict(kind="qsa", rows=16, requests=16, tokens=65536, hq=8, hkv=1, page=128, fp8=False,
+                             scaling="weak"),   # the case profiler captures run on (1.1 GB of cache)
     "qsa_prefill": dict(kind="qsa", rows=2048, requests=1, tokens=32768, hq=8, hkv=1, page=128, fp8=False,
                         scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
@@ -114,7 +116,11 @@ WORKLOADS = {
 # (dram__bytes_read.sum + dram__bytes_write.sum on the small case of the same kernel; traffic grows in proportion
 # to the K/V bytes a launch reads, so the ratio carries to the full-size launch).
 NCU_TRAFFIC_RATIO = {"kv_write": 1.0, "kv_write_small": 1.0, "kv_write_fp8": 1.0,
-                     "decode_q1": 1.0241, "decode_q1_small": 1.0241, "decode_q4_window": 1.0588, "decode_q4_small": 1.0588}
+                     "decode_q1": 1.0250, "decode_q1_small": 1.0250, "decode_q4_window": 1.0553, "decode_q4_small": 1.0553,
+                     "qsa_decode": 1.0, "qsa_decode_small": 1.0}
+# The tensor-bound BF16 prefill kernel: DRAM bytes per byte of (Q + O + K + V), from the captures of prefill_small
+# (0.963) and of two 32768-token requests (0.988); K/V re-reads are served by L2.
+NCU_PREFILL_IO_RATIO = {"prefill_small": 0.963, "prefill_long2": 0.988, "prefill_hd128": 0.988, "prefill_sharded": 0.988}
 E2E_MAX_BYTES = 8 << 30   # largest Q the end-to-end leg stages in pinned host memory
 KIND = {
     "decode": dict(metric="paged_decode_hbm_bandwidth", unit="GB/s", scale=1e9, bound="hbm"),
@@ -716,7 +722,7 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
     elif variant == "cp":
         sharding_note += "; exchange = two NCCL all-gathers, then the merge kernel"
 
-    def step():
+    def step(case=case):
         if exchange is not None:
             case["out"] = exchange.out_buffer(case["q"].shape[0])
             result = atrex.flash_attn_varlen_func(**case)
@@ -799,17 +805,29 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
 
     # ---------------- end to end: host inputs in, host result out ----------------
     skip_e2e = case["q"].numel() * case["q"].element_size() > E2E_MAX_BYTES
-    dev_in = {key: case[key] for key in host}
+    # The step's inputs travel as ONE pinned buffer and one copy (each at a 256-byte aligned offset), the way a
+    # serving loop stages its per-step tensors; the call reads views of the device copy.
+    offsets, cursor = {}, 0
+    for key, src in host.items():
+        offsets[key] = cursor
+        cursor += (src.numel() * src.element_size() + 255) // 256 * 256
+    staged_host = torch.empty(max(cursor, 1), dtype=torch.uint8).pin_memory()
+    staged_dev = torch.empty(max(cursor, 1), dtype=torch.uint8, device=device)
+    e2e_case = dict(case)
+    for key, src in host.items():
+        nbytes = src.numel() * src.element_size()
+        staged_host[offsets[key]: offsets[key] + nbytes].copy_(src.contiguous().view(torch.uint8).reshape(-1))
+        if not skip_e2e or key != "q":
+            e2e_case[key] = staged_dev[offsets[key]: offsets[key] + nbytes].view(src.dtype).view(src.shape)
     out_shape = (1,) if skip_e2e else ((case["q"].shape[0], spec["hq"], spec["d"]) if variant == "headsplit"
                                        else tuple(case["out"].shape))
     out_host = torch.empty(out_shape, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    h2d = staged_host.numel()
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step(sync=True):
-        for key, src in host.items():
-            dev_in[key].copy_(src, non_blocking=True)
-        out_host.copy_(step(), non_blocking=True)
+        staged_dev.copy_(staged_host, non_blocking=True)
+        out_host.copy_(step(e2e_case), non_blocking=True)
         if sync:
             torch.cuda.current_stream().synchronize()
 
@@ -857,8 +875,12 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
     if info.route == runtime.ROUTE_UMMA:
         kernel_name = "atrex_sm100_fwd_umma_kernel" if info.m_rows == 256 else "atrex_sm100_fwd_umma1_kernel"
     ratio = NCU_TRAFFIC_RATIO.get(name)
+    traffic = None if ratio is None else ratio * my_work
+    if name in NCU_PREFILL_IO_RATIO:      # Q read, O written, K and V read once (BF16)
+        io_bytes = 2 * (2 * sum(q_lens) * spec["hq"] + 2 * sum(case_kv) * spec["hkv"]) * spec["d"]
+        traffic, ratio = NCU_PREFILL_IO_RATIO[name] * io_bytes, NCU_PREFILL_IO_RATIO[name]
     roofline = dict(bound=kind["bound"], achieved=achieved, peak=peak, unit=kind["unit"], frac=achieved / peak,
-                    traffic=None if ratio is None else ratio * my_work, peak_source=peaks["source"],
+                    traffic=traffic, peak_source=peaks["source"],
                     kernel=kernel_name, kernel_ms=kernel_ms_avg, kernel_ms_min=kernel_ms[0],
                     kernel_ms_max=kernel_ms[-1], kernel_launches_timed=len(kernel_ms))
     if ratio is not None:
@@ -906,9 +928,10 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
                  value_max=None if skip_e2e else total / (min(e2e_sample_ms) * 1e-3) / kind["scale"],
                  pipelined_value=None if skip_e2e else total / (e2e_pipelined_ms * 1e-3) / kind["scale"],
                  skipped="Q exceeds the pinned staging limit of this benchmark" if skip_e2e else None,
-                 note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory, "
-                      "O copied back; the paged KV cache is resident device state; `value` waits for every step's "
-                      "result before issuing the next, `pipelined_value` queues the same steps and waits once"),
+                 note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory as one "
+                      "staged buffer, O copied back; the paged KV cache is resident device state; `value` waits for "
+                      "every step's result before issuing the next, `pipelined_value` queues the same steps and "
+                      "waits once"),
         gpu_launches=per_step * steps * len(sample_ms), gpu_launches_per_step=per_step,
         clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"], reasons=clocks["reasons"]),
         device_status=status,
@@ -1106,10 +1129,11 @@ def run_qsa(args, spec, rank, world, local):
                         head_dim=256, page_size=spec["page"], blocks_per_row=512, num_splits=info.num_splits,
                         sharding="one batch per rank, no collective",
                         l2="K/V rows gathered per step (134 MB BF16) spread over a 4.3 GB cache: above the 126 MB L2"
-                        if spec["rows"] == 64 else "one request's 32 MB cache: L2-resident gather",
+                        if spec["requests"] > 1 else "one request's 32 MB cache: L2-resident gather",
                         algorithmic_work_per_step_rank0=work),
             roofline=dict(bound="hbm", achieved=achieved, peak=peaks["hbm"], unit="GB/s", frac=achieved / peaks["hbm"],
-                          traffic=None, peak_source=peaks["source"],
+                          traffic=None if args.workload not in NCU_TRAFFIC_RATIO else NCU_TRAFFIC_RATIO[args.workload] * work,
+                          peak_source=peaks["source"],
                           kernel="atrex_sm100_qsa_kernel" + (" + atrex_sm100_qsa_combine_kernel" if info.num_splits > 1 else ""),
                           kernel_ms=call, kernel_ms_min=call_ms[0], kernel_ms_max=call_ms[-1],
                           frac_of_nominal_8tbs=achieved / 8000.0,
