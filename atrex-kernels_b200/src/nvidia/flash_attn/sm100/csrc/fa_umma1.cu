@@ -485,7 +485,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     bool dead = false;
     for (int item = blockIdx.x; !dead; item += step, ++it_count) {
       Item256 it;
+      if (tid == 0) TRACE1(20, it_count);
       if (!decode_item256<BN>(p, item, it)) break;
+      if (tid == 0) TRACE1(22, it_count);
       if (group_barrier_or(kGroupBar, kGroup, *(volatile int*)abort_flag != 0)) break;   // leave together
       if (tid == 0) TRACE1(12, it_count);
       const int row = it.row0 + r;
@@ -526,12 +528,14 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
 
       float m_run = -INFINITY, l_run = 0.f;   // l_run: this thread's half of the row sum, in units of 2^kShift
       for (int j = 0; j < it.n_tiles; ++j) {
+        if (tid == 0) TRACE1(17, tt);
         const int buf = j & 1;
         const uint32_t s_tmem = tmem_base + lane_off + buf * BN + h * N;   // own scores; P goes over them
         const int tok0 = (it.tile_lo + j) * BN;
         const bool need_mask = tok0 < full_lo || tok0 + BN > full_hi;
         if (tid == 0) TRACE1(16, tt);
         if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) dead = true;
+        if (tid == 0) TRACE1(18, tt);
         ++cs[buf];
         tcgen05_fence_after();
         if (tid == 0) TRACE1(0, tt);
@@ -589,6 +593,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++co;
         tcgen05_fence_after();
       }
+      if (tid == 0) TRACE1(21, it_count);
       // ---- epilogue: row sum = both halves; each thread normalises and stores its half of the O columns ----
       float* slot = xchg + (cx & 1u) * (2 * kRows);
       ++cx;
