@@ -468,10 +468,13 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
     const uint32_t s_tmem = tmem_base + lane_off + w * kBN;
     const uint32_t o_tmem = tmem_base + lane_off + 2 * kBN + w * kHD;
     uint32_t cs = 0, co = 0;
+    [[maybe_unused]] uint32_t itc = 0;   // items so far (trace index)
     bool dead = false;
     for (int item = blockIdx.x; !dead; item += n_items_step) {
       Item it;
+      if (tid == 0) TRACE(30, itc);
       if (!decode_item(p, item, it)) break;
+      if (tid == 0) TRACE(31, itc);
       if (*(volatile int*)abort_flag) break;
       const int sub_row0 = it.row0 + w * kBM;
       const int row = sub_row0 + r;
@@ -506,9 +509,10 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
                                       : tile_max<false>(s_tmem, s, scale_log2, tok0, vis_lo, vis_hi, m_run);
         if (j > 0) {
           // O(j-1) must be complete before it is rescaled, and rescaled before the first part of P V(j) adds to it.
-          if (!mbar_wait(&bars[kOFull + w], co & 1u)) { dead = true; break; }
+          // It is: the issuer issues Q K^T(j) of this subtile after its P V(j-1), and the commit behind S(j), waited
+          // for above, covers every earlier MMA.  So this phase of the O barrier is only counted, not waited for
+          // (a satisfied wait and its fence cost ~170 cycles per tile).
           ++co;
-          tcgen05_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
             // narrow chunks: the tile's 128 scores stay in registers across this rare step
 #pragma unroll
@@ -554,6 +558,7 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
         break;
       }
       // ---- epilogue: O from TMEM, normalise, store BF16 row and natural-log LSE ----
+      if (tid == 0) TRACE(27, itc);
       float sink_l2 = -INFINITY;
       if (p.sink != nullptr && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
       const float m_f = fmaxf(m_run, sink_l2);
@@ -565,6 +570,10 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
       const int64_t q_row = it.q_start + row / p.group;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
                            (int64_t)hd * p.out_head_stride;
+      // Rows on 32-byte boundaries: one full sector per store (the epilogue is bound by the number of cache lines
+      // its stores touch, since every lane writes another row).
+      const bool out_vec32 = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (p.out_row_stride & 15) == 0 &&
+                             (p.out_head_stride & 15) == 0;
 #pragma unroll
       for (int c = 0; c < kHD / 32; ++c) {
         uint32_t v[32];
@@ -575,22 +584,14 @@ atrex_sm100_fwd_umma_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
-        if (row < it.rows_total) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-            pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-            pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
-          }
-        }
+        if (row < it.rows_total) store_bf16_row32(dst + c * 32, v, inv, out_vec32);
       }
       if (row < it.rows_total && p.lse != nullptr)
         p.lse[(int64_t)hd * p.total_q + q_row] = l > 0.f ? (m_use + log2f(l)) * kLn2 : -INFINITY;
       // the next item's first P V overwrites O only after this warp's next P arrival, i.e. after these loads
       tcgen05_fence_before();
+      if (tid == 0) TRACE(29, itc);
+      ++itc;
     }
   }
 

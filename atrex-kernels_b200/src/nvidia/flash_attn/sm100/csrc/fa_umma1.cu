@@ -17,8 +17,8 @@
 //     of the O columns, exchanging their partial row maximum through shared memory (two warps per
 //     scheduler keep the MUFU pipe busy where one cannot);
 //   * warps 9 and 10 are the K (+Q) and V TMA producers over a 4-slot ring of 32 KB tiles; every CTA
-//     loads its own copy; Q comes by TMA when the GQA group divides 128, otherwise the two threads of a
-//     row copy half of it each into the swizzled tile;
+//     loads its own copy; Q comes by TMA when the GQA group divides 128, otherwise warp 11 copies the rows
+//     into the swizzled tile, one item ahead; warp 11 also resolves the next work item for the softmax warps;
 //   * FP8: q_descale * k_descale ride in the softmax scale, P is written as E4M3 shifted up by 2^4
 //     with a lazy-rescale threshold of 2^4 (P <= 256 < 448, prefill_cutedsl.py:2577-2593), V stays
 //     MN-major E4M3 in shared memory, v_descale is applied in the epilogue;
@@ -41,7 +41,7 @@ constexpr int kRing = 4;            // K/V ring slots of 32 KB
 #endif
 constexpr int kPolyOf8_1 = ATREX_UMMA1_POLY_OF8;   // pairs of every 8 whose exponential runs on the FMA pipe
 constexpr int kSoftmaxWarps1 = 8;                 // two threads per row: 2 x 4 warps
-constexpr int kMmaWarp1 = 8, kKWarp1 = 9, kVWarp1 = 10;   // warp 11 idles
+constexpr int kMmaWarp1 = 8, kKWarp1 = 9, kVWarp1 = 10, kQWarp1 = 11;   // warp 11 copies Q where TMA cannot
 constexpr int kThreads1 = (kSoftmaxWarps1 + 4) * 32;       // 384 threads, up to 168 registers each
 
 template <int D, bool kFp8>
@@ -63,7 +63,8 @@ struct Cfg1 {
   static constexpr int kOffKV = kQBytes;
   static constexpr int kOffBar = kOffKV + kRing * kSlotBytes;
   static constexpr int kOffXchg = kOffBar + 256;              // [parity][half][row] floats for the row max / sum
-  static constexpr int kSmemBytes = kOffXchg + 2 * 2 * kRows * 4;
+  static constexpr int kOffItem = kOffXchg + 2 * 2 * kRows * 4;   // two ItemSlot
+  static constexpr int kSmemBytes = kOffItem + 2 * 64;
   static constexpr uint32_t kFmt = kFp8 ? 0u : 1u;            // E4M3 (f8f6f4) / BF16 (f16)
   static_assert(2 * kBN + D <= 512, "S0 | S1 | O must fit the 512 TMEM columns");
   static_assert(kBN / 2 >= 32, "each softmax thread takes at least one 32-column chunk");
@@ -77,11 +78,20 @@ __device__ long long g_umma1_trace[8192];
 #define TRACE1(slot, idx) do { } while (0)
 #endif
 
-enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bCount = 15 };
+enum Bar256 { bQFull = 0, bQEmpty = 1, bKVFull = 2, bKVEmpty = 6, bSFull = 10, bPFull = 12, bOFull = 14, bOFinal = 15,
+              bItemFull = 16, bItemEmpty = 18, bCount = 20 };
 
 struct Item256 {
   int b, kvh, split, n_splits, row0, q_start, q_len, rows_total, kv_len, k_start, off, tile_lo, n_tiles;
 };
+// What warp 11 resolves one item ahead for the softmax warps (two slots in shared memory): the item, whether there
+// is one, and the request's scales.
+struct __align__(16) ItemSlot {
+  Item256 it;
+  int valid;
+  float scale_log2, dv;
+};
+static_assert(sizeof(ItemSlot) == 64, "four 16-byte vectors");
 
 // Work item `item` -> (row tile, KV head, KV split), split fastest.  Row tiles come from the device-side plan
 // (heaviest request first, last row tile of a request first) or, when a request cannot have more than one
@@ -296,7 +306,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
   }
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(&bars[bQFull], p.q_via_tma ? 1 : 2 * kRows);
+    mbar_init(&bars[bQFull], 1);   // the K warp's TMA transaction, or lane 0 of the Q-copying warp
     mbar_init(&bars[bQEmpty], 1);
     for (int s = 0; s < kRing; ++s) {
       mbar_init(&bars[bKVFull + s], 1);
@@ -307,6 +317,11 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       mbar_init(&bars[bPFull + b], 2 * kRows);
     }
     mbar_init(&bars[bOFull], 1);
+    mbar_init(&bars[bOFinal], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[bItemFull + s], 1);
+      mbar_init(&bars[bItemEmpty + s], kSoftmaxWarps1);
+    }
     fence_barrier_init();
   }
   if (warp == kMmaWarp1) {
@@ -362,6 +377,82 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       for (uint32_t back = 2; back <= (uint32_t)kRing && back <= seq; back += 2) {
         const uint32_t n = seq - back;
         mbar_wait(&bars[bKVFull + n % kRing], (n / kRing) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kQWarp1) {
+    // ------------------------------- item steward -------------------------------
+    // One item ahead of the softmax warps this warp (a) resolves the item (request lookup, lengths, scales: seven
+    // or eight dependent global loads, ~2 000 cycles that the 256 softmax threads used to spend at every item
+    // boundary) into one of two shared-memory slots, and (b) when the GQA group does not tile the 128 rows as one
+    // TMA box, copies the item's Q rows into the swizzled tile with asynchronous 16-byte copies (zeros past the
+    // request's rows): the tile is free from the previous item's last S = Q K^T on, so the copy runs under that
+    // item's last tiles and epilogue.
+    constexpr int kChunksRow = C::kNKB * 8;          // 16-byte chunks per row
+    static_assert(kChunksRow <= 32 && 32 % kChunksRow == 0, "a warp-wide copy covers whole rows");
+    constexpr int kRpi = 32 / kChunksRow;            // rows per warp-wide copy
+    const int sub = lane / kChunksRow, chunk = lane % kChunksRow;
+    const uint8_t* q_base = reinterpret_cast<const uint8_t*>(p.q) + chunk * 16;
+    uint8_t* dst0 = q_smem + (chunk >> 3) * C::kQBlock;
+    ItemSlot* slots = reinterpret_cast<ItemSlot*>(smem + C::kOffItem);
+    uint32_t n = 0;
+    for (int item = blockIdx.x;; item += step, ++n) {
+      ItemSlot* slot = slots + (n & 1u);
+      // the softmax warps must have read what the slot held (item n - 2)
+      if (n >= 2 && !mbar_wait(&bars[bItemEmpty + (n & 1u)], ((n >> 1) - 1u) & 1u)) {
+        if (lane == 0) {
+          if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
+          atomicExch(abort_flag, 1);
+        }
+        break;
+      }
+      if (lane == 0) {
+        // resolved straight into the slot: no private copy of the item in this warp's registers
+        const bool ok = decode_item256<BN>(p, item, slot->it) && *(volatile int*)abort_flag == 0;
+        float dq = 1.f, dk = 1.f, dvs = 1.f;
+        if (ok) {
+          const int b = slot->it.b, kvh = slot->it.kvh;
+          if (p.q_descale) dq = p.q_descale[b * p.q_descale_bs + kvh * p.q_descale_hs];
+          if (p.k_descale) dk = p.k_descale[b * p.k_descale_bs + kvh * p.k_descale_hs];
+          if (p.v_descale) dvs = p.v_descale[b * p.v_descale_bs + kvh * p.v_descale_hs];
+        }
+        slot->valid = ok ? 1 : 0;
+        slot->scale_log2 = p.softmax_scale * dq * dk * kLog2e;   // > 0 on this route
+        slot->dv = dvs;
+        mbar_arrive(&bars[bItemFull + (n & 1u)]);                 // release: the slot is written before the arrival
+      }
+      __syncwarp();
+      const Item256 it = slot->it;                              // all lanes, for the copy below
+      if (!slot->valid) break;
+      if (!p.q_via_tma) {
+        if (n > 0 && !mbar_wait(&bars[bQEmpty], (n - 1u) & 1u)) {
+          if (lane == 0) {
+            if (p.status) atomicExch(p.status, kWaitEmptyTimeout);
+            atomicExch(abort_flag, 1);
+          }
+          break;
+        }
+        // (query position, head inside the group) of this lane's row advance by kRpi rows per copy: no division
+        // per chunk (with one, this copy was slower than the tiles it is meant to hide under)
+        int row = it.row0 + sub;
+        int pos = row / p.group, head = row - pos * p.group;
+#pragma unroll 4
+        for (int k = 0; k < kRows / kRpi; ++k) {
+          const uint8_t* src = q_base + ((int64_t)(it.q_start + pos) * p.q_row_stride +
+                                         (int64_t)(it.kvh * p.group + head) * p.q_head_stride) * C::kEsz;
+          const bool valid = row < it.rows_total;
+          cp_async_16(dst0 + swz128(k * kRpi + sub, chunk & 7), valid ? src : q_base, valid);
+          row += kRpi;
+          head += kRpi;
+          while (head >= p.group) {
+            head -= p.group;
+            ++pos;
+          }
+        }
+        cp_async_wait_all();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[bQFull]);
       }
     }
     __syncwarp();
@@ -457,6 +548,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
               umma_ts_f16_lead(lead, tmem_base + o_col, tmem_base + pcol, vd + voff, kIdescPV, (j > 0) | (ks > 0));
           }
           umma_commit_lead(lead, &bars[bOFull]);
+          if (j + 1 == it.n_tiles) umma_commit_lead(lead, &bars[bOFinal]);   // one phase per item: O is final
           umma_commit_lead(lead, &bars[bKVEmpty + slot_v]);
           if (lane == 0) TRACE1(11, tt);
         }
@@ -480,52 +572,45 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     const uint32_t o_tmem = tmem_base + lane_off + o_col + h * (D / 2);   // this thread's half of the O columns
     float* xchg = reinterpret_cast<float*>(smem + C::kOffXchg);            // [parity][half][row]
     constexpr int kGroupBar = 1, kGroup = kSoftmaxWarps1 * 32;
-    uint32_t cs[2] = {0, 0}, co = 0, it_count = 0, cx = 0;
+    uint32_t cs[2] = {0, 0}, co = 0, cf = 0, it_count = 0, cx = 0;
     [[maybe_unused]] uint32_t tt = 0;   // tiles so far (trace index)
     bool dead = false;
-    for (int item = blockIdx.x; !dead; item += step, ++it_count) {
-      Item256 it;
+    const ItemSlot* slots = reinterpret_cast<const ItemSlot*>(smem + C::kOffItem);
+    for (; !dead; ++it_count) {
       if (tid == 0) TRACE1(20, it_count);
-      if (!decode_item256<BN>(p, item, it)) break;
+      // the item was resolved by warp 11 while the previous one was being worked on
+      const ItemSlot* item_slot = slots + (it_count & 1u);
+      const bool got = mbar_wait(&bars[bItemFull + (it_count & 1u)], (it_count >> 1) & 1u);
+      Item256 it;
+      bool valid = false;
+      float scale_log2 = 0.f, dv = 1.f;
+      if (got) {
+        it = item_slot->it;
+        valid = item_slot->valid != 0;
+        scale_log2 = item_slot->scale_log2;
+        dv = item_slot->dv;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[bItemEmpty + (it_count & 1u)]);
       if (tid == 0) TRACE1(22, it_count);
-      if (group_barrier_or(kGroupBar, kGroup, *(volatile int*)abort_flag != 0)) break;   // leave together
+      // leave together: no more items, an abort seen by the steward, or a wait that expired in one thread
+      if (group_barrier_or(kGroupBar, kGroup, !got || !valid || *(volatile int*)abort_flag != 0)) {
+        if (!got) {
+          if (p.status) atomicExch(p.status, kWaitFullTimeout);
+          atomicExch(abort_flag, 1);
+        }
+        break;
+      }
       if (tid == 0) TRACE1(12, it_count);
       const int row = it.row0 + r;
       const int qi = min(row / p.group, max(it.q_len - 1, 0));
       const int hd = it.kvh * p.group + row % p.group;
-      if (!p.q_via_tma) {
-        // The GQA group does not tile the 128 rows as one TMA box: the two threads of a row copy half of
-        // it each into the swizzled tile (zeros past the request's rows).
-        if (it_count > 0 && !mbar_wait(&bars[bQEmpty], (it_count - 1) & 1u)) dead = true;
-        if (!dead) {
-          const bool valid = row < it.rows_total;
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                               ((int64_t)(it.q_start + row / p.group) * p.q_row_stride +
-                                (int64_t)hd * p.q_head_stride) * C::kEsz;
-          constexpr int kChunksHalf = C::kNKB * 4;         // 16-byte chunks each thread copies
-#pragma unroll
-          for (int i = 0; i < kChunksHalf; ++i) {
-            const int chunk = h * kChunksHalf + i, kb = chunk >> 3, c = chunk & 7;
-            const uint4 val = valid ? __ldg(reinterpret_cast<const uint4*>(src + kb * 128 + c * 16))
-                                    : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(q_smem + kb * C::kQBlock + swz128(r, c)) = val;
-          }
-          fence_proxy_async();
-        }
-        mbar_arrive(&bars[bQFull]);   // also when dead: the issuer must not be left waiting for this phase
-      }
       const int vis_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, qi + it.off)) : it.kv_len;
       const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
       const int sqi_lo = it.row0 / p.group;
       const int sqi_hi = min(it.q_len - 1, (it.row0 + kRows - 1) / p.group);
       const int full_lo = p.window_left >= 0 ? max(0, sqi_hi + it.off - p.window_left) : 0;
       const int full_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, sqi_lo + it.off)) : it.kv_len;
-      float dq = 1.f, dk = 1.f, dv = 1.f;
-      if (p.q_descale) dq = p.q_descale[it.b * p.q_descale_bs + it.kvh * p.q_descale_hs];
-      if (p.k_descale) dk = p.k_descale[it.b * p.k_descale_bs + it.kvh * p.k_descale_hs];
-      if (p.v_descale) dv = p.v_descale[it.b * p.v_descale_bs + it.kvh * p.v_descale_hs];
-      const float scale_log2 = p.softmax_scale * dq * dk * kLog2e;   // > 0 on this route
-
       float m_run = -INFINITY, l_run = 0.f;   // l_run: this thread's half of the row sum, in units of 2^kShift
       for (int j = 0; j < it.n_tiles; ++j) {
         if (tid == 0) TRACE1(17, tt);
@@ -564,11 +649,19 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
                                            : half_exp<D, kFp8, kPolyOf8_1>(s_tmem, s, scale_log2, neg_m));
         if (tid == 0) TRACE1(3, tt);
         if (j > 0) {
-          // O(j-1) must be complete before it may be rescaled and before P(j) lets the next P V start.
-          if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;   // reported at the next group barrier
+          // O(j-1) must be complete before it is rescaled; the tensor pipe itself keeps P V(j) behind P V(j-1).
+          // Without a rescale this phase of the O barrier is only counted (a satisfied wait and its fence cost
+          // ~170 cycles per tile).  A later wait cannot mistake an older phase for its own: S(j), waited for above,
+          // was committed after P V(j-2), so at most the phase being waited for is still open.  The end of the item
+          // has no such guarantee (P V(n-2) may still be waiting for its V tile when the last softmax is done, in a
+          // memory-bound decode), which is why it waits on a barrier of its own with one phase per item.
+          const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
+          if (rescale) {
+            if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;   // reported at the next group barrier
+            tcgen05_fence_after();
+          }
           ++co;
-          tcgen05_fence_after();
-          if (!dead && __any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!dead && rescale) {
 #pragma unroll
             for (int c = 0; c < D / 64; ++c) {
               uint32_t v[32];
@@ -589,7 +682,8 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         ++tt;
       }
       if (!dead && it.n_tiles > 0) {
-        if (!mbar_wait(&bars[bOFull], co & 1u)) dead = true;
+        if (!mbar_wait(&bars[bOFinal], cf & 1u)) dead = true;
+        ++cf;
         ++co;
         tcgen05_fence_after();
       }
@@ -617,6 +711,10 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       const int64_t q_row = it.q_start + row / p.group;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
                            (int64_t)hd * p.out_head_stride + h * (D / 2);
+      // Rows on 32-byte boundaries: one full sector per store (the epilogue is bound by the number of cache lines
+      // its stores touch, since every lane writes another row).
+      const bool out_vec32 = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (p.out_row_stride & 15) == 0 &&
+                             (p.out_head_stride & 15) == 0;
       const int64_t part_slot = ((int64_t)it.split * p.total_q + q_row) * p.num_q_heads + hd;
       float* part = split_mode ? p.part_o + part_slot * D + h * (D / 2) : nullptr;
 #pragma unroll
@@ -636,15 +734,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
                 make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
                             __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
         } else if (row < it.rows_total) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-            pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-            pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
-          }
+          store_bf16_row32(dst + c * 32, v, inv, out_vec32);
         }
       }
       if (h == 0 && row < it.rows_total) {

@@ -97,6 +97,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return mbar_wait_slow(bar, parity);
 }
 
+// 16-byte asynchronous copy global -> shared (no registers held while in flight); zeros when !valid.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+  const uint32_t bytes = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
 // 4-D tiled TMA load into this CTA only.  Coordinates are innermost first.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tensor_map, uint64_t* bar, int c0,
                                             int c1, int c2, int c3) {
@@ -142,6 +152,36 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 32-byte store (one full DRAM sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+// Eight consecutive FP32 values times `scale`, as eight BF16, to 16 bytes / sixteen to 32 bytes.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi);
+__device__ __forceinline__ void store_bf16_row32(__nv_bfloat16* dst, const uint32_t (&v)[32], float scale, bool vec32) {
+  if (vec32) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 16) {
+      uint32_t pk[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        pk[u] = pack_bf16(__uint_as_float(v[i + 2 * u]) * scale, __uint_as_float(v[i + 2 * u + 1]) * scale);
+      st_global_v8(dst + i, pk);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 pk;
+      pk.x = pack_bf16(__uint_as_float(v[i]) * scale, __uint_as_float(v[i + 1]) * scale);
+      pk.y = pack_bf16(__uint_as_float(v[i + 2]) * scale, __uint_as_float(v[i + 3]) * scale);
+      pk.z = pack_bf16(__uint_as_float(v[i + 4]) * scale, __uint_as_float(v[i + 5]) * scale);
+      pk.w = pack_bf16(__uint_as_float(v[i + 6]) * scale, __uint_as_float(v[i + 7]) * scale);
+      *reinterpret_cast<uint4*>(dst + i) = pk;
+    }
+  }
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
