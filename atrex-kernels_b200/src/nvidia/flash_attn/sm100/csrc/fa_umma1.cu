@@ -488,7 +488,10 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       if (!mbar_wait(&bars[bQFull], it_count & 1u)) { dead = true; break; }
       if (lane == 0) TRACE1(14, it_count);
       if (it.n_tiles == 0) {
-        if (lane == 0) mbar_arrive(&bars[bQEmpty]);
+        if (lane == 0) {
+          mbar_arrive(&bars[bQEmpty]);
+          mbar_arrive(&bars[bOFinal]);   // one phase per item, with or without tiles
+        }
         ++it_count;
         continue;
       }
@@ -572,7 +575,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
     const uint32_t o_tmem = tmem_base + lane_off + o_col + h * (D / 2);   // this thread's half of the O columns
     float* xchg = reinterpret_cast<float*>(smem + C::kOffXchg);            // [parity][half][row]
     constexpr int kGroupBar = 1, kGroup = kSoftmaxWarps1 * 32;
-    uint32_t cs[2] = {0, 0}, co = 0, cf = 0, it_count = 0, cx = 0;
+    uint32_t cs[2] = {0, 0}, co = 0, it_count = 0, cx = 0;
     [[maybe_unused]] uint32_t tt = 0;   // tiles so far (trace index)
     bool dead = false;
     const ItemSlot* slots = reinterpret_cast<const ItemSlot*>(smem + C::kOffItem);
@@ -581,17 +584,16 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       // the item was resolved by warp 11 while the previous one was being worked on
       const ItemSlot* item_slot = slots + (it_count & 1u);
       const bool got = mbar_wait(&bars[bItemFull + (it_count & 1u)], (it_count >> 1) & 1u);
+      // The slot stays this item's until the end of the epilogue, which reads the item again instead of keeping
+      // its fields in registers across the tile loop.
       Item256 it;
       bool valid = false;
-      float scale_log2 = 0.f, dv = 1.f;
+      float scale_log2 = 0.f;
       if (got) {
         it = item_slot->it;
         valid = item_slot->valid != 0;
         scale_log2 = item_slot->scale_log2;
-        dv = item_slot->dv;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[bItemEmpty + (it_count & 1u)]);
       if (tid == 0) TRACE1(22, it_count);
       // leave together: no more items, an abort seen by the steward, or a wait that expired in one thread
       if (group_barrier_or(kGroupBar, kGroup, !got || !valid || *(volatile int*)abort_flag != 0)) {
@@ -602,9 +604,7 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         break;
       }
       if (tid == 0) TRACE1(12, it_count);
-      const int row = it.row0 + r;
-      const int qi = min(row / p.group, max(it.q_len - 1, 0));
-      const int hd = it.kvh * p.group + row % p.group;
+      const int qi = min((it.row0 + r) / p.group, max(it.q_len - 1, 0));
       const int vis_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, qi + it.off)) : it.kv_len;
       const int vis_lo = p.window_left >= 0 ? max(0, qi + it.off - p.window_left) : 0;
       const int sqi_lo = it.row0 / p.group;
@@ -612,11 +612,12 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
       const int full_lo = p.window_left >= 0 ? max(0, sqi_hi + it.off - p.window_left) : 0;
       const int full_hi = p.window_right >= 0 ? min(it.kv_len, right_bound(p, sqi_lo + it.off)) : it.kv_len;
       float m_run = -INFINITY, l_run = 0.f;   // l_run: this thread's half of the row sum, in units of 2^kShift
-      for (int j = 0; j < it.n_tiles; ++j) {
+      const int n_tiles = it.n_tiles, tile_lo = it.tile_lo;
+      for (int j = 0; j < n_tiles; ++j) {
         if (tid == 0) TRACE1(17, tt);
         const int buf = j & 1;
         const uint32_t s_tmem = tmem_base + lane_off + buf * BN + h * N;   // own scores; P goes over them
-        const int tok0 = (it.tile_lo + j) * BN;
+        const int tok0 = (tile_lo + j) * BN;
         const bool need_mask = tok0 < full_lo || tok0 + BN > full_hi;
         if (tid == 0) TRACE1(16, tt);
         if (!mbar_wait(&bars[bSFull + buf], cs[buf] & 1u)) dead = true;
@@ -681,10 +682,9 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         if (tid == 128) TRACE1(7, tt);
         ++tt;
       }
-      if (!dead && it.n_tiles > 0) {
-        if (!mbar_wait(&bars[bOFinal], cf & 1u)) dead = true;
-        ++cf;
-        ++co;
+      if (!dead) {
+        if (!mbar_wait(&bars[bOFinal], it_count & 1u)) dead = true;   // one phase per item
+        if (n_tiles > 0) ++co;
         tcgen05_fence_after();
       }
       if (tid == 0) TRACE1(21, it_count);
@@ -699,50 +699,56 @@ atrex_sm100_fwd_umma1_kernel(const __grid_constant__ FwdParams p) {
         break;
       }
       const float l_row = l_run + slot[(h ^ 1) * kRows + r];
-      const bool split_mode = it.n_splits > 1;    // the combine kernel adds the sink and converts to BF16
+      const Item256 ie = item_slot->it;            // read again: see the top of the item loop
+      const float dv = item_slot->dv;
+      const int row = ie.row0 + r;
+      const int hd = ie.kvh * p.group + row % p.group;
+      const bool split_mode = ie.n_splits > 1;    // the combine kernel adds the sink and converts to BF16
       float sink_l2 = -INFINITY;
-      if (p.sink != nullptr && !split_mode && row < it.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
+      if (p.sink != nullptr && !split_mode && row < ie.rows_total) sink_l2 = __bfloat162float(p.sink[hd]) * kLog2e;
       const float m_f = fmaxf(m_run, sink_l2);
       const float m_use = m_f == -INFINITY ? 0.f : m_f;
       const float resc = fast_exp2(m_run - m_use);
       float l = l_row * resc;                                        // in units of 2^kShift
       if (sink_l2 != -INFINITY) l += fast_exp2(sink_l2 - m_use + C::kShift);
-      const float inv = (l > 0.f && it.n_tiles > 0) ? dv * resc / l : 0.f;
-      const int64_t q_row = it.q_start + row / p.group;
+      const float inv = (l > 0.f && ie.n_tiles > 0) ? dv * resc / l : 0.f;
+      const int64_t q_row = ie.q_start + row / p.group;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + q_row * p.out_row_stride +
                            (int64_t)hd * p.out_head_stride + h * (D / 2);
       // Rows on 32-byte boundaries: one full sector per store (the epilogue is bound by the number of cache lines
       // its stores touch, since every lane writes another row).
       const bool out_vec32 = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (p.out_row_stride & 15) == 0 &&
                              (p.out_head_stride & 15) == 0;
-      const int64_t part_slot = ((int64_t)it.split * p.total_q + q_row) * p.num_q_heads + hd;
+      const int64_t part_slot = ((int64_t)ie.split * p.total_q + q_row) * p.num_q_heads + hd;
       float* part = split_mode ? p.part_o + part_slot * D + h * (D / 2) : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
-        if (it.n_tiles > 0) {
+        if (ie.n_tiles > 0) {
           tmem_ld32(o_tmem + c * 32, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
-        if (row < it.rows_total && split_mode) {
+        if (row < ie.rows_total && split_mode) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<float4*>(part + c * 32 + i) =
                 make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
                             __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-        } else if (row < it.rows_total) {
+        } else if (row < ie.rows_total) {
           store_bf16_row32(dst + c * 32, v, inv, out_vec32);
         }
       }
-      if (h == 0 && row < it.rows_total) {
+      if (h == 0 && row < ie.rows_total) {
         const float lse_l2 = l > 0.f ? m_use + log2f(l) - C::kShift : -INFINITY;
         if (split_mode) p.part_lse[part_slot] = lse_l2;
         else if (p.lse != nullptr) p.lse[(int64_t)hd * p.total_q + q_row] = lse_l2 * kLn2;
       }
       tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[bItemEmpty + (it_count & 1u)]);   // warp 11 may resolve item n + 2 into the slot
       if (tid == 0) TRACE1(13, it_count);
     }
   }
