@@ -59,9 +59,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // for up to kSuspendHintNs, so the limit is seconds, far above any real wait.
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kSuspendHintNs = 1000;
-// The loop holds one try_wait with a suspend-time hint, a count-down and nothing else.  Without the hint a
-// waiting warp came back every ~240 cycles and the waits were 37 % of all instructions the head_dim-128
-// prefill kernel executed; with it that kernel is 2.5 % faster at the power cap (1 012 -> 1 037 TFLOP/s).
+// The loop holds one try_wait with a suspend-time hint, a count-down and nothing else.  Without the hint, and with
+// the iteration test and a sleep in the loop, a waiting warp came back every ~240 cycles and the waits were 37 %
+// of all instructions the head_dim-128 prefill kernel executed.  Effect on that kernel: +2.5 % in 10-step runs
+// (1 012 -> 1 037 TFLOP/s), none in 40-step runs at the power cap (1 042 - 1 047 with or without the hint).
 // The spinning part is also kept out of line: a wait has a dozen call sites per kernel, and an inlined
 // loop at each of them pushes the hot loops of the MMA-issuing and TMA-issuing warps out of the
 // instruction cache.
