@@ -70,40 +70,8 @@ struct QsaParams {
   int32_t* status;
   long long q_row_stride, q_head_stride, kv_page_stride, kv_row_stride, kv_head_stride;
   int rows, hq, hkv, group, num_pages, page_size, batch, table_width, pos64, num_splits;
-  int piece_tiles;    // > 0: balanced pieces (see the kernel); the partials are then [piece][16][256] / [piece][16]
   float scale_log2, v_scale;
 };
-
-// Tiles of the longest token list a row can have (512 blocks + the unfinished one).
-constexpr int kRowTilesMax = (kTopk * 4 + 3 + kTile - 1) / kTile;
-
-// Balanced pieces.  Rows x KV heads CTAs with a uniform split leave SMs idle whenever that product does not divide
-// the SM count (64 decode rows x 2 splits = 128 CTAs on 148 SMs), and more CTAs than SMs cost a second wave of
-// 200 KB CTAs.  Instead the rows' token lists are laid end to end, every (row, KV head) taking kRowTilesMax virtual
-// tiles, and cut into one piece of `piece_tiles` virtual tiles per CTA: a CTA serves the end of one row's list and
-// the start of the next (at most two segments, since piece_tiles <= kRowTilesMax), each segment publishing its
-// own partial; the combine kernel finds a row's partials from the same arithmetic.  Rows with shorter lists leave
-// the tail of their virtual range empty.  Everything is computed from static sizes: no metadata is read on the host.
-struct PieceSegment {
-  int t, h, tile_lo, tile_hi, piece;   // tile range in the row's VIRTUAL tiles; piece = partial slot
-};
-__device__ __forceinline__ int piece_segments(const QsaParams& p, int cta, PieceSegment (&seg)[2]) {
-  const long long total = (long long)p.rows * p.hkv * kRowTilesMax;
-  const long long v_lo = (long long)cta * p.piece_tiles;
-  const long long v_hi = min(v_lo + p.piece_tiles, total);
-  if (v_lo >= v_hi) return 0;
-  const int rh0 = (int)(v_lo / kRowTilesMax), rh1 = (int)((v_hi - 1) / kRowTilesMax);
-  int n = 0;
-  for (int rh = rh0; rh <= rh1 && n < 2; ++rh, ++n) {
-    const long long base = (long long)rh * kRowTilesMax;
-    seg[n].t = rh / p.hkv;
-    seg[n].h = rh % p.hkv;
-    seg[n].tile_lo = (int)(max(v_lo, base) - base);
-    seg[n].tile_hi = (int)(min(v_hi, base + kRowTilesMax) - base);
-    seg[n].piece = cta * 2 + n;
-  }
-  return n;
-}
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
   const uint32_t bytes = valid ? 16u : 0u;   // 0: the destination is zero-filled and nothing is read
@@ -142,24 +110,12 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   long long* block_off = meta + kWarps * kStages * kTile;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = blockIdx.x / p.hkv, h = blockIdx.x % p.hkv;
+  const int split = blockIdx.y;
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (tid == 0 && p.status) atomicExch(p.status, kBadSmemAlignment);
     return;
   }
-  // what this CTA serves: one (row, KV head, split), or the one or two segments of its balanced piece
-  PieceSegment segs[2];
-  int n_seg = 1;
-  if (p.piece_tiles > 0) {
-    n_seg = piece_segments(p, blockIdx.x, segs);
-  } else {
-    segs[0].t = blockIdx.x / p.hkv;
-    segs[0].h = blockIdx.x % p.hkv;
-    segs[0].piece = blockIdx.y;
-    segs[0].tile_lo = segs[0].tile_hi = 0;   // set from the row's own tile count below
-  }
-  for (int si = 0; si < n_seg; ++si) {
-  const int t = segs[si].t, h = segs[si].h;
-  const int split = segs[si].piece;
 
   // ---- the row's token list: complete blocks from the id list, then the unfinished block ----
   const long long position = p.pos64 ? reinterpret_cast<const long long*>(p.pos)[t]
@@ -171,10 +127,8 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   const int n_tok = live ? complete * 4 + (int)(visible % 4) : 0;
   const long long tail_start = (visible / 4) * 4;
   const int n_tiles_row = (n_tok + kTile - 1) / kTile;
-  const int tile_lo = p.piece_tiles > 0 ? min(segs[si].tile_lo, n_tiles_row)
-                                        : (int)(((long long)n_tiles_row * split) / p.num_splits);
-  const int tile_hi = p.piece_tiles > 0 ? min(segs[si].tile_hi, n_tiles_row)
-                                        : (int)(((long long)n_tiles_row * (split + 1)) / p.num_splits);
+  const int tile_lo = (int)(((long long)n_tiles_row * split) / p.num_splits);
+  const int tile_hi = (int)(((long long)n_tiles_row * (split + 1)) / p.num_splits);
   const int32_t* row_ids = p.ids + (long long)t * kTopk;
   const int32_t* table_row = p.table + (long long)(live ? request : 0) * p.table_width;
 
@@ -429,7 +383,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     }
   }
   __syncthreads();
-  const bool split_mode = p.num_splits > 1 || p.piece_tiles > 0;
+  const bool split_mode = p.num_splits > 1;
   for (int idx = tid; idx < p.group * (kD / 4); idx += kThreads) {
     const int r = idx / (kD / 4), c4 = idx % (kD / 4);
     const int head = h * p.group + r;
@@ -452,7 +406,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
     const long long slot = (long long)t * p.hq + head;
     if (split_mode) {
-      const long long ps = p.piece_tiles > 0 ? (long long)split * 16 + r : (long long)split * p.rows * p.hq + slot;
+      const long long ps = (long long)split * p.rows * p.hq + slot;
       *reinterpret_cast<float4*>(p.part_o + ps * kD + c4 * 4) = o;
       if (c4 == 0) p.part_lse[ps] = l > 0.f ? m_use + log2f(l) : -INFINITY;
     } else {
@@ -472,8 +426,6 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
       *reinterpret_cast<uint2*>(p.out + slot * kD + c4 * 4) = packed;
     }
   }
-  __syncthreads();   // the next segment reuses the Q tile, the tile buffers (the merge aliases them) and the offsets
-  }   // segments
 }
 
 // Split combine: out = bf16( bf16( sum_i w_i A_i / sum_i w_i * v_scale ) * sigmoid(gate) ), w_i = 2^(lse_i - max);
@@ -484,40 +436,18 @@ atrex_sm100_qsa_combine_kernel(const __grid_constant__ QsaParams p) {
   const long long slot = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const long long slots = (long long)p.rows * p.hq;
   if (slot >= slots) return;
-  // where this (row, head)'s partials are: `n_parts` of them, the i-th at index first + i * stride (+ fix-up)
-  int n_parts = p.num_splits;
-  long long first = slot, stride = slots;
-  int k0 = 0, rh = 0;
-  if (p.piece_tiles > 0) {
-    // balanced pieces: the CTAs whose piece overlaps the row's virtual tile range; a CTA's first segment has
-    // partial slot 2k, its second 2k + 1
-    const int t = (int)(slot / p.hq), head = (int)(slot % p.hq);
-    rh = t * p.hkv + head / p.group;
-    const long long base = (long long)rh * kRowTilesMax;
-    k0 = (int)(base / p.piece_tiles);
-    n_parts = (int)((base + kRowTilesMax - 1) / p.piece_tiles) - k0 + 1;
-    first = head % p.group;
-    stride = 0;
-  }
-  auto part_index = [&](int i) -> long long {
-    if (p.piece_tiles == 0) return first + (long long)i * stride;
-    const int k = k0 + i;
-    const int seg = (int)(((long long)k * p.piece_tiles) / kRowTilesMax) == rh ? 0 : 1;
-    return (long long)(k * 2 + seg) * 16 + first;
-  };
   float mx = -INFINITY;
-  for (int s = 0; s < n_parts; ++s) mx = fmaxf(mx, p.part_lse[part_index(s)]);
+  for (int s = 0; s < p.num_splits; ++s) mx = fmaxf(mx, p.part_lse[s * slots + slot]);
   float acc[8], denom = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   if (mx != -INFINITY) {
-    for (int s = 0; s < n_parts; ++s) {
-      const long long pi = part_index(s);
-      const float l = p.part_lse[pi];
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float l = p.part_lse[s * slots + slot];
       if (l == -INFINITY) continue;
       const float w = fast_exp2(l - mx);
       denom += w;
-      const float4* src = reinterpret_cast<const float4*>(p.part_o + pi * kD + lane * 8);
+      const float4* src = reinterpret_cast<const float4*>(p.part_o + (s * slots + slot) * kD + lane * 8);
       const float4 a = src[0], b = src[1];
       acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
       acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
@@ -539,8 +469,6 @@ atrex_sm100_qsa_combine_kernel(const __grid_constant__ QsaParams p) {
 
 struct QsaResolved {
   int splits, launches;
-  int piece_tiles;      // > 0: balanced pieces, one per CTA
-  unsigned grid_x, grid_y;
   uint64_t off_lse, off_o, bytes;
 };
 
@@ -577,31 +505,16 @@ int qsa_check(const atrex_qsa_sm100_params* p) {
 }
 
 void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) {
-  const long long ctas = (long long)p->rows * p->num_kv_heads;
-  r->piece_tiles = 0;
-  if (p->num_splits == 0 && ctas > 0 && ctas < sm_count) {
-    // Fewer (row, KV head) pairs than SMs: one balanced piece per SM, all CTAs in ONE wave (one 200 KB CTA is
-    // resident per SM; measured on 64 decode rows: 2 uniform splits = 128 CTAs 33 us, 3 = 192 CTAs in two waves
-    // 46 us).  A piece is at least one tile per warp.
-    const long long total = ctas * kRowTilesMax;
-    long long len = (total + sm_count - 1) / sm_count;
-    if (len < kWarps) len = kWarps;
-    r->piece_tiles = (int)len;
-    r->grid_x = (unsigned)((total + len - 1) / len);
-    r->grid_y = 1;
-    r->splits = (int)((kRowTilesMax + len - 1) / len) + 1;   // most partials one row can have
-    r->launches = 2;
-    const uint64_t pieces = 2ull * r->grid_x;
-    r->off_lse = 0;
-    r->off_o = (4ull * pieces * 16 + 255) / 256 * 256;
-    r->bytes = r->off_o + 4ull * pieces * 16 * kD;
-    return;
+  int splits = p->num_splits;
+  if (splits == 0) {
+    // rows x KV heads CTAs, one resident per SM: split the token lists while all CTAs still run in ONE wave
+    // (measured on 64 decode rows: 2 splits = 128 CTAs 37 us, 3 splits = 192 CTAs in two waves 46 us)
+    const long long ctas = (long long)p->rows * p->num_kv_heads;
+    const long long want = ctas > 0 ? sm_count / ctas : 1;
+    splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
   }
-  const int splits = p->num_splits == 0 ? 1 : p->num_splits;
   r->splits = splits;
   r->launches = splits > 1 ? 2 : 1;
-  r->grid_x = (unsigned)ctas;
-  r->grid_y = (unsigned)splits;
   const uint64_t slots = (uint64_t)p->rows * p->num_q_heads;
   r->off_lse = 0;
   r->off_o = splits > 1 ? (4ull * splits * slots + 255) / 256 * 256 : 0;
@@ -662,26 +575,25 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   k.out = static_cast<__nv_bfloat16*>(p->out);
   k.status = p->device_status;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  if (r.launches > 1) {
+  if (r.splits > 1) {
     k.part_lse = reinterpret_cast<float*>(ws + r.off_lse);
     k.part_o = reinterpret_cast<float*>(ws + r.off_o);
   }
-  k.piece_tiles = r.piece_tiles;
   k.q_row_stride = p->q_row_stride; k.q_head_stride = p->q_head_stride;
   k.kv_page_stride = p->kv_page_stride; k.kv_row_stride = p->kv_row_stride; k.kv_head_stride = p->kv_head_stride;
   k.rows = p->rows; k.hq = p->num_q_heads; k.hkv = p->num_kv_heads; k.group = p->num_q_heads / p->num_kv_heads;
   k.num_pages = p->num_pages; k.page_size = p->page_size; k.batch = p->batch; k.table_width = p->table_width;
   k.pos64 = p->positions_are_int64 ? 1 : 0;
-  k.num_splits = r.piece_tiles > 0 ? 1 : r.splits;
+  k.num_splits = r.splits;
   k.scale_log2 = p->sm_scale * kLog2e;
   k.v_scale = p->v_scale;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  const dim3 grid(r.grid_x, r.grid_y, 1);
+  const dim3 grid((unsigned)((long long)p->rows * p->num_kv_heads), (unsigned)r.splits, 1);
   cudaError_t e = p->dtype == ATREX_FA_E4M3
                       ? launch_kernel(atrex_sm100_qsa_kernel<true>, grid, dim3(kThreads), kSmemBytes, stream, k)
                       : launch_kernel(atrex_sm100_qsa_kernel<false>, grid, dim3(kThreads), kSmemBytes, stream, k);
   if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention kernel", e);
-  if (r.launches > 1) {
+  if (r.splits > 1) {
     const long long slots = (long long)p->rows * p->num_q_heads;
     e = launch_kernel(atrex_sm100_qsa_combine_kernel, dim3((unsigned)((slots + 7) / 8)), dim3(256), 0, stream, k);
     if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention combine kernel", e);
