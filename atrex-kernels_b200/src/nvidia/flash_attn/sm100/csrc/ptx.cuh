@@ -62,7 +62,9 @@ constexpr uint32_t kSuspendHintNs = 1000;
 // The loop holds one try_wait with a suspend-time hint, a count-down and nothing else.  Without the hint, and with
 // the iteration test and a sleep in the loop, a waiting warp came back every ~240 cycles and the waits were 37 %
 // of all instructions the head_dim-128 prefill kernel executed.  Effect on that kernel: +2.5 % in 10-step runs
-// (1 012 -> 1 037 TFLOP/s), none in 40-step runs at the power cap (1 042 - 1 047 with or without the hint).
+// (1 012 -> 1 037 TFLOP/s), none in 40-step runs at the power cap (1 042 - 1 047 with or without the hint).  The
+// opcode counters afterwards show SYNCS and NANOSLEEP in a loop: the hinted try_wait is itself a poll with a sleep,
+// not a blocking wait, and the waits remain ~40 % of the executed instructions (from warps with nothing else to do).
 // The spinning part is also kept out of line: a wait has a dozen call sites per kernel, and an inlined
 // loop at each of them pushes the hot loops of the MMA-issuing and TMA-issuing warps out of the
 // instruction cache.
