@@ -306,6 +306,21 @@ def test_fp8_prefill_hd256(page):
     T.check(case, fp8=True)
 
 
+@pytest.mark.parametrize("d,fp8,hq,hkv", [(256, False, 24, 2), (128, True, 12, 1), (256, True, 24, 2), (128, True, 3, 1),
+                                          (128, True, 10, 2)])
+def test_q_rows_copied_by_the_steward_warp(d, fp8, hq, hkv):
+    """GQA groups that do not tile 128 rows as one TMA box (12, 3, 5): warp 11 of the single-tile kernel copies the
+    item's Q rows into the swizzled tile one item ahead, one, two or four rows per warp-wide copy depending on the
+    row size (512 / 256 / 128 bytes).  Empty requests, a request of one row, many row tiles per request (several
+    items per CTA: the two item slots wrap), zeros past a request's rows; oracle on every request."""
+    from atrex.src.nvidia.flash_attn.sm100 import runtime
+
+    case = T.make_case(64, [0, 5, 1400, 130, 0, 1], [40, 700, 1400, 1000, 0, 9], hq=hq, hkv=hkv, d=d, fp8=fp8,
+                       std=0.6, poison_tail=True, seed=d + hq)
+    assert _planned_route(case) == runtime.ROUTE_UMMA     # head_dim 256 or E4M3: the single-tile tcgen05 kernel
+    T.check(case, fp8=fp8)
+
+
 def test_fp8_descales_matter_and_are_reread():
     """A non-unit descale must change the result, and a descale mutated in place between calls must be read
     again (reference: op_test/ppu/flash_attn/test_flash_attn_zwm890p.py:268-309)."""
