@@ -18,9 +18,10 @@
 //     while the next tile's copies are in flight; no block-wide barrier inside the loop;
 //   * tokens that do not count (hidden block, request id out of range, page outside the table or the pool) are
 //     zero-filled in shared memory and masked in S, so no address is formed from them;
-//   * E4M3 caches are copied as bytes (half the traffic) and widened to BF16 in shared memory when a tile is
-//     consumed - every E4M3 value is exact in BF16 - so one MMA path serves both types; sm_scale carries the
-//     Q and K scales, v_scale multiplies the result;
+//   * E4M3 caches are copied as bytes (half the traffic); S = Q K^T runs on the E4M3 MMA (m16n8k32) straight
+//     from the raw K tile, V is widened to BF16 in shared memory when a tile is consumed (every E4M3 value is
+//     exact in BF16) and P V runs in BF16 like the other type; sm_scale carries the Q and K scales, v_scale
+//     multiplies the result;
 //   * the warps' partial states merge through shared memory; the epilogue rounds A to BF16, multiplies by
 //     sigmoid(gate) and stores BF16 (or writes a normalised FP32 partial + log2 LSE for the split combine).
 #include <cuda_fp8.h>
@@ -82,6 +83,13 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 // 16 E4M3 bytes -> 16 BF16 (two 16-byte vectors), exact.
 __device__ __forceinline__ void widen_e4m3x16(const uint4& raw, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -132,22 +140,15 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   const int32_t* row_ids = p.ids + (long long)t * kTopk;
   const int32_t* table_row = p.table + (long long)(live ? request : 0) * p.table_width;
 
-  // ---- Q rows of this KV head's group -> shared memory as BF16 (swizzled like K) ----
+  // ---- Q rows of this KV head's group -> shared memory in the cache's own type (swizzled like K) ----
   {
-    constexpr int kChunks = kD / 8;   // 16-byte BF16 chunks per row
+    constexpr int kChunks = kFp8 ? kD / 16 : kD / 8;   // 16-byte chunks per row: 16 E4M3 or 8 BF16 each
     for (int idx = tid; idx < 16 * kChunks; idx += kThreads) {
       const int r = idx / kChunks, c = idx % kChunks;
       uint4 val = make_uint4(0, 0, 0, 0);
       if (r < p.group) {
-        const long long e = (long long)t * p.q_row_stride + (long long)(h * p.group + r) * p.q_head_stride + c * 8;
-        if (kFp8) {
-          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.q) + e));
-          uint4 lo, hi;
-          widen_e4m3x16(make_uint4(raw.x, raw.y, 0, 0), lo, hi);
-          val = lo;
-        } else {
-          val = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + e * 2));
-        }
+        const long long e = (long long)t * p.q_row_stride + (long long)(h * p.group + r) * p.q_head_stride;
+        val = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + e * (kFp8 ? 1 : 2) + c * 16));
       }
       *reinterpret_cast<uint4*>(q_smem + (c / 8) * (16 * 128) + swz128(r, c % 8)) = val;
     }
@@ -208,8 +209,8 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
         const long long row_off = __shfl_sync(0xffffffffu, off, r);
         const bool ok = row_off >= 0;
         const long long byte = ok ? row_off + c * 16 : 0;
-        cp_async16(raw_k(s) + r * kRowBytes + c * 16, kbase + byte, ok);
-        cp_async16(raw_v(s) + r * kRowBytes + c * 16, vbase + byte, ok);
+        cp_async16(raw_k(s) + (c / 8) * (kTile * 128) + swz128(r, c % 8), kbase + byte, ok);   // MMA layout: used as it is
+        cp_async16(raw_v(s) + r * kRowBytes + c * 16, vbase + byte, ok);                       // plain rows: widened below
       }
     } else {
       // a row is 512 bytes = 32 chunks: one row per warp instruction, written in the swizzled MMA layout
@@ -259,22 +260,19 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
 
     uint32_t k_addr, v_addr;
     if (kFp8) {
-      // widen the raw tile into the BF16 tile (second half of the warp's region), swizzled for the MMA
-      uint8_t* wide_k = my + kStages * 2 * kRawOperand;
-      uint8_t* wide_v = wide_k + kOperandBytes;
+      // K is multiplied as E4M3 straight from its raw stage; V is widened into the BF16 tile behind the raw stages
+      // (P stays BF16: three mantissa bits are too few for the probabilities), swizzled for the MMA
+      uint8_t* wide_v = my + kStages * 2 * kRawOperand;
 #pragma unroll
       for (int j = 0; j < kTile / 2; ++j) {
         const int r = 2 * j + (lane >> 4), c = lane & 15;   // raw chunk c = elements 16c .. 16c + 15 = BF16 chunks 2c, 2c + 1
         uint4 lo, hi;
-        widen_e4m3x16(*reinterpret_cast<const uint4*>(raw_k(stage) + r * kRowBytes + c * 16), lo, hi);
-        *reinterpret_cast<uint4*>(wide_k + ((2 * c) / 8) * (kTile * 128) + swz128(r, (2 * c) % 8)) = lo;
-        *reinterpret_cast<uint4*>(wide_k + ((2 * c + 1) / 8) * (kTile * 128) + swz128(r, (2 * c + 1) % 8)) = hi;
         widen_e4m3x16(*reinterpret_cast<const uint4*>(raw_v(stage) + r * kRowBytes + c * 16), lo, hi);
         *reinterpret_cast<uint4*>(wide_v + ((2 * c) / 8) * (kTile * 128) + swz128(r, (2 * c) % 8)) = lo;
         *reinterpret_cast<uint4*>(wide_v + ((2 * c + 1) / 8) * (kTile * 128) + swz128(r, (2 * c + 1) % 8)) = hi;
       }
       __syncwarp();
-      k_addr = smem_u32(wide_k);
+      k_addr = smem_u32(raw_k(stage));
       v_addr = smem_u32(wide_v);
     } else {
       k_addr = smem_u32(raw_k(stage));
@@ -285,18 +283,29 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     // four independent accumulator pairs (one per 64-element block of the head dimension) instead of one chain
     // of sixteen dependent MMAs: a warp is alone on its scheduler here, so only instruction-level parallelism
     // hides the MMA latency
-    float s4[kD / 64][2][4];
+    // An E4M3 cache is multiplied by the E4M3 Q with m16n8k32 (the byte layout of a tile is that of a 16-bit tile
+    // of half the depth, so the same ldmatrix addressing serves both): half the instructions of the BF16 product.
+    float s4[4][2][4];
 #pragma unroll
-    for (int kb = 0; kb < kD / 64; ++kb) {
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s4[kb][0][e] = s4[kb][1][e] = 0.f;
+      for (int e = 0; e < 4; ++e) s4[i][0][e] = s4[i][1][e] = 0.f;
+    constexpr int kBlocks = kFp8 ? kD / 128 : kD / 64;     // 128-byte column blocks of a row
+#pragma unroll
+    for (int kb = 0; kb < kBlocks; ++kb) {
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         uint32_t a[4], b0, b1, b2, b3;
         ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + kb * (16 * 128) + swz128(q_lane_row, ks * 2 + q_lane_chunk));
         ldmatrix_x4(b0, b1, b2, b3, k_addr + kb * (kTile * 128) + swz128(k_lane_row, ks * 2 + k_lane_chunk));
-        mma_bf16_16816(s4[kb][0], a, b0, b1);
-        mma_bf16_16816(s4[kb][1], a, b2, b3);
+        const int acc = kFp8 ? kb * 2 + (ks & 1) : kb;     // four independent chains either way
+        if constexpr (kFp8) {
+          mma_e4m3_16832(s4[acc][0], a, b0, b1);
+          mma_e4m3_16832(s4[acc][1], a, b2, b3);
+        } else {
+          mma_bf16_16816(s4[acc][0], a, b0, b1);
+          mma_bf16_16816(s4[acc][1], a, b2, b3);
+        }
       }
     }
     float s[2][4];
