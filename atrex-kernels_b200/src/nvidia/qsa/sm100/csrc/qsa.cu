@@ -12,7 +12,8 @@
 //   * the CTA first resolves its share of the row's blocks to cache addresses (block id -> first token -> page
 //     table -> address; a four-token block never straddles a page) into shared memory: two dependent global
 //     loads once per CTA instead of once per tile on every warp's critical path;
-//   * each of the six warps is then its own pipeline: it takes every sixth 16-token tile (four blocks),
+//   * each of the six (BF16 cache) or eight (E4M3 cache) warps is then its own pipeline: it takes every sixth /
+//     eighth 16-token tile (four blocks),
 //     fetches K and V with 16-byte cp.async copies into its private double buffer (a row is one coalesced
 //     512-byte request) and computes S = Q K^T, the online softmax (log2 domain) and O += P V with mma.sync
 //     while the next tile's copies are in flight; no block-wide barrier inside the loop;
@@ -37,24 +38,37 @@ constexpr int kD = ATREX_QSA_SM100_HEAD_DIM;
 constexpr int kTopk = ATREX_QSA_SM100_TOPK;
 constexpr int kTile = 16;                 // tokens per warp tile = four blocks
 // Measured on B200 (64 decode rows / 2048 prefill rows, device time per call): 4 warps x 2 stages 32.0 / 510 us,
-// 4 x 3 32.2 / 548 us, 6 x 2 33.1 / 496 us (E4M3 decode 41.6 / 40.7 / 36.9 us): six warps with double buffers.
+// 4 x 3 32.2 / 548 us, 6 x 2 33.1 / 496 us (E4M3 decode 41.6 / 40.7 / 36.9 us): six warps with double buffers.  The
+// E4M3 decode then went 37.2 -> 31.4 us with S = Q K^T on the E4M3 MMA (K not widened) and -> 27.3 us with eight
+// warps, which fit once K needs no widened tile; a third raw stage (31.0), skipping the O rescale when no row
+// maximum moved (32.6) and widening to FP16 instead of BF16 (39.7 against 37.0 before the E4M3 MMA) did not help.
 #ifndef ATREX_QSA_WARPS
 #define ATREX_QSA_WARPS 6
 #endif
 #ifndef ATREX_QSA_STAGES
 #define ATREX_QSA_STAGES 2
 #endif
-constexpr int kWarps = ATREX_QSA_WARPS;
-constexpr int kThreads = kWarps * 32;
+#ifndef ATREX_QSA_WARPS_FP8
+#define ATREX_QSA_WARPS_FP8 8
+#endif
 constexpr int kMaxSplits = 16;
-constexpr int kQBytes = 16 * kD * 2;      // Q tile: 16 rows (8 or 12 used) x 256 BF16
+constexpr int kQBytes = 16 * kD * 2;      // Q tile: 16 rows (8 or 12 used) x 256 BF16 (E4M3: half of it)
 constexpr int kOperandBytes = kTile * kD * 2;          // one K or V tile as BF16: 8 KB
 constexpr int kStages = ATREX_QSA_STAGES;              // tiles resident per warp: one being consumed, the others in flight
-constexpr int kWarpBytes = kStages * 2 * kOperandBytes;   // per warp: kStages x (K + V) as BF16; E4M3: raw stages + one widened tile
-constexpr int kMetaBytes = kWarps * kStages * kTile * 8;  // per warp and stage: 16 row offsets (int64, -1 = does not count)
 constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of every block's first row (-1 = does not count)
-constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
-static_assert(kWarps * 16 * (kD + 2) * 4 <= kWarps * kWarpBytes, "merge buffer aliases the tile buffers");
+// Per cache type.  A warp's region holds kStages x (K + V) tiles as BF16 (32 KB), or for E4M3 the raw stages (half
+// the bytes) and one widened V tile (24 KB): eight warps then fit where six BF16 warps do, and the E4M3 call, which
+// moves half the bytes and is bound by the warps' own pace per tile rather than by memory, gets a third more of them.
+template <bool kFp8>
+struct QsaCfg {
+  static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS;
+  static constexpr int kThreads = kWarps * 32;
+  static constexpr int kWarpBytes = kFp8 ? kStages * 2 * (kTile * kD) + kOperandBytes : kStages * 2 * kOperandBytes;
+  static constexpr int kMetaBytes = kWarps * kStages * kTile * 8;   // per warp and stage: 16 row offsets (int64, -1 = does not count)
+  static constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
+  static_assert(16 * (kD + 2) * 4 <= kWarpBytes, "merge buffer aliases the tile buffers");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
+};
 
 struct QsaParams {
   const void* q;
@@ -109,8 +123,9 @@ __device__ __forceinline__ void widen_e4m3x16(const uint4& raw, uint4& lo, uint4
 }
 
 template <bool kFp8>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(QsaCfg<kFp8>::kThreads, 1)
 atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
+  constexpr int kWarps = QsaCfg<kFp8>::kWarps, kThreads = QsaCfg<kFp8>::kThreads, kWarpBytes = QsaCfg<kFp8>::kWarpBytes;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_smem = smem;
   uint8_t* tiles = smem + kQBytes;
@@ -184,7 +199,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   constexpr int kRawOperand = kTile * kRowBytes;       // raw bytes of one K or V tile
   // BF16: stage s holds K at s * 2 * kOperandBytes, V right behind.  E4M3: raw stage s at s * 2 * kRawOperand
   // (K then V); the widened tile (K then V) sits behind the raw stages.
-  static_assert(!kFp8 || kStages * 2 * (kTile * kD) + 2 * kOperandBytes <= kWarpBytes, "raw stages + widened tile fit");
+  static_assert(!kFp8 || kStages * 2 * (kTile * kD) + kOperandBytes <= kWarpBytes, "raw stages + the widened V tile fit");
   auto raw_k = [&](int s) { return my + s * 2 * kRawOperand; };
   auto raw_v = [&](int s) { return my + s * 2 * kRawOperand + kRawOperand; };
 
@@ -571,9 +586,11 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !prepared[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         QsaCfg<false>::kSmemBytes);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               QsaCfg<true>::kSmemBytes);
     if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (sparse attention kernels)", e);
     prepared[dev].store(1, std::memory_order_release);
   }
@@ -599,8 +616,10 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const dim3 grid((unsigned)((long long)p->rows * p->num_kv_heads), (unsigned)r.splits, 1);
   cudaError_t e = p->dtype == ATREX_FA_E4M3
-                      ? launch_kernel(atrex_sm100_qsa_kernel<true>, grid, dim3(kThreads), kSmemBytes, stream, k)
-                      : launch_kernel(atrex_sm100_qsa_kernel<false>, grid, dim3(kThreads), kSmemBytes, stream, k);
+                      ? launch_kernel(atrex_sm100_qsa_kernel<true>, grid, dim3(QsaCfg<true>::kThreads),
+                                      QsaCfg<true>::kSmemBytes, stream, k)
+                      : launch_kernel(atrex_sm100_qsa_kernel<false>, grid, dim3(QsaCfg<false>::kThreads),
+                                      QsaCfg<false>::kSmemBytes, stream, k);
   if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention kernel", e);
   if (r.splits > 1) {
     const long long slots = (long long)p->rows * p->num_q_heads;
