@@ -63,7 +63,9 @@ template <bool kFp8>
 struct QsaCfg {
   static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS;
   static constexpr int kThreads = kWarps * 32;
-  static constexpr int kWarpBytes = kFp8 ? kStages * 2 * (kTile * kD) + kOperandBytes : kStages * 2 * kOperandBytes;
+  static constexpr int kRawBytes = kStages * 2 * (kTile * kD);        // E4M3: kStages x (K + V) as bytes
+  static constexpr int kMergeBytes = ((16 * (kD + 2) * 4 + 1023) / 1024) * 1024;
+  static constexpr int kWarpBytes = kFp8 ? (kRawBytes > kMergeBytes ? kRawBytes : kMergeBytes) : kStages * 2 * kOperandBytes;
   static constexpr int kMetaBytes = kWarps * kStages * kTile * 8;   // per warp and stage: 16 row offsets (int64, -1 = does not count)
   static constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
   static_assert(16 * (kD + 2) * 4 <= kWarpBytes, "merge buffer aliases the tile buffers");
@@ -102,6 +104,23 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint32_t (&a
       "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// Two E4M3 bytes of `word` (selected by a byte-permute pattern) -> two FP16, exact.
+template <uint32_t kSelector>
+__device__ __forceinline__ uint32_t e4m3_pair_to_f16x2(uint32_t word) {
+  const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)__byte_perm(word, 0u, kSelector), __NV_E4M3);
+  return (uint32_t)h2.x | ((uint32_t)h2.y << 16);
 }
 
 // 16 E4M3 bytes -> 16 BF16 (two 16-byte vectors), exact.
@@ -199,7 +218,7 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   constexpr int kRawOperand = kTile * kRowBytes;       // raw bytes of one K or V tile
   // BF16: stage s holds K at s * 2 * kOperandBytes, V right behind.  E4M3: raw stage s at s * 2 * kRawOperand
   // (K then V); the widened tile (K then V) sits behind the raw stages.
-  static_assert(!kFp8 || kStages * 2 * (kTile * kD) + kOperandBytes <= kWarpBytes, "raw stages + the widened V tile fit");
+  static_assert(!kFp8 || kStages * 2 * (kTile * kD) <= kWarpBytes, "the raw stages fit");
   auto raw_k = [&](int s) { return my + s * 2 * kRawOperand; };
   auto raw_v = [&](int s) { return my + s * 2 * kRawOperand + kRawOperand; };
 
@@ -224,8 +243,9 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
         const long long row_off = __shfl_sync(0xffffffffu, off, r);
         const bool ok = row_off >= 0;
         const long long byte = ok ? row_off + c * 16 : 0;
-        cp_async16(raw_k(s) + (c / 8) * (kTile * 128) + swz128(r, c % 8), kbase + byte, ok);   // MMA layout: used as it is
-        cp_async16(raw_v(s) + r * kRowBytes + c * 16, vbase + byte, ok);                       // plain rows: widened below
+        const uint32_t dst = (c / 8) * (kTile * 128) + swz128(r, c % 8);   // the MMA layout: both tiles are used raw
+        cp_async16(raw_k(s) + dst, kbase + byte, ok);
+        cp_async16(raw_v(s) + dst, vbase + byte, ok);
       }
     } else {
       // a row is 512 bytes = 32 chunks: one row per warp instruction, written in the swizzled MMA layout
@@ -273,26 +293,8 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     // which of the tile's 16 tokens count (bit r = token r)
     const unsigned live_mask = __ballot_sync(0xffffffffu, lane < kTile && my_meta[stage * kTile + lane] >= 0) & 0xFFFFu;
 
-    uint32_t k_addr, v_addr;
-    if (kFp8) {
-      // K is multiplied as E4M3 straight from its raw stage; V is widened into the BF16 tile behind the raw stages
-      // (P stays BF16: three mantissa bits are too few for the probabilities), swizzled for the MMA
-      uint8_t* wide_v = my + kStages * 2 * kRawOperand;
-#pragma unroll
-      for (int j = 0; j < kTile / 2; ++j) {
-        const int r = 2 * j + (lane >> 4), c = lane & 15;   // raw chunk c = elements 16c .. 16c + 15 = BF16 chunks 2c, 2c + 1
-        uint4 lo, hi;
-        widen_e4m3x16(*reinterpret_cast<const uint4*>(raw_v(stage) + r * kRowBytes + c * 16), lo, hi);
-        *reinterpret_cast<uint4*>(wide_v + ((2 * c) / 8) * (kTile * 128) + swz128(r, (2 * c) % 8)) = lo;
-        *reinterpret_cast<uint4*>(wide_v + ((2 * c + 1) / 8) * (kTile * 128) + swz128(r, (2 * c + 1) % 8)) = hi;
-      }
-      __syncwarp();
-      k_addr = smem_u32(raw_k(stage));
-      v_addr = smem_u32(wide_v);
-    } else {
-      k_addr = smem_u32(raw_k(stage));
-      v_addr = smem_u32(raw_v(stage));
-    }
+    // E4M3 tiles are multiplied from their raw stage: K by the E4M3 MMA, V converted in registers (below)
+    const uint32_t k_addr = smem_u32(raw_k(stage)), v_addr = smem_u32(raw_v(stage));
 
     // ---- S = Q K^T : 16 rows x 16 tokens ----
     // four independent accumulator pairs (one per 64-element block of the head dimension) instead of one chain
@@ -365,18 +367,43 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     // ---- O += P V : one 16-token step ----
     {
       uint32_t a[4];
-      a[0] = pack_bf16(s[0][0], s[0][1]);
-      a[1] = pack_bf16(s[0][2], s[0][3]);
-      a[2] = pack_bf16(s[1][0], s[1][1]);
-      a[3] = pack_bf16(s[1][2], s[1][3]);
+      if constexpr (kFp8) {
+        // E4M3 V: the transposing 16-bit ldmatrix hands a thread, per 16-byte chunk (16 head dimensions) and token
+        // half, the bytes V[2tq][2g], V[2tq][2g+1], V[2tq+1][2g], V[2tq+1][2g+1].  Bytes 0 and 2 are the B fragment
+        // of an MMA over the chunk's EVEN dimensions, bytes 1 and 3 of one over its ODD dimensions; each pair is
+        // widened to FP16 in registers (exact) and P is FP16 too.  No widened tile in shared memory; the accumulators
+        // come out with the chunk's dimensions interleaved, which the merge below undoes when it stores them.
+        a[0] = pack_f16(s[0][0], s[0][1]);
+        a[1] = pack_f16(s[0][2], s[0][3]);
+        a[2] = pack_f16(s[1][0], s[1][1]);
+        a[3] = pack_f16(s[1][2], s[1][3]);
 #pragma unroll
-      for (int kb = 0; kb < kD / 64; ++kb) {
+        for (int kb = 0; kb < kD / 128; ++kb) {
 #pragma unroll
-        for (int cp = 0; cp < 4; ++cp) {
-          uint32_t b0, b1, b2, b3;
-          ldmatrix_x4_trans(b0, b1, b2, b3, v_addr + kb * (kTile * 128) + swz128(v_lane_row, cp * 2 + v_lane_chunk));
-          mma_bf16_16816(o_acc[kb * 8 + cp * 2], a, b0, b1);
-          mma_bf16_16816(o_acc[kb * 8 + cp * 2 + 1], a, b2, b3);
+          for (int cp = 0; cp < 4; ++cp) {
+            uint32_t r0, r1, r2, r3;   // chunk c: tokens 0-7, 8-15; chunk c + 1: tokens 0-7, 8-15
+            ldmatrix_x4_trans(r0, r1, r2, r3, v_addr + kb * (kTile * 128) + swz128(v_lane_row, cp * 2 + v_lane_chunk));
+            const int c = kb * 8 + cp * 2;
+            mma_f16_16816(o_acc[2 * c], a, e4m3_pair_to_f16x2<0x4420>(r0), e4m3_pair_to_f16x2<0x4420>(r1));
+            mma_f16_16816(o_acc[2 * c + 1], a, e4m3_pair_to_f16x2<0x4431>(r0), e4m3_pair_to_f16x2<0x4431>(r1));
+            mma_f16_16816(o_acc[2 * c + 2], a, e4m3_pair_to_f16x2<0x4420>(r2), e4m3_pair_to_f16x2<0x4420>(r3));
+            mma_f16_16816(o_acc[2 * c + 3], a, e4m3_pair_to_f16x2<0x4431>(r2), e4m3_pair_to_f16x2<0x4431>(r3));
+          }
+        }
+      } else {
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int kb = 0; kb < kD / 64; ++kb) {
+#pragma unroll
+          for (int cp = 0; cp < 4; ++cp) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, v_addr + kb * (kTile * 128) + swz128(v_lane_row, cp * 2 + v_lane_chunk));
+            mma_bf16_16816(o_acc[kb * 8 + cp * 2], a, b0, b1);
+            mma_bf16_16816(o_acc[kb * 8 + cp * 2 + 1], a, b2, b3);
+          }
         }
       }
     }
@@ -398,9 +425,18 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   for (int hh = 0; hh < 2; ++hh) {
     const int r = g + hh * 8;
     float* dst = red_o + ((size_t)warp * 16 + r) * kD;
+    if constexpr (kFp8) {
+      // accumulator 2c holds the even, 2c + 1 the odd dimensions of 16-dimension chunk c: this thread's four are
+      // the consecutive dimensions 16c + 4tq .. + 3
 #pragma unroll
-    for (int n = 0; n < kD / 8; ++n)
-      *reinterpret_cast<float2*>(dst + n * 8 + 2 * tq) = make_float2(o_acc[n][2 * hh], o_acc[n][2 * hh + 1]);
+      for (int c = 0; c < kD / 16; ++c)
+        *reinterpret_cast<float4*>(dst + c * 16 + 4 * tq) =
+            make_float4(o_acc[2 * c][2 * hh], o_acc[2 * c + 1][2 * hh], o_acc[2 * c][2 * hh + 1], o_acc[2 * c + 1][2 * hh + 1]);
+    } else {
+#pragma unroll
+      for (int n = 0; n < kD / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8 + 2 * tq) = make_float2(o_acc[n][2 * hh], o_acc[n][2 * hh + 1]);
+    }
     if (tq == 0) {
       red_m[warp * 16 + r] = m_run[hh];
       red_l[warp * 16 + r] = l_run[hh];
