@@ -19,10 +19,11 @@
 //     while the next tile's copies are in flight; no block-wide barrier inside the loop;
 //   * tokens that do not count (hidden block, request id out of range, page outside the table or the pool) are
 //     zero-filled in shared memory and masked in S, so no address is formed from them;
-//   * E4M3 caches are copied as bytes (half the traffic); S = Q K^T runs on the E4M3 MMA (m16n8k32) straight
-//     from the raw K tile, V is widened to BF16 in shared memory when a tile is consumed (every E4M3 value is
-//     exact in BF16) and P V runs in BF16 like the other type; sm_scale carries the Q and K scales, v_scale
-//     multiplies the result;
+//   * E4M3 caches are copied as bytes (half the traffic) and nothing is widened in shared memory: S = Q K^T runs
+//     on the E4M3 MMA (m16n8k32) straight from the raw K tile; for P V the transposing ldmatrix reads the raw V
+//     tile, the bytes are widened to FP16 in registers (exact) and two FP16 MMAs per 16-byte chunk take its even
+//     and its odd head dimensions (P stays 16-bit: three mantissa bits are too few for the probabilities);
+//     sm_scale carries the Q and K scales, v_scale multiplies the result;
 //   * the warps' partial states merge through shared memory; the epilogue rounds A to BF16, multiplies by
 //     sigmoid(gate) and stores BF16 (or writes a normalised FP32 partial + log2 LSE for the split combine).
 #include <cuda_fp8.h>
@@ -40,8 +41,9 @@ constexpr int kTile = 16;                 // tokens per warp tile = four blocks
 // Measured on B200 (64 decode rows / 2048 prefill rows, device time per call): 4 warps x 2 stages 32.0 / 510 us,
 // 4 x 3 32.2 / 548 us, 6 x 2 33.1 / 496 us (E4M3 decode 41.6 / 40.7 / 36.9 us): six warps with double buffers.  The
 // E4M3 decode then went 37.2 -> 31.4 us with S = Q K^T on the E4M3 MMA (K not widened) and -> 27.3 us with eight
-// warps, which fit once K needs no widened tile; a third raw stage (31.0), skipping the O rescale when no row
-// maximum moved (32.6) and widening to FP16 instead of BF16 (39.7 against 37.0 before the E4M3 MMA) did not help.
+// warps, and -> 23.0 us with P V from the raw V tile (bytes widened to FP16 in registers); a third raw stage
+// (31.0), skipping the O rescale when no row maximum moved (32.6) and widening to FP16 instead of BF16 in shared
+// memory (39.7 against 37.0 before the E4M3 MMA) did not help.
 #ifndef ATREX_QSA_WARPS
 #define ATREX_QSA_WARPS 6
 #endif
@@ -56,9 +58,10 @@ constexpr int kQBytes = 16 * kD * 2;      // Q tile: 16 rows (8 or 12 used) x 25
 constexpr int kOperandBytes = kTile * kD * 2;          // one K or V tile as BF16: 8 KB
 constexpr int kStages = ATREX_QSA_STAGES;              // tiles resident per warp: one being consumed, the others in flight
 constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of every block's first row (-1 = does not count)
-// Per cache type.  A warp's region holds kStages x (K + V) tiles as BF16 (32 KB), or for E4M3 the raw stages (half
-// the bytes) and one widened V tile (24 KB): eight warps then fit where six BF16 warps do, and the E4M3 call, which
-// moves half the bytes and is bound by the warps' own pace per tile rather than by memory, gets a third more of them.
+// Per cache type.  A warp's region holds kStages x (K + V) tiles as BF16 (32 KB), or for E4M3 the raw stages (16 KB;
+// at least the 16.1 KB its share of the merge buffer needs): the E4M3 call, which moves half the bytes and is bound
+// by the warps' own pace per tile rather than by memory, runs eight warps, as many as 255 registers per thread allow
+// (ten or twelve warps at 168 registers spill: 29.4 / 26.2 us against 22.8).
 template <bool kFp8>
 struct QsaCfg {
   static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS;
@@ -121,24 +124,6 @@ template <uint32_t kSelector>
 __device__ __forceinline__ uint32_t e4m3_pair_to_f16x2(uint32_t word) {
   const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)__byte_perm(word, 0u, kSelector), __NV_E4M3);
   return (uint32_t)h2.x | ((uint32_t)h2.y << 16);
-}
-
-// 16 E4M3 bytes -> 16 BF16 (two 16-byte vectors), exact.
-__device__ __forceinline__ void widen_e4m3x16(const uint4& raw, uint4& lo, uint4& hi) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w[i] >> (16 * half)) & 0xFFFFu);
-      const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-      o[2 * i + half] = pack_bf16(f.x, f.y);
-    }
-  }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
 template <bool kFp8>
