@@ -26,6 +26,7 @@
 //     sm_scale carries the Q and K scales, v_scale multiplies the result;
 //   * the warps' partial states merge through shared memory; the epilogue rounds A to BF16, multiplies by
 //     sigmoid(gate) and stores BF16 (or writes a normalised FP32 partial + log2 LSE for the split combine).
+#include <cooperative_groups.h>
 #include <cuda_fp8.h>
 
 #include "atrex_qsa_sm100.h"
@@ -62,6 +63,8 @@ constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of ever
 // at least the 16.1 KB its share of the merge buffer needs): the E4M3 call, which moves half the bytes and is bound
 // by the warps' own pace per tile rather than by memory, runs eight warps, as many as 255 registers per thread allow
 // (ten or twelve warps at 168 registers spill: 29.4 / 26.2 us against 22.8).
+constexpr int kMaxClusterSplits = 8;                   // portable cluster size
+constexpr int kPartStride = kD + 4;                    // floats per (split, head) partial in the leader: A, then the LSE
 template <bool kFp8>
 struct QsaCfg {
   static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS;
@@ -73,6 +76,7 @@ struct QsaCfg {
   static constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
   static_assert(16 * (kD + 2) * 4 <= kWarpBytes, "merge buffer aliases the tile buffers");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
+  static_assert(kMaxClusterSplits * 12 * kPartStride * 4 <= kWarps * kWarpBytes, "the cluster's partials fit the leader's tile buffers");
 };
 
 struct QsaParams {
@@ -90,8 +94,10 @@ struct QsaParams {
   int32_t* status;
   long long q_row_stride, q_head_stride, kv_page_stride, kv_row_stride, kv_head_stride;
   int rows, hq, hkv, group, num_pages, page_size, batch, table_width, pos64, num_splits;
+  int cluster_combine;   // the CTAs of one (row, KV head) are a thread-block cluster and combine their splits themselves
   float scale_log2, v_scale;
 };
+
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
   const uint32_t bytes = valid ? 16u : 0u;   // 0: the destination is zero-filled and nothing is read
@@ -429,6 +435,97 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   }
   __syncthreads();
   const bool split_mode = p.num_splits > 1;
+  if (p.cluster_combine) {
+    // The splits of this (row, KV head) are the CTAs of one cluster: each normalises its own partial, all of them
+    // write theirs into the leader's shared memory (distributed shared memory; the leader's tile buffers are free
+    // once every CTA of the cluster has passed the first cluster barrier), and the leader combines, gates and stores.
+    // No second kernel and no scratch in global memory.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int kItems = (12 * (kD / 4) + kThreads - 1) / kThreads;   // (head, 4 dimensions) items per thread
+    float4 o_loc[kItems];
+    float lse_loc[kItems];
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const int idx = tid + k * kThreads;
+      o_loc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      lse_loc[k] = -INFINITY;
+      if (idx >= p.group * (kD / 4)) continue;
+      const int r = idx / (kD / 4), c4 = idx % (kD / 4);
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) m = fmaxf(m, red_m[w * 16 + r]);
+      const float m_use = m == -INFINITY ? 0.f : m;
+      float l = 0.f;
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float mw = red_m[w * 16 + r];
+        if (mw == -INFINITY) continue;
+        const float sc = fast_exp2(mw - m_use);
+        l += red_l[w * 16 + r] * sc;
+        const float4 ow = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * kD + c4 * 4);
+        o.x += ow.x * sc; o.y += ow.y * sc; o.z += ow.z * sc; o.w += ow.w * sc;
+      }
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      o_loc[k] = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+      lse_loc[k] = l > 0.f ? m_use + log2f(l) : -INFINITY;
+    }
+    __syncthreads();     // this CTA is done with its merge buffer
+    cluster.sync();      // and so is every CTA of the row: the leader's buffers may be written
+    float* part_local = reinterpret_cast<float*>(tiles);          // [split][12][kPartStride]
+    float* part = cluster.map_shared_rank(part_local, 0);
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const int idx = tid + k * kThreads;
+      if (idx >= p.group * (kD / 4)) continue;
+      const int r = idx / (kD / 4), c4 = idx % (kD / 4);
+      float* dst = part + ((size_t)split * 12 + r) * kPartStride;
+      *reinterpret_cast<float4*>(dst + c4 * 4) = o_loc[k];
+      if (c4 == 0) dst[kD] = lse_loc[k];
+    }
+    cluster.sync();      // all partials are in the leader's shared memory
+    if (split == 0) {
+#pragma unroll
+      for (int k = 0; k < kItems; ++k) {
+        const int idx = tid + k * kThreads;
+        if (idx >= p.group * (kD / 4)) continue;
+        const int r = idx / (kD / 4), c4 = idx % (kD / 4);
+        const long long slot = (long long)t * p.hq + h * p.group + r;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < p.num_splits; ++sp) mx = fmaxf(mx, part_local[((size_t)sp * 12 + r) * kPartStride + kD]);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float denom = 0.f;
+        if (mx != -INFINITY) {
+          for (int sp = 0; sp < p.num_splits; ++sp) {
+            const float* src = part_local + ((size_t)sp * 12 + r) * kPartStride;
+            const float l = src[kD];
+            if (l == -INFINITY) continue;
+            const float w = fast_exp2(l - mx);
+            denom += w;
+            const float4 a = *reinterpret_cast<const float4*>(src + c4 * 4);
+            acc.x += w * a.x; acc.y += w * a.y; acc.z += w * a.z; acc.w += w * a.w;
+          }
+        }
+        const float inv = denom > 0.f ? p.v_scale / denom : 0.f;
+        const uint2 graw = *reinterpret_cast<const uint2*>(p.gate + slot * kD + c4 * 4);
+        const float gt[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xFFFF0000u),
+                             __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xFFFF0000u)};
+        const float av[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+        float res[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a_bf16 = __bfloat162float(__float2bfloat16(av[i]));     // A leaves the attention as BF16
+          res[i] = a_bf16 * (1.f / (1.f + __expf(-gt[i])));
+        }
+        uint2 packed;
+        packed.x = pack_bf16(res[0], res[1]);
+        packed.y = pack_bf16(res[2], res[3]);
+        *reinterpret_cast<uint2*>(p.out + slot * kD + c4 * 4) = packed;
+      }
+    }
+    return;
+  }
   for (int idx = tid; idx < p.group * (kD / 4); idx += kThreads) {
     const int r = idx / (kD / 4), c4 = idx % (kD / 4);
     const int head = h * p.group + r;
@@ -514,6 +611,7 @@ atrex_sm100_qsa_combine_kernel(const __grid_constant__ QsaParams p) {
 
 struct QsaResolved {
   int splits, launches;
+  bool cluster;         // the splits of a row combine inside the attention kernel (one cluster per row and KV head)
   uint64_t off_lse, off_o, bytes;
 };
 
@@ -549,6 +647,52 @@ int qsa_check(const atrex_qsa_sm100_params* p) {
   return ATREX_FA_OK;
 }
 
+// Kernel attributes, once per device.
+cudaError_t qsa_prepare() {
+  static std::atomic<int> prepared[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || prepared[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QsaCfg<false>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QsaCfg<true>::kSmemBytes);
+  if (e == cudaSuccess) prepared[dev].store(1, std::memory_order_release);
+  return e;
+}
+
+// How many clusters of `splits` CTAs of the attention kernel this device can hold at once (one 200 KB CTA per SM and
+// a cluster inside one GPC); 0 when it cannot be asked (no device: the plan of a CPU-side test).  Asked once per
+// size, type and device.
+int qsa_resident_clusters(bool fp8, int splits) {
+  static std::atomic<int> cache[64][2][kMaxClusterSplits + 1];   // value + 1; 0 = not asked yet
+  int dev = 0;
+  if (splits < 2 || splits > kMaxClusterSplits || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  const int seen = cache[dev][fp8][splits].load(std::memory_order_acquire);
+  if (seen > 0) return seen - 1;
+  if (qsa_prepare() != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, (unsigned)splits, 1);
+  cfg.blockDim = dim3(fp8 ? QsaCfg<true>::kThreads : QsaCfg<false>::kThreads);
+  cfg.dynamicSmemBytes = fp8 ? QsaCfg<true>::kSmemBytes : QsaCfg<false>::kSmemBytes;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 1;
+  attr.val.clusterDim.y = (unsigned)splits;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  const cudaError_t e = fp8 ? cudaOccupancyMaxActiveClusters(&clusters, atrex_sm100_qsa_kernel<true>, &cfg)
+                            : cudaOccupancyMaxActiveClusters(&clusters, atrex_sm100_qsa_kernel<false>, &cfg);
+  if (e != cudaSuccess) {
+    cudaGetLastError();   // the query failed, nothing was launched: not this call's error
+    clusters = 0;
+  }
+  cache[dev][fp8][splits].store(clusters + 1, std::memory_order_release);
+  return clusters;
+}
+
 void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) {
   int splits = p->num_splits;
   if (splits == 0) {
@@ -559,11 +703,17 @@ void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) 
     splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
   }
   r->splits = splits;
-  r->launches = splits > 1 ? 2 : 1;
+  // The splits of a row combine inside the attention kernel when every row's cluster can be resident at once (one
+  // wave, as for the split count itself); otherwise through scratch and the combine kernel.
+  const long long clusters = (long long)p->rows * p->num_kv_heads;
+  r->cluster = splits >= 2 && splits <= kMaxClusterSplits &&
+               qsa_resident_clusters(p->dtype == ATREX_FA_E4M3, splits) >= clusters;
+  r->launches = splits > 1 && !r->cluster ? 2 : 1;
   const uint64_t slots = (uint64_t)p->rows * p->num_q_heads;
   r->off_lse = 0;
-  r->off_o = splits > 1 ? (4ull * splits * slots + 255) / 256 * 256 : 0;
-  r->bytes = splits > 1 ? r->off_o + 4ull * splits * slots * kD : 0;
+  const bool scratch = splits > 1 && !r->cluster;   // partials in global memory only for the combine kernel
+  r->off_o = scratch ? (4ull * splits * slots + 255) / 256 * 256 : 0;
+  r->bytes = scratch ? r->off_o + 4ull * splits * slots * kD : 0;
 }
 
 }  // namespace
@@ -603,17 +753,9 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   if (r.bytes > 0 && (workspace == nullptr || workspace_bytes < r.bytes || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
     return report_failure(ATREX_FA_WORKSPACE_TOO_SMALL, "workspace missing, misaligned or too small");
   if (p->rows == 0) return ATREX_FA_OK;
-  static std::atomic<int> prepared[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !prepared[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         QsaCfg<false>::kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               QsaCfg<true>::kSmemBytes);
+  {
+    const cudaError_t e = qsa_prepare();
     if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "cudaFuncSetAttribute (sparse attention kernels)", e);
-    prepared[dev].store(1, std::memory_order_release);
   }
   QsaParams k = {};
   k.q = p->q; k.k = p->k_cache; k.v = p->v_cache; k.ids = p->block_ids; k.pos = p->query_positions;
@@ -622,7 +764,7 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   k.out = static_cast<__nv_bfloat16*>(p->out);
   k.status = p->device_status;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  if (r.splits > 1) {
+  if (r.bytes > 0) {
     k.part_lse = reinterpret_cast<float*>(ws + r.off_lse);
     k.part_o = reinterpret_cast<float*>(ws + r.off_o);
   }
@@ -632,17 +774,30 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   k.num_pages = p->num_pages; k.page_size = p->page_size; k.batch = p->batch; k.table_width = p->table_width;
   k.pos64 = p->positions_are_int64 ? 1 : 0;
   k.num_splits = r.splits;
+  k.cluster_combine = r.cluster ? 1 : 0;
   k.scale_log2 = p->sm_scale * kLog2e;
   k.v_scale = p->v_scale;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const dim3 grid((unsigned)((long long)p->rows * p->num_kv_heads), (unsigned)r.splits, 1);
-  cudaError_t e = p->dtype == ATREX_FA_E4M3
-                      ? launch_kernel(atrex_sm100_qsa_kernel<true>, grid, dim3(QsaCfg<true>::kThreads),
-                                      QsaCfg<true>::kSmemBytes, stream, k)
-                      : launch_kernel(atrex_sm100_qsa_kernel<false>, grid, dim3(QsaCfg<false>::kThreads),
-                                      QsaCfg<false>::kSmemBytes, stream, k);
+  const bool fp8 = p->dtype == ATREX_FA_E4M3;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(fp8 ? QsaCfg<true>::kThreads : QsaCfg<false>::kThreads);
+  cfg.dynamicSmemBytes = fp8 ? QsaCfg<true>::kSmemBytes : QsaCfg<false>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  if (r.cluster) {   // the CTAs (x, 0 .. splits - 1) of one row and KV head form a cluster
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = (unsigned)r.splits;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = fp8 ? cudaLaunchKernelEx(&cfg, atrex_sm100_qsa_kernel<true>, k)
+                      : cudaLaunchKernelEx(&cfg, atrex_sm100_qsa_kernel<false>, k);
   if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention kernel", e);
-  if (r.splits > 1) {
+  if (r.splits > 1 && !r.cluster) {
     const long long slots = (long long)p->rows * p->num_q_heads;
     e = launch_kernel(atrex_sm100_qsa_combine_kernel, dim3((unsigned)((slots + 7) / 8)), dim3(256), 0, stream, k);
     if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention combine kernel", e);

@@ -227,10 +227,13 @@ def test_ragged_prefill_rows(page, hkv, ratio, fp8):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fp8", [False, True])
-@pytest.mark.parametrize("rows,splits", [(1, 0), (4, 0), (8, 5), (32, 16), (7, 1)])
+@pytest.mark.parametrize("rows,splits", [(1, 0), (4, 0), (8, 5), (32, 16), (7, 1), (8, 8), (6, 3), (20, 7), (33, 0)])
 def test_decode_rows_with_split_token_lists(rows, splits, fp8):
-    """Few rows, every row with a full list of 512 blocks (2048+ tokens): the token list is split over CTAs and
-    merged by the combine kernel; automatic and explicit split counts, scratch poisoned beforehand."""
+    """Few rows, every row with a full list of 512 blocks (2048+ tokens): the token list is split over CTAs.  Up
+    to eight splits of a row run as one thread-block cluster and combine in the leader's shared memory when every
+    row's cluster can be resident at once (2, 3, 5 and 8 splits here); otherwise (16 splits, or 40 clusters of 7)
+    the partials go through scratch and the combine kernel; automatic and explicit split counts, scratch poisoned
+    beforehand."""
     from atrex.src.nvidia.qsa.sm100 import runtime
 
     case, data, kwargs = _random_case(rows, 128, 2, 12, fp8, seed=rows + splits, full=True)
