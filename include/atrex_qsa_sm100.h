@@ -64,12 +64,15 @@ typedef struct atrex_qsa_sm100_params {
 typedef struct atrex_qsa_sm100_plan_info {
   int32_t num_splits;       /* resolved split count                */
   int32_t kernel_launches;  /* kernels one forward call enqueues   */
-  uint64_t workspace_bytes; /* scratch forward needs (0 unsplit)   */
+  uint64_t workspace_bytes; /* scratch forward needs (0 unsplit, and 0 when the 2 .. 8 splits of a row run as one
+                               thread-block cluster and combine inside the attention kernel) */
 } atrex_qsa_sm100_plan_info;
 
 ATREX_FA_API int atrex_qsa_sm100_abi_version(void);
 ATREX_FA_API size_t atrex_qsa_sm100_params_bytes(void);
-/* Validates `p` and resolves the split count from graph-static sizes (rows, heads, SM count).  Launches nothing. */
+/* Validates `p` and resolves the split count from graph-static sizes (rows, heads, SM count).  Launches nothing.
+ * Whether the splits combine in a cluster depends on how many clusters the CURRENT device can hold at once, so plan
+ * on the device that will run the call (without a device the plan assumes the scratch path). */
 ATREX_FA_API int atrex_qsa_sm100_plan(const atrex_qsa_sm100_params* p, atrex_qsa_sm100_plan_info* plan);
 /* Enqueues the call on `stream`; `workspace` is caller scratch of plan.workspace_bytes, 256-byte aligned, contents
  * irrelevant.  Detail of a failure: atrex_fa_sm100_last_error(). */
