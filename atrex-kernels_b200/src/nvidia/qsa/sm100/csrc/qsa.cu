@@ -63,6 +63,7 @@ constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of ever
 // at least the 16.1 KB its share of the merge buffer needs): the E4M3 call, which moves half the bytes and is bound
 // by the warps' own pace per tile rather than by memory, runs eight warps, as many as 255 registers per thread allow
 // (ten or twelve warps at 168 registers spill: 29.4 / 26.2 us against 22.8).
+constexpr int kRowTilesMax = (kTopk * 4 + 3 + kTile - 1) / kTile;   // tiles of the longest token list a row can have
 constexpr int kMaxClusterSplits = 8;                   // portable cluster size
 constexpr int kPartStride = kD + 4;                    // floats per (split, head) partial in the leader: A, then the LSE
 template <bool kFp8>
@@ -701,6 +702,12 @@ void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) 
     const long long ctas = (long long)p->rows * p->num_kv_heads;
     const long long want = ctas > 0 ? sm_count / ctas : 1;
     splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
+    // A CTA's time is the number of rounds its warps make over its tiles (a full list has kRowTilesMax tiles): the
+    // fewest splits that still give that many rounds leave less to combine (16 rows, six warps: 9 splits 14.4 us
+    // per call, 8 splits 13.6, 7 splits - a fourth round - 15.8).
+    const int warps = p->dtype == ATREX_FA_E4M3 ? QsaCfg<true>::kWarps : QsaCfg<false>::kWarps;
+    auto rounds = [&](int n) { return ((kRowTilesMax + n - 1) / n + warps - 1) / warps; };
+    while (splits > 1 && rounds(splits - 1) == rounds(splits)) --splits;
   }
   r->splits = splits;
   // The splits of a row combine inside the attention kernel when every row's cluster can be resident at once (one
