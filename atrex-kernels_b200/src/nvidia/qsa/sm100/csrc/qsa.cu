@@ -12,8 +12,9 @@
 //   * the CTA first resolves its share of the row's blocks to cache addresses (block id -> first token -> page
 //     table -> address; a four-token block never straddles a page) into shared memory: two dependent global
 //     loads once per CTA instead of once per tile on every warp's critical path;
-//   * each of the six (BF16 cache) or eight (E4M3 cache) warps is then its own pipeline: it takes every sixth /
-//     eighth 16-token tile (four blocks),
+//   * each of the six or eight warps (eight for an E4M3 cache and for BF16 calls of one wave with long token
+//     lists, which keep a ring of three operand tiles instead of two K + V stages) is then its own pipeline: it
+//     takes every sixth / eighth 16-token tile (four blocks),
 //     fetches K and V with 16-byte cp.async copies into its private double buffer (a row is one coalesced
 //     512-byte request) and computes S = Q K^T, the online softmax (log2 domain) and O += P V with mma.sync
 //     while the next tile's copies are in flight; no block-wide barrier inside the loop;
@@ -66,14 +67,21 @@ constexpr int kBlockOffBytes = (kTopk + 4) * 8;        // element offset of ever
 constexpr int kRowTilesMax = (kTopk * 4 + 3 + kTile - 1) / kTile;   // tiles of the longest token list a row can have
 constexpr int kMaxClusterSplits = 8;                   // portable cluster size
 constexpr int kPartStride = kD + 4;                    // floats per (split, head) partial in the leader: A, then the LSE
-template <bool kFp8>
+// kRing: the warp's region is a ring of THREE operand tiles (K(i), V(i), K(i+1) -> V(i), K(i+1), V(i+1) -> ...) instead
+// of two whole (K + V) stages: the same bytes in flight in a quarter less shared memory, so that the BF16 kernel runs
+// eight warps as well.  It pays two waits, two barriers and two address passes per tile instead of one, which only
+// the BF16 call of ONE wave (decode) wins back: 33.0 -> 30.7 us, against 0.499 -> 0.517 ms for a prefill chunk and
+// 22.7 -> 25.4 us for the E4M3 decode, which has its eight warps anyway.  So the ring serves BF16 single-wave calls.
+template <bool kFp8, bool kRing>
 struct QsaCfg {
-  static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS;
+  static constexpr int kWarps = kFp8 ? ATREX_QSA_WARPS_FP8 : (kRing ? ATREX_QSA_WARPS_FP8 : ATREX_QSA_WARPS);
   static constexpr int kThreads = kWarps * 32;
+  static constexpr int kOpBytes = kTile * kD * (kFp8 ? 1 : 2);        // one K or V tile of 16 tokens
   static constexpr int kRawBytes = kStages * 2 * (kTile * kD);        // E4M3: kStages x (K + V) as bytes
   static constexpr int kMergeBytes = ((16 * (kD + 2) * 4 + 1023) / 1024) * 1024;
-  static constexpr int kWarpBytes = kFp8 ? (kRawBytes > kMergeBytes ? kRawBytes : kMergeBytes) : kStages * 2 * kOperandBytes;
-  static constexpr int kMetaBytes = kWarps * kStages * kTile * 8;   // per warp and stage: 16 row offsets (int64, -1 = does not count)
+  static constexpr int kTileBytes = kRing ? 3 * kOpBytes : (kFp8 ? kRawBytes : kStages * 2 * kOperandBytes);
+  static constexpr int kWarpBytes = kTileBytes > kMergeBytes ? kTileBytes : kMergeBytes;
+  static constexpr int kMetaBytes = kWarps * kStages * kTile * 8;   // per warp, two tiles: 16 row offsets (int64, -1 = does not count)
   static constexpr int kSmemBytes = kQBytes + kWarps * kWarpBytes + kMetaBytes + kBlockOffBytes;
   static_assert(16 * (kD + 2) * 4 <= kWarpBytes, "merge buffer aliases the tile buffers");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
@@ -133,10 +141,12 @@ __device__ __forceinline__ uint32_t e4m3_pair_to_f16x2(uint32_t word) {
   return (uint32_t)h2.x | ((uint32_t)h2.y << 16);
 }
 
-template <bool kFp8>
-__global__ void __launch_bounds__(QsaCfg<kFp8>::kThreads, 1)
+template <bool kFp8, bool kRing>
+__global__ void __launch_bounds__(QsaCfg<kFp8, kRing>::kThreads, 1)
 atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
-  constexpr int kWarps = QsaCfg<kFp8>::kWarps, kThreads = QsaCfg<kFp8>::kThreads, kWarpBytes = QsaCfg<kFp8>::kWarpBytes;
+  using Cfg = QsaCfg<kFp8, kRing>;
+  constexpr int kWarps = Cfg::kWarps, kThreads = Cfg::kThreads, kWarpBytes = Cfg::kWarpBytes;
+  static_assert(kStages == 2, "two tiles of row offsets per warp");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_smem = smem;
   uint8_t* tiles = smem + kQBytes;
@@ -254,6 +264,45 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
     cp_async_commit();
   };
 
+  // ---- the ring variant: operand 2i is K of the warp's i-th tile, 2i + 1 its V; operand n lives in buffer n % 3;
+  // one copy group per operand (an empty one where no tile is left)
+  auto ring = [&](int n) { return my + (n % 3) * Cfg::kOpBytes; };
+  auto tile_offsets = [&](int ti, int slot) {   // the 16 tokens of tile `ti` -> row offsets in meta slot `slot`
+    if (lane < kTile) {
+      long long off = -1;
+      const int i = ti * kTile + lane;
+      if (ti < tile_hi && i < n_tok) {
+        const long long base = block_off[(i >> 2) - tile_lo * 4];
+        if (base >= 0) off = base + (i & 3) * p.kv_row_stride;
+      }
+      my_meta[slot * kTile + lane] = off;
+    }
+    __syncwarp();
+  };
+  auto issue_operand = [&](const void* tensor, int slot, uint8_t* dst_tile, bool exists) {
+    if (exists) {
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(tensor);
+      const long long off = lane < kTile ? my_meta[slot * kTile + lane] : -1;
+      if (kFp8) {
+#pragma unroll
+        for (int j = 0; j < kTile / 2; ++j) {
+          const int r = 2 * j + (lane >> 4), c = lane & 15;
+          const long long row_off = __shfl_sync(0xffffffffu, off, r);
+          const bool ok = row_off >= 0;
+          cp_async16(dst_tile + (c / 8) * (kTile * 128) + swz128(r, c % 8), base + (ok ? row_off + c * 16 : 0), ok);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < kTile; ++r) {
+          const long long row_off = __shfl_sync(0xffffffffu, off, r);
+          const bool ok = row_off >= 0;
+          cp_async16(dst_tile + (lane / 8) * (kTile * 128) + swz128(r, lane % 8), base + (ok ? row_off * 2 + lane * 16 : 0), ok);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o_acc[kD / 8][4];
 #pragma unroll
@@ -270,23 +319,38 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
   // are complete" always means "this iteration's tile has landed".
   int stage = 0;
   const int first = tile_lo + warp;
-  if (first < tile_hi) issue_tile(first, 0);
+  if constexpr (kRing) {
+    // K and V of the warp's first tile, K of its second
+    tile_offsets(first, 0);
+    issue_operand(p.k, 0, ring(0), first < tile_hi);
+    issue_operand(p.v, 0, ring(1), first < tile_hi);
+    tile_offsets(first + kWarps, 1);
+    issue_operand(p.k, 1, ring(2), first + kWarps < tile_hi);
+  } else {
+    if (first < tile_hi) issue_tile(first, 0);
 #pragma unroll
-  for (int d = 1; d < kStages - 1; ++d) {
-    if (first + d * kWarps < tile_hi) issue_tile(first + d * kWarps, d);
-    else cp_async_commit();
+    for (int d = 1; d < kStages - 1; ++d) {
+      if (first + d * kWarps < tile_hi) issue_tile(first + d * kWarps, d);
+      else cp_async_commit();
+    }
   }
-  for (int ti = first; ti < tile_hi; ti += kWarps) {
-    const int ahead = ti + (kStages - 1) * kWarps;
-    if (ahead < tile_hi) issue_tile(ahead, (stage + kStages - 1) % kStages);
-    else cp_async_commit();
-    cp_async_wait<kStages - 1>();
+  int n_op = 0;   // ring: the operand about to be consumed (2i)
+  for (int ti = first; ti < tile_hi; ti += kWarps, n_op += 2) {
+    if constexpr (kRing) {
+      cp_async_wait<2>();                                // all but the two newest groups: K(i) has landed
+    } else {
+      const int ahead = ti + (kStages - 1) * kWarps;
+      if (ahead < tile_hi) issue_tile(ahead, (stage + kStages - 1) % kStages);
+      else cp_async_commit();
+      cp_async_wait<kStages - 1>();
+    }
     __syncwarp();
-    // which of the tile's 16 tokens count (bit r = token r)
+    // which of the tile's 16 tokens count (bit r = token r); the ring keeps tile i's offsets in slot i & 1
     const unsigned live_mask = __ballot_sync(0xffffffffu, lane < kTile && my_meta[stage * kTile + lane] >= 0) & 0xFFFFu;
 
     // E4M3 tiles are multiplied from their raw stage: K by the E4M3 MMA, V converted in registers (below)
-    const uint32_t k_addr = smem_u32(raw_k(stage)), v_addr = smem_u32(raw_v(stage));
+    const uint32_t k_addr = smem_u32(kRing ? ring(n_op) : raw_k(stage));
+    const uint32_t v_addr = smem_u32(kRing ? ring(n_op + 1) : raw_v(stage));
 
     // ---- S = Q K^T : 16 rows x 16 tokens ----
     // four independent accumulator pairs (one per 64-element block of the head dimension) instead of one chain
@@ -316,6 +380,11 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
           mma_bf16_16816(s4[acc][1], a, b2, b3);
         }
       }
+    }
+    if constexpr (kRing) {
+      // K(i) is consumed: its buffer takes V of the next tile (operand 2i + 3), whose offsets are in the other slot
+      __syncwarp();
+      issue_operand(p.v, stage ^ 1, ring(n_op + 3), ti + kWarps < tile_hi);
     }
     float s[2][4];
 #pragma unroll
@@ -357,6 +426,10 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
       o_acc[n][3] *= alpha[1];
     }
     // ---- O += P V : one 16-token step ----
+    if constexpr (kRing) {
+      cp_async_wait<2>();                                // all but the two newest groups: V(i) has landed
+      __syncwarp();
+    }
     {
       uint32_t a[4];
       if constexpr (kFp8) {
@@ -400,6 +473,11 @@ atrex_sm100_qsa_kernel(const __grid_constant__ QsaParams p) {
       }
     }
     __syncwarp();          // every lane is done with this stage before the next iteration's copies may land in it
+    if constexpr (kRing) {
+      // V(i) is consumed: its buffer takes K of the tile after next (operand 2i + 4), whose offsets replace this tile's
+      tile_offsets(ti + 2 * kWarps, stage);
+      issue_operand(p.k, stage, ring(n_op + 4), ti + 2 * kWarps < tile_hi);
+    }
     stage = (stage + 1) % kStages;
   }
 #pragma unroll
@@ -612,6 +690,7 @@ atrex_sm100_qsa_combine_kernel(const __grid_constant__ QsaParams p) {
 
 struct QsaResolved {
   int splits, launches;
+  int variant;          // QsaVariant
   bool cluster;         // the splits of a row combine inside the attention kernel (one cluster per row and KV head)
   uint64_t off_lse, off_o, bytes;
 };
@@ -648,6 +727,27 @@ int qsa_check(const atrex_qsa_sm100_params* p) {
   return ATREX_FA_OK;
 }
 
+// The three instantiations: BF16 with two-stage buffers (six warps), BF16 with the operand ring (eight warps; calls of
+// one wave), E4M3 (eight warps).
+enum QsaVariant { kBf16Stages = 0, kBf16Ring = 1, kE4m3 = 2, kVariants = 3 };
+struct QsaLaunchShape {
+  const void* kernel;
+  int threads, smem, warps;
+};
+QsaLaunchShape qsa_shape(int variant) {
+  switch (variant) {
+    case kBf16Ring:
+      return {reinterpret_cast<const void*>(&atrex_sm100_qsa_kernel<false, true>), QsaCfg<false, true>::kThreads,
+              QsaCfg<false, true>::kSmemBytes, QsaCfg<false, true>::kWarps};
+    case kE4m3:
+      return {reinterpret_cast<const void*>(&atrex_sm100_qsa_kernel<true, false>), QsaCfg<true, false>::kThreads,
+              QsaCfg<true, false>::kSmemBytes, QsaCfg<true, false>::kWarps};
+    default:
+      return {reinterpret_cast<const void*>(&atrex_sm100_qsa_kernel<false, false>), QsaCfg<false, false>::kThreads,
+              QsaCfg<false, false>::kSmemBytes, QsaCfg<false, false>::kWarps};
+  }
+}
+
 // Kernel attributes, once per device.
 cudaError_t qsa_prepare() {
   static std::atomic<int> prepared[64];
@@ -655,27 +755,29 @@ cudaError_t qsa_prepare() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64 || prepared[dev].load(std::memory_order_acquire)) return cudaSuccess;
-  e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QsaCfg<false>::kSmemBytes);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(atrex_sm100_qsa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QsaCfg<true>::kSmemBytes);
+  for (int v = 0; v < kVariants && e == cudaSuccess; ++v) {
+    const QsaLaunchShape sh = qsa_shape(v);
+    e = cudaFuncSetAttribute(sh.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sh.smem);
+  }
   if (e == cudaSuccess) prepared[dev].store(1, std::memory_order_release);
   return e;
 }
 
-// How many clusters of `splits` CTAs of the attention kernel this device can hold at once (one 200 KB CTA per SM and
-// a cluster inside one GPC); 0 when it cannot be asked (no device: the plan of a CPU-side test).  Asked once per
-// size, type and device.
-int qsa_resident_clusters(bool fp8, int splits) {
-  static std::atomic<int> cache[64][2][kMaxClusterSplits + 1];   // value + 1; 0 = not asked yet
+// How many clusters of `splits` CTAs of the attention kernel this device can hold at once (one CTA of up to 214 KB per
+// SM and a cluster inside one GPC); 0 when it cannot be asked (no device: the plan of a CPU-side test).  Asked once
+// per size, variant and device.
+int qsa_resident_clusters(int variant, int splits) {
+  static std::atomic<int> cache[64][kVariants][kMaxClusterSplits + 1];   // value + 1; 0 = not asked yet
   int dev = 0;
   if (splits < 2 || splits > kMaxClusterSplits || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  const int seen = cache[dev][fp8][splits].load(std::memory_order_acquire);
+  const int seen = cache[dev][variant][splits].load(std::memory_order_acquire);
   if (seen > 0) return seen - 1;
   if (qsa_prepare() != cudaSuccess) return 0;
+  const QsaLaunchShape sh = qsa_shape(variant);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1, (unsigned)splits, 1);
-  cfg.blockDim = dim3(fp8 ? QsaCfg<true>::kThreads : QsaCfg<false>::kThreads);
-  cfg.dynamicSmemBytes = fp8 ? QsaCfg<true>::kSmemBytes : QsaCfg<false>::kSmemBytes;
+  cfg.blockDim = dim3(sh.threads);
+  cfg.dynamicSmemBytes = sh.smem;
   cudaLaunchAttribute attr = {};
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 1;
@@ -684,37 +786,40 @@ int qsa_resident_clusters(bool fp8, int splits) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  const cudaError_t e = fp8 ? cudaOccupancyMaxActiveClusters(&clusters, atrex_sm100_qsa_kernel<true>, &cfg)
-                            : cudaOccupancyMaxActiveClusters(&clusters, atrex_sm100_qsa_kernel<false>, &cfg);
-  if (e != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&clusters, sh.kernel, &cfg) != cudaSuccess) {
     cudaGetLastError();   // the query failed, nothing was launched: not this call's error
     clusters = 0;
   }
-  cache[dev][fp8][splits].store(clusters + 1, std::memory_order_release);
+  cache[dev][variant][splits].store(clusters + 1, std::memory_order_release);
   return clusters;
 }
 
 void qsa_resolve(const atrex_qsa_sm100_params* p, int sm_count, QsaResolved* r) {
   int splits = p->num_splits;
+  const bool fp8 = p->dtype == ATREX_FA_E4M3;
+  const long long ctas = (long long)p->rows * p->num_kv_heads;
+  // BF16 calls of one wave whose CTAs have long token lists (at most four splits of a row: 33 tiles or more per CTA)
+  // take the operand ring with eight warps (see QsaCfg); with short lists the ring's longer start costs more than
+  // the warps bring (16 rows: 15.8 us against 13.5 with the two-stage kernel).
+  const long long upper = splits == 0 ? (ctas > 0 ? sm_count / ctas : 0) : splits;   // splits, or the most that fit
+  const bool ring = !fp8 && ctas > 0 && upper >= 1 && upper <= 4 && ctas * (splits == 0 ? 1 : splits) <= sm_count;
+  r->variant = fp8 ? kE4m3 : (ring ? kBf16Ring : kBf16Stages);
   if (splits == 0) {
     // rows x KV heads CTAs, one resident per SM: split the token lists while all CTAs still run in ONE wave
     // (measured on 64 decode rows: 2 splits = 128 CTAs 37 us, 3 splits = 192 CTAs in two waves 46 us)
-    const long long ctas = (long long)p->rows * p->num_kv_heads;
     const long long want = ctas > 0 ? sm_count / ctas : 1;
     splits = (int)(want < 1 ? 1 : (want > kMaxSplits ? kMaxSplits : want));
     // A CTA's time is the number of rounds its warps make over its tiles (a full list has kRowTilesMax tiles): the
     // fewest splits that still give that many rounds leave less to combine (16 rows, six warps: 9 splits 14.4 us
     // per call, 8 splits 13.6, 7 splits - a fourth round - 15.8).
-    const int warps = p->dtype == ATREX_FA_E4M3 ? QsaCfg<true>::kWarps : QsaCfg<false>::kWarps;
+    const int warps = qsa_shape(r->variant).warps;
     auto rounds = [&](int n) { return ((kRowTilesMax + n - 1) / n + warps - 1) / warps; };
     while (splits > 1 && rounds(splits - 1) == rounds(splits)) --splits;
   }
   r->splits = splits;
   // The splits of a row combine inside the attention kernel when every row's cluster can be resident at once (one
   // wave, as for the split count itself); otherwise through scratch and the combine kernel.
-  const long long clusters = (long long)p->rows * p->num_kv_heads;
-  r->cluster = splits >= 2 && splits <= kMaxClusterSplits &&
-               qsa_resident_clusters(p->dtype == ATREX_FA_E4M3, splits) >= clusters;
+  r->cluster = splits >= 2 && splits <= kMaxClusterSplits && qsa_resident_clusters(r->variant, splits) >= ctas;
   r->launches = splits > 1 && !r->cluster ? 2 : 1;
   const uint64_t slots = (uint64_t)p->rows * p->num_q_heads;
   r->off_lse = 0;
@@ -786,11 +891,11 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
   k.v_scale = p->v_scale;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const dim3 grid((unsigned)((long long)p->rows * p->num_kv_heads), (unsigned)r.splits, 1);
-  const bool fp8 = p->dtype == ATREX_FA_E4M3;
+  const QsaLaunchShape sh = qsa_shape(r.variant);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(fp8 ? QsaCfg<true>::kThreads : QsaCfg<false>::kThreads);
-  cfg.dynamicSmemBytes = fp8 ? QsaCfg<true>::kSmemBytes : QsaCfg<false>::kSmemBytes;
+  cfg.blockDim = dim3(sh.threads);
+  cfg.dynamicSmemBytes = sh.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr = {};
   if (r.cluster) {   // the CTAs (x, 0 .. splits - 1) of one row and KV head form a cluster
@@ -801,8 +906,8 @@ int atrex_qsa_sm100_forward(const atrex_qsa_sm100_params* p, void* workspace, ui
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = fp8 ? cudaLaunchKernelEx(&cfg, atrex_sm100_qsa_kernel<true>, k)
-                      : cudaLaunchKernelEx(&cfg, atrex_sm100_qsa_kernel<false>, k);
+  void* args[] = {&k};
+  cudaError_t e = cudaLaunchKernelExC(&cfg, sh.kernel, args);
   if (e != cudaSuccess) return report_failure(ATREX_FA_CUDA_ERROR, "launch of the sparse attention kernel", e);
   if (r.splits > 1 && !r.cluster) {
     const long long slots = (long long)p->rows * p->num_q_heads;
