@@ -117,7 +117,7 @@ WORKLOADS = {
 # to the K/V bytes a launch reads, so the ratio carries to the full-size launch).
 NCU_TRAFFIC_RATIO = {"kv_write": 1.0, "kv_write_small": 1.0, "kv_write_fp8": 1.0,
                      "decode_q1": 1.0250, "decode_q1_small": 1.0250, "decode_q4_window": 1.0553, "decode_q4_small": 1.0553,
-                     "qsa_decode": 1.0, "qsa_decode_small": 1.0}
+                     "qsa_decode": 1.0226, "qsa_decode_fp8": 1.0114, "qsa_decode_small": 1.0}
 # The tensor-bound BF16 prefill kernel: DRAM bytes per byte of (Q + O + K + V), from the captures of prefill_small
 # (0.963) and of two 32768-token requests (0.988); K/V re-reads are served by L2.
 NCU_PREFILL_IO_RATIO = {"prefill_small": 0.963, "prefill_long2": 0.988, "prefill_hd128": 0.988, "prefill_sharded": 0.988}
