@@ -109,6 +109,8 @@ WORKLOADS = {
                              scaling="weak"),   # the case profiler captures run on (1.1 GB of cache)
     "qsa_prefill": dict(kind="qsa", rows=2048, requests=1, tokens=32768, hq=8, hkv=1, page=128, fp8=False,
                         scaling="weak"),
+    "qsa_prefill_fp8": dict(kind="qsa", rows=2048, requests=1, tokens=32768, hq=8, hkv=1, page=128, fp8=True,
+                            scaling="weak"),
     "prefill_sharded": dict(kind="prefill", batch=256, hq=64, hkv=8, d=128, page=64, median=8192, sigma=0.75,
                             clip=(1024, 131072), window=None, sink=False, lse=False, scaling="strong"),
 }
