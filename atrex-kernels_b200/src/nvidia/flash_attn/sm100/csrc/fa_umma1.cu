@@ -36,10 +36,13 @@ namespace {
 
 constexpr int kRows = 128;          // packed rows per work item (UMMA M)
 constexpr int kRing = 4;            // K/V ring slots of 32 KB
+// Pairs of every 8 whose exponential runs on the FMA pipe.  FP8 head_dim-256 prefill, alternating builds in one call:
+// 30-step runs 1 574 - 1 586 / 1 579 / 1 602 - 1 606 TFLOP/s with 0 / 1 / 2 of 8; 150-step runs at the power cap
+// 1 540 - 1 550 / 1 559 / 1 504 - 1 510 with 1 / 2 / 3 of 8.
 #ifndef ATREX_UMMA1_POLY_OF8
-#define ATREX_UMMA1_POLY_OF8 1
+#define ATREX_UMMA1_POLY_OF8 2
 #endif
-constexpr int kPolyOf8_1 = ATREX_UMMA1_POLY_OF8;   // pairs of every 8 whose exponential runs on the FMA pipe
+constexpr int kPolyOf8_1 = ATREX_UMMA1_POLY_OF8;
 constexpr int kSoftmaxWarps1 = 8;                 // two threads per row: 2 x 4 warps
 constexpr int kMmaWarp1 = 8, kKWarp1 = 9, kVWarp1 = 10, kQWarp1 = 11;   // warp 11 copies Q where TMA cannot
 constexpr int kThreads1 = (kSoftmaxWarps1 + 4) * 32;       // 384 threads, up to 168 registers each
