@@ -859,12 +859,42 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
             e2e_step(sync=False)
         job.barrier()
         e2e_pipelined_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    # The same step (copy in, the public call, copy out) captured once as a CUDA graph and replayed, waiting for every
+    # step's result: how a serving engine issues its decode steps (the reference's decode tests time graph replays
+    # too, op_test/nvidia/qsa/test_qsa_sm100.py:454-471).  Every replay re-reads the pinned host buffer.
+    e2e_graph_ms = [float("nan")]
+    if not skip_e2e and variant is None and spec["kind"] == "decode":
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            e2e_step(sync=False)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                e2e_step(sync=False)
+        torch.cuda.synchronize()
+        out_host.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(out_host, step(e2e_case).cpu()):
+            raise SystemExit(f"{name}: the graph replay's result differs from the eager call's")
+        e2e_graph_ms = []
+        for _ in range(e2e_samples):
+            job.barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                graph.replay()
+                torch.cuda.current_stream().synchronize()
+            e2e_graph_ms.append((time.perf_counter() - t0) * 1e3 / e2e_steps)
+            job.barrier()
     status = runtime.check_device_status(device)
 
     # ---------------- reduce over ranks: per sample the slowest rank counts ----------------
     sample_ms = job.reduce(sample_ms)
     e2e_sample_ms = job.reduce(e2e_sample_ms)
     e2e_pipelined_ms = job.reduce([e2e_pipelined_ms])[0]
+    e2e_graph_ms = job.reduce(e2e_graph_ms)
     total = job.reduce([float(my_work)], op="sum")[0]
     if rank != 0:
         return None
@@ -929,11 +959,13 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
                  value_min=None if skip_e2e else total / (max(e2e_sample_ms) * 1e-3) / kind["scale"],
                  value_max=None if skip_e2e else total / (min(e2e_sample_ms) * 1e-3) / kind["scale"],
                  pipelined_value=None if skip_e2e else total / (e2e_pipelined_ms * 1e-3) / kind["scale"],
+                 graph_value=(None if e2e_graph_ms[0] != e2e_graph_ms[0] else
+                              total / (statistics.median(e2e_graph_ms) * 1e-3) / kind["scale"]),
                  skipped="Q exceeds the pinned staging limit of this benchmark" if skip_e2e else None,
                  note="per-step inputs (q, cu_seqlens_q, seqused_k, block_table) copied from pinned host memory as one "
                       "staged buffer, O copied back; the paged KV cache is resident device state; `value` waits for "
                       "every step's result before issuing the next, `pipelined_value` queues the same steps and "
-                      "waits once"),
+                      "waits once, `graph_value` replays the step captured as one CUDA graph and waits for every result"),
         gpu_launches=per_step * steps * len(sample_ms), gpu_launches_per_step=per_step,
         clocks=dict(sm_mhz=clocks["sm_mhz"], sm_max_mhz=clocks["sm_max_mhz"], reasons=clocks["reasons"]),
         device_status=status,
