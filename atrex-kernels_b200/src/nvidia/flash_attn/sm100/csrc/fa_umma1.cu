@@ -13,6 +13,10 @@
 //   * TMEM = S0 | S1 | O (tile_n + tile_n + head_dim columns); warp 8 issues QK^T for tile j+1 into
 //     the other S buffer while the softmax warps work on tile j, then P V for tile j as soon as its P
 //     is in TMEM, so the matrix work of one tile hides behind the softmax of the next;
+//   * the score load and row maximum of tile j+1 stay in front of tile j+1 and are not run under the exponentials
+//     of tile j: S(j+1) follows P V(j-1) on the tensor pipe (P lies over S, so the order is fixed) and is complete
+//     only late in tile j's exponentials, and a wait for it there stalls longer than the load costs where it is
+//     (E4M3 head_dim-256 prefill 1 497 against 1 602 TFLOP/s; with P in shared memory, which frees the order, 1 484);
 //   * warps 0-7 are the softmax: TWO threads per row, each with half of the tile's key columns and half
 //     of the O columns, exchanging their partial row maximum through shared memory (two warps per
 //     scheduler keep the MUFU pipe busy where one cannot);
