@@ -866,7 +866,9 @@ def measure_attention(job, name, spec, steps, warmup, samples, *, num_splits=0, 
     # step's result: how a serving engine issues its decode steps (the reference's decode tests time graph replays
     # too, op_test/nvidia/qsa/test_qsa_sm100.py:454-471).  Every replay re-reads the pinned host buffer.
     e2e_graph_ms = [float("nan")]
-    if not skip_e2e and variant is None and spec["kind"] == "decode":
+    # Single-process runs only: with a process group alive its watchdog thread makes CUDA calls of its own, which a
+    # stream capture in the default (global) mode does not tolerate.
+    if not skip_e2e and variant is None and spec["kind"] == "decode" and world == 1:
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
